@@ -1,0 +1,114 @@
+/*
+ * uniql_b200 — C ABI of the B200 (sm_100a) kernels behind UniQL's W4A16 hot path.
+ *
+ * Plain pointers and sizes only; no torch types.  All pointers are DEVICE
+ * pointers unless a comment says otherwise.  Every function enqueues work on
+ * `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream)
+ * and returns without synchronising.  Return value: 0 on success, a negative
+ * UNIQL_E* code otherwise (nothing was enqueued in that case).  No function
+ * allocates device memory unless its comment says so; scratch is supplied by
+ * the caller.  Nothing throws across this boundary.
+ *
+ * Reference citations are paths inside the UniQL project.
+ */
+#ifndef UNIQL_B200_H_
+#define UNIQL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define UNIQL_ABI_VERSION 1
+
+enum {
+  UNIQL_OK = 0,
+  UNIQL_EINVAL = -1,       /* null pointer, negative size, misaligned pointer          */
+  UNIQL_EGROUPSIZE = -2,   /* groupsize other than 128 (per-channel mode unsupported)   */
+  UNIQL_ESHAPE = -3,       /* n % 64 != 0, k % 128 != 0, dim not a supported size, ...  */
+  UNIQL_ESCRATCH = -4,     /* scratch buffer missing or too small                       */
+  UNIQL_ECUDA = -5,        /* a CUDA runtime call failed (see uniql_last_cuda_error)    */
+  UNIQL_EDTYPE = -6        /* unsupported element type code                             */
+};
+
+/* Element type codes for uniql_hadamard. */
+enum { UNIQL_F16 = 0, UNIQL_BF16 = 1, UNIQL_F32 = 2 };
+
+/* Bits that kernels OR into *status_word (device int, may be NULL). */
+enum {
+  UNIQL_STATUS_BAD_TOKEN_ID = 1   /* an embedding id was outside [0, vocab); row written as zeros */
+};
+
+int uniql_abi_version(void);
+const char* uniql_strerror(int code);
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
+int uniql_last_cuda_error(void);
+
+/*
+ * W4A16 linear forward:  D[m, 0:n_out] = A[m, k] * dequant(B, s) (+ bias), fp32 accumulation, fp16 output.
+ * Replaces quant_linear_cuda.w4a16o16_gemm (csrc/linear/quant_linear.cpp:6-24, host wrapper
+ * csrc/linear/marlin_gemm_kernel.cuh:991-1052) and the bias add / padding slice of
+ * W4A16B16O16Linear.forward (quantize/quant_linear_layers.py:91-116).
+ *
+ *   A          fp16 [m, k], row stride lda elements (lda >= k, rows 16-byte aligned)
+ *   B          int32 [k/16, 2*n] packed int4 in the reference's permuted order
+ *              (quantize/quantize_helpers.py:145-165, 67-84)
+ *   s          fp16 [k/128, n] group scales in the reference's permuted order (:54-62, 169-180)
+ *   bias       fp16 [n_out] or NULL
+ *   D          fp16 [m, n_out], row stride ldd elements
+ *   n          stored (padded) output width, multiple of 64; n_out <= n columns are written
+ *   k          multiple of 128
+ *   groupsize  128; -1 (per-channel) returns UNIQL_EGROUPSIZE
+ *   hadamard_dim  0, or k: apply y = H_k * x / sqrt(k) to every row of A first
+ *              (quantize/quant_hadamard_layers.py:16-18 placed in front of the linear);
+ *              the transformed rows are rounded to fp16 exactly as the separate module would.
+ *   scratch    device buffer of at least uniql_w4a16_scratch_bytes(m, n, k, hadamard_dim) bytes,
+ *              256-byte aligned.  Its first UNIQL_SCRATCH_COUNTER_BYTES bytes must be zero before the
+ *              first call and are left zero by every call; do not share one scratch buffer between
+ *              calls that may overlap on the GPU.
+ *   status_word  optional device int for kernel-side diagnostics (unused bits stay untouched)
+ */
+#define UNIQL_SCRATCH_COUNTER_BYTES 16384
+int uniql_w4a16_linear(const void* A, int64_t lda, const void* B, const void* s, const void* bias,
+                       void* D, int64_t ldd, int64_t m, int64_t n, int64_t n_out, int64_t k,
+                       int groupsize, int64_t hadamard_dim, void* scratch, size_t scratch_bytes,
+                       int* status_word, void* stream);
+
+/* Scratch requirement of uniql_w4a16_linear for this problem on the current device. */
+size_t uniql_w4a16_scratch_bytes(int64_t m, int64_t n, int64_t k, int64_t hadamard_dim);
+
+/*
+ * 4-bit embedding gather: out[t, :] = fp16((q - 8) * scales[ids[t]]), bit-exact with
+ * quant_embedding_cuda.w4a16_embedding_lookup (csrc/embedding/quant_embedding.cpp:3-8,
+ * kernel csrc/embedding/quant_embedding_kernel.cuh:47-114).
+ *
+ *   ids     int64 [n_ids]
+ *   W       int32 [vocab, dim/8]  (quantize/quant_embedding_layers.py:33-43 packing)
+ *   scales  fp16 [vocab]
+ *   out     fp16 [n_ids, dim]
+ *   dim     multiple of 8
+ * An id outside [0, vocab) writes a zero row and sets UNIQL_STATUS_BAD_TOKEN_ID in *status_word
+ * (the reference reads out of bounds there).
+ */
+int uniql_w4_embedding(const int64_t* ids, int64_t n_ids, const void* W, const void* scales,
+                       void* out, int64_t vocab, int64_t dim, int* status_word, void* stream);
+
+/*
+ * Hadamard transform along the last axis: y[r, :] = (H_dim x[r, :]) * scale.
+ * Replaces fast_hadamard_transform_cuda.fast_hadamard_transform{,_12N,_20N,_28N,_40N}
+ * (call sites quantize/hadamard_helpers.py:18-48).  dim = base * 2^j with base chosen in the
+ * reference's order 40, 28, 20, 12, else 1 (power of two).  x and y may alias.
+ *   dtype  UNIQL_F16 / UNIQL_BF16 / UNIQL_F32 (both x and y); arithmetic is fp32.
+ */
+int uniql_hadamard(const void* x, void* y, int64_t rows, int64_t dim, float scale, int dtype, void* stream);
+
+/* Host helper: writes the base x base ±1 matrix (row-major int8) this library uses for
+ * base in {12, 20, 28, 40}; `out` is a HOST pointer.  Returns UNIQL_ESHAPE for other orders. */
+int uniql_hadamard_base_matrix(int base, int8_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UNIQL_B200_H_ */

@@ -1,0 +1,82 @@
+"""GPU: Hadamard transform (power-of-two and 12N/20N/28N/40N) and the fused Hadamard + linear.
+Power-of-two sizes follow the unambiguous Sylvester definition.  For 12N/20N/28N/40N the reference's
+third-party matrices are unavailable, so parity there is against this build's own (Paley) matrices."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import linear_tolerance_check, make_acts, quantized_layer
+from oracle import uniql_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+DIMS = [8, 64, 256, 512, 4096, 8192, 32768, 96, 768, 1536, 160, 5120, 224, 3584, 14336, 320, 10240, 40960]
+
+
+@pytest.mark.parametrize("dim", DIMS)
+@pytest.mark.parametrize("rows", [1, 5])
+def test_transform_fp32(dim, rows):
+    from uniql_b200 import ops
+    rng = np.random.default_rng(dim + rows)
+    x = rng.standard_normal((rows, dim)).astype(np.float32)
+    y = ops.hadamard(torch.from_numpy(x).cuda(), 1.0 / np.sqrt(dim)).cpu().numpy()
+    want = orc.hadamard_transform(x.astype(np.float64))
+    assert np.abs(y - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("dim", [4096, 14336, 8192, 3584])
+def test_transform_16bit(dim, dtype):
+    from uniql_b200 import ops
+    x = make_acts(dim, 3, dim).to(dtype)
+    y = ops.hadamard(x.cuda(), 1.0 / np.sqrt(dim)).cpu()
+    want = orc.hadamard_transform(x.double().numpy())
+    eps = 2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7
+    assert np.abs(y.double().numpy() - want).max() <= eps * np.abs(want).max() + 1e-6
+    assert y.dtype == dtype
+
+
+def test_module_and_helpers_follow_reference_dispatch():
+    from uniql_b200.quantize.hadamard_helpers import get_had_fn, had_transform
+    from uniql_b200.quantize.quant_hadamard_layers import Hadamard
+    assert get_had_fn(14336)[1] == 28 and get_had_fn(8192)[1] == 2 and get_had_fn(5120)[1] == 40
+    with pytest.raises(AssertionError):
+        get_had_fn(12160)
+    had = Hadamard(3584).to("cuda")
+    x = make_acts(1, 6, 3584).cuda().reshape(2, 3, 3584)
+    y = had(x)
+    assert y.shape == x.shape and y.data_ptr() != x.data_ptr()
+    want = orc.hadamard_transform(x.double().cpu().numpy())
+    assert np.abs(y.double().cpu().numpy() - want).max() <= 2e-3 * np.abs(want).max()
+    w = torch.randn(16, 512, device="cuda", dtype=torch.float16)
+    assert torch.allclose(had_transform(had_transform(w)).float(), w.float(), atol=2e-2)
+
+
+@pytest.mark.parametrize("n,k", [(4096, 14336), (4096, 8192), (256, 3584), (512, 1536)])
+@pytest.mark.parametrize("m", [1, 4, 16, 40])
+def test_fused_hadamard_linear(n, k, m):
+    """linear(Hadamard(x)) with the transformed activations rounded to fp16 in between."""
+    from uniql_b200 import ops
+    layer = quantized_layer(n + k + 1, n, k)
+    x = make_acts(m, m, k)
+    y = ops.w4a16_linear(x.cuda(), torch.from_numpy(layer["packed"]).cuda(), torch.from_numpy(layer["scales"]).cuda(),
+                         None, n, hadamard_dim=k).cpu().numpy()
+    xh = orc.hadamard_transform(x.double().numpy()).astype(np.float16)
+    want = orc.linear_ref(xh, None, None, None, n, w_deq=layer["w_deq"])
+    linear_tolerance_check(y, want)
+    # and it equals the two-step module composition bit for bit
+    xh_gpu = ops.hadamard(x.cuda(), 1.0 / np.sqrt(k))
+    y2 = ops.w4a16_linear(xh_gpu, torch.from_numpy(layer["packed"]).cuda(), torch.from_numpy(layer["scales"]).cuda(),
+                          None, n).cpu().numpy()
+    assert np.array_equal(y.view(np.uint16), y2.view(np.uint16))
+
+
+def test_had_linear_offline_rotation_matches_online():
+    """HadLinear folds H into the weight; y = x W^T must equal (xH)(WH)^T."""
+    from uniql_b200.quantize.quant_linear_layers import HadLinear
+    lin = torch.nn.Linear(512, 64, bias=False).half().cuda()
+    had = HadLinear(lin, input_transform=True, output_transform=False, fuse_had=True)
+    from uniql_b200 import ops
+    x = torch.randn(4, 512, device="cuda", dtype=torch.float16)
+    y = had(ops.hadamard(x, 1.0 / np.sqrt(512)))
+    assert torch.allclose(y.float(), (x.float() @ lin.weight.float().t()), atol=3e-2)

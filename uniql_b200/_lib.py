@@ -1,0 +1,62 @@
+"""ctypes binding of libuniql_b200.so (the C ABI declared in include/uniql_b200.h).
+
+There is no fallback: if the library is missing or a call fails, a RuntimeError is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from ._build import LIB_PATH
+
+_c = ctypes
+_lib = None
+
+# name -> (restype, argtypes); must list every symbol include/uniql_b200.h declares
+SYMBOLS = {
+    "uniql_abi_version": (_c.c_int, []),
+    "uniql_strerror": (_c.c_char_p, [_c.c_int]),
+    "uniql_last_cuda_error": (_c.c_int, []),
+    "uniql_w4a16_linear": (_c.c_int, [
+        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64,
+        _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_size_t,
+        _c.c_void_p, _c.c_void_p]),
+    "uniql_w4a16_scratch_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64]),
+    "uniql_w4_embedding": (_c.c_int, [
+        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64,
+        _c.c_void_p, _c.c_void_p]),
+    "uniql_hadamard": (_c.c_int, [
+        _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_float, _c.c_int, _c.c_void_p]),
+    "uniql_hadamard_base_matrix": (_c.c_int, [_c.c_int, _c.c_void_p]),
+}
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m uniql_b200._build` "
+                "(needs nvcc). uniql_b200 has no CPU or PyTorch fallback.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+class UniqlError(RuntimeError):
+    def __init__(self, code: int, where: str):
+        msg = lib().uniql_strerror(code).decode()
+        if code == -5:
+            msg += f" [cudaError {lib().uniql_last_cuda_error()}]"
+        super().__init__(f"{where}: {msg} (code {code})")
+        self.code = code
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        raise UniqlError(code, where)

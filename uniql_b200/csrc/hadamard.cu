@@ -1,0 +1,324 @@
+// Hadamard transform along the last axis for sm_100a:  y = (H_base (x) H_{2^j}) x * scale.
+//
+// Replaces the third-party fast_hadamard_transform_cuda entry points UniQL calls from
+// quantize/hadamard_helpers.py:18-48 (power-of-two, 12N, 20N, 28N, 40N).  The index splits as
+// i = a * 2^j + b: b runs through a Sylvester-ordered Walsh-Hadamard transform, a through a fixed
+// base x base Hadamard matrix (Paley I for 12 and 20, Paley II for 28, H_2 (x) H_20 for 40).
+//
+// One CTA per row.  Pass A: each thread takes 8 contiguous elements (one 16-byte load for 16-bit
+// types), does 3 butterfly stages in registers and up to 5 more with warp shuffles, and parks the
+// result in shared memory as fp32.  Pass B: the remaining stages run radix-8/4/2 out of shared
+// memory with a stride >= 256 (bank-conflict free).  Pass C: the base matrix is applied per column b
+// with signs taken from a bit mask in the kernel parameters, scaled, converted and stored coalesced.
+// HBM-bound for many rows (2 * dim * sizeof(T) bytes per row); latency-bound for a single row.
+#include "common.cuh"
+#include "linear_internal.cuh"
+
+namespace uniql {
+
+struct HadSigns {
+  uint64_t row[40];   // bit a' of row[a] set  <=>  H[a][a'] = -1
+};
+
+// ------------------------------------------------------------- base matrices (host, deterministic)
+static int legendre(int a, int q) {
+  a %= q;
+  if (a < 0) a += q;
+  if (a == 0) return 0;
+  long long r = 1, b = a;
+  int e = (q - 1) / 2;
+  while (e) {
+    if (e & 1) r = r * b % q;
+    b = b * b % q;
+    e >>= 1;
+  }
+  return r == 1 ? 1 : -1;
+}
+
+static void paley1(int q, int8_t* h) {   // order q + 1, q = 3 mod 4
+  const int n = q + 1;
+  for (int i = 0; i < n; ++i)
+    for (int j = 0; j < n; ++j) {
+      int v;
+      if (i == 0 && j == 0) v = 0;
+      else if (i == 0) v = 1;
+      else if (j == 0) v = -1;
+      else v = legendre(j - i, q);
+      if (i == j) v += 1;
+      h[i * n + j] = (int8_t)v;
+    }
+}
+
+static void paley2(int q, int8_t* h) {   // order 2(q + 1), q = 1 mod 4
+  const int n = q + 1, n2 = 2 * n;
+  for (int i = 0; i < n; ++i)
+    for (int j = 0; j < n; ++j) {
+      int cij;
+      if (i == 0 && j == 0) cij = 0;
+      else if (i == 0 || j == 0) cij = 1;
+      else cij = legendre(j - i, q);
+      int blk[4];
+      if (cij == 0) { blk[0] = 1; blk[1] = 1; blk[2] = 1; blk[3] = -1; }
+      else { blk[0] = cij; blk[1] = -cij; blk[2] = -cij; blk[3] = -cij; }
+      h[(2 * i) * n2 + 2 * j] = (int8_t)blk[0];
+      h[(2 * i) * n2 + 2 * j + 1] = (int8_t)blk[1];
+      h[(2 * i + 1) * n2 + 2 * j] = (int8_t)blk[2];
+      h[(2 * i + 1) * n2 + 2 * j + 1] = (int8_t)blk[3];
+    }
+}
+
+static int base_matrix(int base, int8_t* h) {
+  if (base == 12) paley1(11, h);
+  else if (base == 20) paley1(19, h);
+  else if (base == 28) paley2(13, h);
+  else if (base == 40) {
+    int8_t h20[400];
+    paley1(19, h20);
+    for (int i = 0; i < 40; ++i)
+      for (int j = 0; j < 40; ++j) {
+        int v = h20[(i % 20) * 20 + (j % 20)];
+        if (i >= 20 && j >= 20) v = -v;
+        h[i * 40 + j] = (int8_t)v;
+      }
+  } else return UNIQL_ESHAPE;
+  return UNIQL_OK;
+}
+
+static bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
+
+int hadamard_base_of(int64_t dim) {
+  if (dim <= 0) return 0;
+  const int bases[4] = {40, 28, 20, 12};   // the reference's dispatch order
+  for (int b : bases)
+    if (dim % b == 0 && is_pow2(dim / b)) return b;
+  return is_pow2(dim) ? 1 : 0;
+}
+
+// ------------------------------------------------------------- element access
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store8(__half* p, const float (&v)[8]) {
+    uint4 r;
+    __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+  }
+  static __device__ __forceinline__ void store1(__half* p, float v) { *p = __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+  }
+  static __device__ __forceinline__ void store1(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+template <> struct Elem<float> {
+  static __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+  static __device__ __forceinline__ void store1(float* p, float v) { *p = v; }
+};
+
+template <int R>
+__device__ __forceinline__ void butterflies(float (&v)[R]) {
+#pragma unroll
+  for (int s = 1; s < R; s <<= 1)
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (!(i & s)) {
+        const float a = v[i], b = v[i | s];
+        v[i] = a + b;
+        v[i | s] = a - b;
+      }
+}
+
+template <int R>
+__device__ __forceinline__ void strided_pass(float* buf, int dim, int h, int tid, int nthreads) {
+  const int groups = dim / R;
+  for (int idx = tid; idx < groups; idx += nthreads) {
+    const int low = idx % h, high = idx / h;
+    float* p = buf + (size_t)high * h * R + low;
+    float v[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) v[i] = p[(size_t)i * h];
+    butterflies<R>(v);
+#pragma unroll
+    for (int i = 0; i < R; ++i) p[(size_t)i * h] = v[i];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) hadamard_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y,
+                                                       int64_t ldy, int dim, int P, int base, float scale,
+                                                       const HadSigns signs, int pdl_trigger) {
+  extern __shared__ __align__(16) float buf[];
+  if (pdl_trigger) pdl_launch_dependents();   // the dependent kernel only prefetches until it waits on us
+  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31;
+  const T* xr = x + (int64_t)blockIdx.x * ldx;
+  T* yr = y + (int64_t)blockIdx.x * ldy;
+
+  // ---- pass A: 8 contiguous elements per thread, stages h = 1..128 (limited by P) ----
+  const int nchunks = dim >> 3;
+  const int nchunks_pad = (nchunks + 31) & ~31;
+  const bool only_a = (base == 1 && P <= 256);   // whole transform fits pass A: store straight from registers
+  for (int ch = tid; ch < nchunks_pad; ch += nthreads) {
+    float v[8];
+    if (ch < nchunks) Elem<T>::load8(xr + (size_t)ch * 8, v);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    butterflies<8>(v);
+#pragma unroll
+    for (int s = 0; s < 5; ++s) {
+      if ((8 << s) < P) {
+        const bool upper = (lane >> s) & 1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float o = __shfl_xor_sync(0xffffffffu, v[i], 1 << s);
+          v[i] = upper ? (o - v[i]) : (v[i] + o);
+        }
+      }
+    }
+    if (ch < nchunks) {
+      if (only_a) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= scale;
+        Elem<T>::store8(yr + (size_t)ch * 8, v);
+      } else {
+        float4* d = reinterpret_cast<float4*>(buf + (size_t)ch * 8);
+        d[0] = make_float4(v[0], v[1], v[2], v[3]);
+        d[1] = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    }
+  }
+  if (only_a) return;
+  __syncthreads();
+
+  // ---- pass B: stages h = 256 .. P/2 out of shared memory ----
+  for (int h = 256; h < P;) {
+    const int rem = P / h;
+    if (rem >= 8) { strided_pass<8>(buf, dim, h, tid, nthreads); h *= 8; }
+    else if (rem == 4) { strided_pass<4>(buf, dim, h, tid, nthreads); h *= 4; }
+    else { strided_pass<2>(buf, dim, h, tid, nthreads); h *= 2; }
+    __syncthreads();
+  }
+
+  // ---- pass C: base matrix across the `base` segments, scale, store ----
+  if (base == 1) {
+    for (int ch = tid; ch < nchunks; ch += nthreads) {
+      float v[8];
+      const float4* s4 = reinterpret_cast<const float4*>(buf + (size_t)ch * 8);
+      const float4 a = s4[0], b = s4[1];
+      v[0] = a.x * scale; v[1] = a.y * scale; v[2] = a.z * scale; v[3] = a.w * scale;
+      v[4] = b.x * scale; v[5] = b.y * scale; v[6] = b.z * scale; v[7] = b.w * scale;
+      Elem<T>::store8(yr + (size_t)ch * 8, v);
+    }
+    return;
+  }
+  int asplit = nthreads / P;            // spread the output rows of a column over idle threads
+  if (asplit < 1) asplit = 1;
+  if (asplit > 8) asplit = 8;
+  const int tasks = P * asplit;
+  for (int task = tid; task < tasks; task += nthreads) {
+    const int b = task % P, part = task / P;
+    const int a_lo = base * part / asplit, a_hi = base * (part + 1) / asplit;
+    float z[40];
+#pragma unroll
+    for (int a = 0; a < 40; ++a) z[a] = (a < base) ? buf[(size_t)a * P + b] : 0.f;
+    for (int a = a_lo; a < a_hi; ++a) {
+      const uint64_t mask = signs.row[a];
+      float sum = 0.f;
+#pragma unroll
+      for (int ap = 0; ap < 40; ++ap) {
+        const uint32_t flip = (uint32_t)((mask >> ap) & 1ull) << 31;
+        sum += __uint_as_float(__float_as_uint(z[ap]) ^ flip);
+      }
+      Elem<T>::store1(yr + (size_t)a * P + b, sum * scale);
+    }
+  }
+}
+
+int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
+                    int dtype, bool pdl_trigger, cudaStream_t stream) {
+  const int base = hadamard_base_of(dim);
+  if (base == 0) return UNIQL_ESHAPE;
+  const int64_t P = dim / base;
+  if (P < 8 || dim > 40960) return UNIQL_ESHAPE;
+  if (rows == 0) return UNIQL_OK;
+  HadSigns signs;
+  for (int i = 0; i < 40; ++i) signs.row[i] = 0;
+  if (base > 1) {
+    int8_t h[1600];
+    base_matrix(base, h);
+    for (int i = 0; i < base; ++i)
+      for (int j = 0; j < base; ++j)
+        if (h[i * base + j] < 0) signs.row[i] |= (1ull << j);
+  }
+  int threads = (int)((dim / 8 + 31) / 32 * 32);
+  if (threads < 64) threads = 64;
+  if (threads > 512) threads = 512;
+  const size_t smem = (size_t)dim * sizeof(float);
+
+#define UNIQL_HAD_LAUNCH(T)                                                                                   \
+  do {                                                                                                        \
+    static thread_local bool attr_done = false;                                                               \
+    if (smem > 48 * 1024 && !attr_done) {                                                                     \
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(hadamard_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                          40960 * (int)sizeof(float)));                                       \
+      attr_done = true;                                                                                       \
+    }                                                                                                         \
+    for (int64_t r0 = 0; r0 < rows; r0 += 1 << 30) {                                                          \
+      const int64_t nr = rows - r0 < (1 << 30) ? rows - r0 : (1 << 30);                                       \
+      hadamard_kernel<T><<<(unsigned)nr, threads, smem, stream>>>((const T*)x + r0 * ldx, ldx, (T*)y + r0 * ldy, \
+                                                                  ldy, (int)dim, (int)P, base, scale, signs,  \
+                                                                  pdl_trigger ? 1 : 0);                       \
+    }                                                                                                         \
+  } while (0)
+
+  if (dtype == UNIQL_F16) UNIQL_HAD_LAUNCH(__half);
+  else if (dtype == UNIQL_BF16) UNIQL_HAD_LAUNCH(__nv_bfloat16);
+  else if (dtype == UNIQL_F32) UNIQL_HAD_LAUNCH(float);
+  else return UNIQL_EDTYPE;
+#undef UNIQL_HAD_LAUNCH
+  return launch_status();
+}
+
+}  // namespace uniql
+
+extern "C" int uniql_hadamard(const void* x, void* y, int64_t rows, int64_t dim, float scale, int dtype,
+                              void* stream) {
+  using namespace uniql;
+  if (rows < 0 || dim <= 0) return UNIQL_EINVAL;
+  if (dtype != UNIQL_F16 && dtype != UNIQL_BF16 && dtype != UNIQL_F32) return UNIQL_EDTYPE;
+  if (hadamard_base_of(dim) == 0) return UNIQL_ESHAPE;
+  if (rows == 0) return UNIQL_OK;
+  if (!x || !y || !aligned16(x) || !aligned16(y)) return UNIQL_EINVAL;
+  return launch_hadamard(x, dim, y, dim, rows, dim, scale, dtype, false, (cudaStream_t)stream);
+}
+
+extern "C" int uniql_hadamard_base_matrix(int base, int8_t* out) {
+  if (!out) return UNIQL_EINVAL;
+  return uniql::base_matrix(base, out);
+}

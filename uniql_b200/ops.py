@@ -1,0 +1,135 @@
+"""Torch-facing wrappers over the C ABI: allocate outputs/scratch with torch, pass raw pointers.
+
+These functions are what the drop-in modules and the `quant_linear_cuda` / `quant_embedding_cuda` /
+`fast_hadamard_transform_cuda` stand-ins call.  All of them require CUDA tensors; there is no fallback.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, lib
+
+_DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+_scratch: dict = {}      # (device index, stream handle) -> uint8 tensor whose counter region is zero
+_status: dict = {}       # device index -> int32[1] status word
+
+
+def _stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def read_and_clear_status(device) -> int:
+    """Synchronising read of the kernel diagnostics word (bit 0: an embedding id was out of range)."""
+    t = status_word(torch.device(device))
+    v = int(t.item())
+    t.zero_()
+    return v
+
+
+def _scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, _stream_handle(device))
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(nbytes, 1 << 20)
+        size = (size + (1 << 20) - 1) >> 20 << 20
+        buf = torch.zeros(size, dtype=torch.uint8, device=torch.device("cuda", idx))
+        _scratch[key] = buf
+    return buf
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (uniql_b200 has no CPU path)")
+
+
+def w4a16_linear(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, bias: torch.Tensor | None,
+                 n_out: int, hadamard_dim: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[m, n_out] = x[m, k] @ dequant(weight, scale)[:, :n_out] (+ bias); x fp16 2-D, row-major."""
+    _require_cuda(x, "x"); _require_cuda(weight, "weight"); _require_cuda(scale, "scale")
+    if x.dtype != torch.float16 or x.dim() != 2:
+        raise RuntimeError("x must be a 2-D float16 tensor")
+    if weight.dtype != torch.int32 or scale.dtype != torch.float16:
+        raise RuntimeError("weight must be int32 and scale float16")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    m, k = x.shape
+    if weight.shape[0] * 16 != k:
+        raise RuntimeError(f"size_k mismatch: x has {k} columns, packed weight covers {weight.shape[0] * 16}")
+    n = weight.shape[1] // 2
+    if scale.shape[0] == 1 and k != 128:
+        groupsize = -1
+    else:
+        if k % scale.shape[0] != 0:
+            raise RuntimeError("scale rows do not divide k")
+        groupsize = k // scale.shape[0]
+    if scale.shape[1] != n:
+        raise RuntimeError("scale width does not match the packed weight")
+    if not weight.is_contiguous() or not scale.is_contiguous():
+        raise RuntimeError("weight and scale must be contiguous")
+    if bias is not None:
+        if bias.dtype != torch.float16 or bias.numel() < n_out or not bias.is_contiguous():
+            raise RuntimeError("bias must be a contiguous float16 tensor with at least n_out elements")
+    if (m > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
+        x = x.clone(memory_format=torch.contiguous_format)
+    lda = x.stride(0) if m > 1 else k
+    if out is None:
+        out = torch.empty((m, n_out), dtype=torch.float16, device=x.device)
+    L = lib()
+    with torch.cuda.device(x.device):
+        nbytes = L.uniql_w4a16_scratch_bytes(m, n, k, hadamard_dim)
+        scratch = _scratch_for(x.device, nbytes)
+        code = L.uniql_w4a16_linear(
+            x.data_ptr(), lda, weight.data_ptr(), scale.data_ptr(), bias.data_ptr() if bias is not None else None,
+            out.data_ptr(), out.stride(0), m, n, n_out, k, groupsize, hadamard_dim,
+            scratch.data_ptr(), scratch.numel(), status_word(x.device).data_ptr(), _stream_handle(x.device))
+    check(code, "uniql_w4a16_linear")
+    return out
+
+
+def w4_embedding(ids: torch.Tensor, weight: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """out[..., :] = dequantised rows of the 4-bit table for int64 ids of shape [T] or [B, T]."""
+    _require_cuda(ids, "input"); _require_cuda(weight, "weight"); _require_cuda(scales, "scale")
+    if weight.dim() != 2 or weight.dtype != torch.int32:
+        raise RuntimeError("weight must be a 2-D int32 tensor")
+    if scales.dim() != 1 or scales.dtype != torch.float16 or scales.numel() != weight.shape[0]:
+        raise RuntimeError("scale must be a 1-D float16 tensor with one entry per table row")
+    if ids.dim() not in (1, 2) or ids.dtype != torch.int64:
+        raise RuntimeError("input must be a 1-D or 2-D int64 tensor")
+    ids_c = ids.contiguous()
+    weight = weight.contiguous()
+    vocab, words = weight.shape
+    dim = words * 8
+    out = torch.empty((*ids.shape, dim), dtype=torch.float16, device=ids.device)
+    with torch.cuda.device(ids.device):
+        code = lib().uniql_w4_embedding(
+            ids_c.data_ptr(), ids_c.numel(), weight.data_ptr(), scales.contiguous().data_ptr(), out.data_ptr(),
+            vocab, dim, status_word(ids.device).data_ptr(), _stream_handle(ids.device))
+    check(code, "uniql_w4_embedding")
+    return out
+
+
+def hadamard(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """New tensor y = H x * scale along the last axis (x is made contiguous first)."""
+    _require_cuda(x, "x")
+    if x.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"unsupported dtype {x.dtype}")
+    xc = x.contiguous()
+    dim = xc.shape[-1]
+    rows = xc.numel() // dim if dim else 0
+    y = torch.empty_like(xc)
+    with torch.cuda.device(x.device):
+        code = lib().uniql_hadamard(xc.data_ptr(), y.data_ptr(), rows, dim, float(scale), _DTYPE_CODE[x.dtype],
+                                    _stream_handle(x.device))
+    check(code, "uniql_hadamard")
+    return y
