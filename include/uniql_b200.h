@@ -38,7 +38,8 @@ enum { UNIQL_F16 = 0, UNIQL_BF16 = 1, UNIQL_F32 = 2 };
 
 /* Bits that kernels OR into *status_word (device int, may be NULL). */
 enum {
-  UNIQL_STATUS_BAD_TOKEN_ID = 1   /* an embedding id was outside [0, vocab); row written as zeros */
+  UNIQL_STATUS_BAD_TOKEN_ID = 1,  /* an embedding id was outside [0, vocab); row written as zeros */
+  UNIQL_STATUS_WAIT_TIMEOUT = 2   /* a bounded wait on an asynchronous copy gave up; the output is invalid */
 };
 
 int uniql_abi_version(void);

@@ -10,7 +10,7 @@ from oracle import uniql_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
-DIMS = [8, 64, 256, 512, 4096, 8192, 32768, 96, 768, 1536, 160, 5120, 224, 3584, 14336, 320, 10240, 40960]
+DIMS = [8, 64, 256, 512, 4096, 8192, 32768, 96, 768, 1536, 640, 5120, 224, 3584, 14336, 320, 10240, 40960]
 
 
 @pytest.mark.parametrize("dim", DIMS)

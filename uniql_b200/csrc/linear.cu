@@ -92,8 +92,8 @@ extern "C" int uniql_w4a16_linear(const void* A, int64_t lda, const void* B, con
   bool pdl = false;
   if (hadamard_dim) {
     __half* xh = (__half*)((char*)scratch + L.xh_off);
-    pdl = decode && m <= 16;   // let the weight stream start while the transform runs
-    int st = launch_hadamard(A, lda, xh, k, m, k, 1.0f / sqrtf((float)k), UNIQL_F16, pdl, stream);
+    pdl = decode;   // let the weight stream start while the transform runs
+    int st = launch_hadamard(A, lda, xh, k, m, k, (float)(1.0 / sqrt((double)k)), UNIQL_F16, pdl, stream);
     if (st != UNIQL_OK) return st;
     Ain = xh;
     lda = k;

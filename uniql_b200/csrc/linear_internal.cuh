@@ -18,7 +18,7 @@ struct LinearArgs {
 };
 
 struct GemvPlan {
-  int WN, WK, S, GCH, MT;
+  int WN, WK, S, GCH, MT, R, xs_rows;
   size_t smem;
   size_t partial_bytes;
 };

@@ -32,6 +32,8 @@ constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = 8;
 constexpr int kRedStride = 68;  // floats per row of a warp's 64-column reduction tile (+4: conflict-free scatter)
 
+constexpr int kSlotBytes = 4096;   // one quantisation group (8 packed rows) of one 64-column block
+
 struct GemvParams {
   const __half* A;
   int64_t lda;
@@ -41,54 +43,164 @@ struct GemvParams {
   __half* D;
   int64_t ldd;
   int M, N, n_out, KT, nblk;
-  int WN, WK, S_split, GCH;
+  int WN, WK, log_wn, S_split, GCH, R;
   int xs_stride;        // halves per staged activation row (GCH*128 + 8)
+  int xs_rows;          // staged rows per warp row: min(M, 8*MT) + 1 (the extra row stays zero)
   float* partials;      // [S_split][M][N]
   int* counters;        // [gridDim.x], zero on entry, zero on exit
-  int pdl;              // 1: launched as a programmatic dependent of the kernel that produces A
+  int* status_word;
 };
+
+// ---- mbarrier / bulk-copy (TMA engine, untiled) helpers -------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: gives up after ~2^20 polls and reports it instead of hanging.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int it = 0; it < (1 << 20); ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// One quantisation group (8 packed rows) of one 64-column block, read from this warp's ring slot.
+// Nibbles are turned into fp16 values (1024 + q) and (64 + q) by a single LOP3 each; the offsets are taken
+// out again through `corr`, an extra MMA whose 16-row operand is the constant (1032 | 72):
+//   sum_k (off_k + q) x  -  sum_k (off_k + 8) x  =  sum_k (q - 8) x.
+template <int MT, bool CHECK>
+__device__ __forceinline__ void gemv_group(uint32_t slot_addr, float (&accg)[MT][4][4], float (&corr)[MT][4],
+                                           const __half* xl, int xs_tile_stride, int kt_base, int w0, int w1) {
+  const uint32_t kcorr[4] = {0x64086408u, 0x64086408u, 0x54805480u, 0x54805480u};   // 1032, 1032, 72, 72
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int kt = kt_base + u;
+    if (!CHECK || (kt >= w0 && kt < w1)) {
+      const uint4 w4 = lds128(slot_addr + u * 512);
+      uint32_t b0[MT], b1[MT];
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        const __half* xr = xl + (size_t)t * xs_tile_stride + u * 16;
+        b0[t] = *reinterpret_cast<const uint32_t*>(xr);
+        b1[t] = *reinterpret_cast<const uint32_t*>(xr + 8);
+      }
+#pragma unroll
+      for (int t = 0; t < MT; ++t) mma_m16n8k16(corr[t], kcorr, b0[t], b1[t]);
+      const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t a[4];
+        const uint32_t q = wq[j], qs = wq[j] >> 8;
+        a[0] = lop3_and_or(q, 0x000f000fu, 0x64006400u);     // n = 16j+g,   k = 2c, 2c+1    : 1024 + q
+        a[2] = lop3_and_or(q, 0x00f000f0u, 0x54005400u);     // n = 16j+g,   k = 2c+8, 2c+9  :   64 + q
+        a[1] = lop3_and_or(qs, 0x000f000fu, 0x64006400u);    // n = 16j+g+8, k = 2c, 2c+1
+        a[3] = lop3_and_or(qs, 0x00f000f0u, 0x54005400u);    // n = 16j+g+8, k = 2c+8, 2c+9
+#pragma unroll
+        for (int t = 0; t < MT; ++t) mma_m16n8k16(accg[t][j], a, b0[t], b1[t]);
+      }
+    }
+  }
+}
 
 template <int MT>
 __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvParams p) {
-  extern __shared__ __align__(16) uint8_t smem_raw[];
+  extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ int s_is_last;
+  __shared__ __align__(8) uint64_t s_bars[kGemvWarps * 4];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
-  const int wn = warp % p.WN, wk = warp / p.WN;
+  const int wn = warp & (p.WN - 1), wk = warp >> p.log_wn;
   const int blk = blockIdx.x * p.WN + wn;
   const bool active = blk < p.nblk;
 
   // k-range of this CTA, then of this warp row (contiguous, balanced to one packed row).
   const int cta_k0 = (int)((int64_t)p.KT * blockIdx.y / p.S_split);
   const int cta_k1 = (int)((int64_t)p.KT * (blockIdx.y + 1) / p.S_split);
-  const int w0 = cta_k0 + (int)((int64_t)(cta_k1 - cta_k0) * wk / p.WK);
-  const int w1 = cta_k0 + (int)((int64_t)(cta_k1 - cta_k0) * (wk + 1) / p.WK);
-  const int g0 = w0 >> 3, g1 = (w1 + 7) >> 3;   // quantisation groups touched (8 packed rows each)
+  const int rw0 = cta_k0 + (cta_k1 - cta_k0) * wk / p.WK;
+  const int rw1 = cta_k0 + (cta_k1 - cta_k0) * (wk + 1) / p.WK;
+  const int g0 = rw0 >> 3, g1 = (rw1 + 7) >> 3;   // quantisation groups touched (8 packed rows each)
+  const int w0 = active ? rw0 : 0, w1 = active ? rw1 : 0;   // empty range for warps past the last block
+  const bool has_work = w0 < w1;
+
+  // ---- shared memory carve-up: [rings: 8 warps x R slots x 4 KB][staged activations] ----
+  uint8_t* ring = smem_raw + (size_t)warp * p.R * kSlotBytes;
+  const uint32_t ring_addr = smem_addr(ring) + lane * 16;
+  const uint32_t bar0 = smem_addr(&s_bars[warp * 4]);
+  __half* xs_all = reinterpret_cast<__half*>(smem_raw + (size_t)kGemvWarps * p.R * kSlotBytes);
+  __half* xs = xs_all + (size_t)wk * p.xs_rows * p.xs_stride;
 
   const uint64_t pol = make_evict_first_policy();
-  const int64_t row_u4 = p.N >> 1;                          // uint4 per packed row
-  const uint4* wptr = p.B + (int64_t)blk * 32 + lane;       // + kt * row_u4
-  const uint4* sptr = p.S + (int64_t)blk * 8 + g;           // + grp * (N/8)
-  const int64_t srow_u4 = p.N >> 3;
+  const size_t row_bytes = (size_t)p.N * 8;                                   // bytes per packed row
+  const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(p.B) + (size_t)(active ? blk : 0) * 512;
+  const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
+  const uint4* sptr = p.S + (size_t)(active ? blk : 0) * 8 + g + (size_t)g0 * srow_u4;
 
-  // ---- fill the ring before anything else so HBM requests are in flight while x is staged ----
-  uint4 ring[8];
-#pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const int kt = 8 * g0 + u;
-    ring[u] = make_uint4(0, 0, 0, 0);
-    if (active && kt >= w0 && kt < w1) ring[u] = ld_stream16(wptr + (int64_t)kt * row_u4, pol);
+  // Issue the bulk copies of group gi into ring slot `slot` (one elected lane; 512 contiguous bytes per row).
+  auto issue_group = [&](int gi, int slot) {
+    if (lane == 0) {
+      const int k_lo = max(8 * gi, w0), k_hi = min(8 * gi + 8, w1);
+      if (k_hi > k_lo) {
+        const uint32_t bar = bar0 + slot * 8;
+        mbar_expect_tx(bar, (uint32_t)(k_hi - k_lo) * 512u);
+        const uint32_t dst = smem_addr(ring) + slot * kSlotBytes;
+        for (int kt = k_lo; kt < k_hi; ++kt)
+          bulk_g2s(dst + (kt - 8 * gi) * 512, wsrc + (size_t)kt * row_bytes, 512u, bar, pol);
+      }
+    }
+  };
+
+  if (lane == 0) {
+    for (int s = 0; s < p.R; ++s) mbar_init(bar0 + s * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  __syncwarp();
+  // ---- start streaming weights before anything else ----
+  if (has_work)
+    for (int s = 0; s < p.R; ++s)
+      if (g0 + s < g1) issue_group(g0 + s, s);
   uint4 s_cur = make_uint4(0, 0, 0, 0);
-  if (active && g0 < g1) s_cur = ld_nc16(sptr + (int64_t)g0 * srow_u4);
+  if (has_work) s_cur = ld_nc16(sptr);
 
-  if (p.pdl) pdl_wait();   // activations may come from the preceding kernel
+  // Let the next kernel in the stream start its own weight prefetch, then wait for the producer of A.
+  pdl_launch_dependents();
+  pdl_wait();
 
-  __half* xs = reinterpret_cast<__half*>(smem_raw) + (size_t)wk * (8 * MT) * p.xs_stride;
   const int row_threads = p.WN * 32;
   const int row_tid = wn * 32 + lane;
+  const int m_staged = p.xs_rows - 1;                 // real rows staged by this kernel (M, at most 8*MT)
+  // the extra row is read by MMA lanes whose batch row does not exist: clear it once
+  for (int v = row_tid; v < p.xs_stride / 8; v += row_threads)
+    *reinterpret_cast<uint4*>(xs + (size_t)m_staged * p.xs_stride + v * 8) = make_uint4(0, 0, 0, 0);
+  // this lane's B-fragment origin for batch tile 0 and the distance to tile 1
+  const int row_t0 = min(g, m_staged), row_t1 = min(8 + g, m_staged);
+  const __half* xl = xs + (size_t)row_t0 * p.xs_stride + 2 * c;
+  const int xs_tile_stride = (row_t1 - row_t0) * p.xs_stride;
 
   float acc[MT][4][4];
 #pragma unroll
@@ -98,80 +210,69 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
 #pragma unroll
       for (int r = 0; r < 4; ++r) acc[t][j][r] = 0.f;
 
+  int chunk_pos = 0;   // group index inside the staged chunk
+  int slot = 0;
+  uint32_t parity = 0;
+  bool timed_out = false;
   for (int gi = g0; gi < g1; ++gi) {
     // ---- stage the next chunk of activations for this warp row (GCH groups = GCH*128 k-values) ----
-    if ((gi - g0) % p.GCH == 0) {
+    if (chunk_pos == 0) {
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
-      const int gend = min(gi + p.GCH, g1);
-      const int vec_per_row = (gend - gi) * 16;               // 16-byte vectors per row
-      const int total = 8 * MT * vec_per_row;
-      for (int v = row_tid; v < total; v += row_threads) {
-        const int r = v / vec_per_row, col = v - r * vec_per_row;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (r < p.M) val = ld_nc16(p.A + (int64_t)r * p.lda + (int64_t)gi * 128 + col * 8);
-        *reinterpret_cast<uint4*>(xs + (size_t)r * p.xs_stride + col * 8) = val;
-      }
+      const int vec_per_row = (min(gi + p.GCH, g1) - gi) * 16;   // 16-byte vectors per row
+      const __half* src = p.A + (size_t)gi * 128;
+      for (int r = 0; r < m_staged; ++r)
+        for (int v = row_tid; v < vec_per_row; v += row_threads)
+          *reinterpret_cast<uint4*>(xs + (size_t)r * p.xs_stride + v * 8) = ld_nc16(src + (size_t)r * p.lda + v * 8);
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
     }
-    uint4 s_next = make_uint4(0, 0, 0, 0);
-    if (active && gi + 1 < g1) s_next = ld_nc16(sptr + (int64_t)(gi + 1) * srow_u4);
+    if (has_work) {
+      uint4 s_next = make_uint4(0, 0, 0, 0);
+      if (gi + 1 < g1) s_next = ld_nc16(sptr + (size_t)(gi + 1 - g0) * srow_u4);
 
-    float accg[MT][4][4];
+      float accg[MT][4][4], corr[MT][4];
 #pragma unroll
-    for (int t = 0; t < MT; ++t)
+      for (int t = 0; t < MT; ++t) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+        for (int r = 0; r < 4; ++r) corr[t][r] = 0.f;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) accg[t][j][r] = 0.f;
-
-    const __half* xg = xs + (size_t)((gi - g0) % p.GCH) * 128;
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int kt = 8 * gi + u;
-      const uint4 cur = ring[u];
-      if (active && kt + 8 < w1) ring[u] = ld_stream16(wptr + (int64_t)(kt + 8) * row_u4, pol);
-      if (active && kt >= w0 && kt < w1) {
-        uint32_t b0[MT], b1[MT];
-#pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          const __half* xr = xg + (size_t)(8 * t + g) * p.xs_stride + u * 16 + 2 * c;
-          b0[t] = *reinterpret_cast<const uint32_t*>(xr);
-          b1[t] = *reinterpret_cast<const uint32_t*>(xr + 8);
-        }
-        const uint32_t wq[4] = {cur.x, cur.y, cur.z, cur.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t a[4];
-          const uint32_t q = wq[j], qs = wq[j] >> 8;
-          a[0] = nib_pair_to_half2_m8(q);        // n = 16j+g,   k = 2c, 2c+1
-          a[2] = nib_pair_hi_to_half2_m8(q);     // n = 16j+g,   k = 2c+8, 2c+9
-          a[1] = nib_pair_to_half2_m8(qs);       // n = 16j+g+8, k = 2c, 2c+1
-          a[3] = nib_pair_hi_to_half2_m8(qs);    // n = 16j+g+8, k = 2c+8, 2c+9
-#pragma unroll
-          for (int t = 0; t < MT; ++t) mma_m16n8k16(accg[t][j], a, b0[t], b1[t]);
-        }
+          for (int r = 0; r < 4; ++r) accg[t][j][r] = 0.f;
       }
-    }
-    // ---- apply this group's scales: lane holds s[64blk + 8g + 2j + b] for j=0..3, b=0..1 ----
-    {
+
+      if (!mbar_wait(bar0 + slot * 8, parity)) timed_out = true;
+      const uint32_t slot_addr = ring_addr + slot * kSlotBytes;
+      const __half* xg = xl + chunk_pos * 128;
+      if (8 * gi >= w0 && 8 * gi + 8 <= w1)
+        gemv_group<MT, false>(slot_addr, accg, corr, xg, xs_tile_stride, 8 * gi, w0, w1);
+      else
+        gemv_group<MT, true>(slot_addr, accg, corr, xg, xs_tile_stride, 8 * gi, w0, w1);
+      // the slot has been read by every lane: hand it back to the copy engine
+      __syncwarp();
+      if (gi + p.R < g1) issue_group(gi + p.R, slot);
+
+      // ---- apply this group's scales: lane holds s[64blk + 8g + 2j + b] for j=0..3, b=0..1 ----
       const __half2* sh = reinterpret_cast<const __half2*>(&s_cur);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 sf = __half22float2(sh[j]);   // .x -> columns 16j+g, .y -> 16j+g+8
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
-          acc[t][j][0] = fmaf(accg[t][j][0], sf.x, acc[t][j][0]);
-          acc[t][j][1] = fmaf(accg[t][j][1], sf.x, acc[t][j][1]);
-          acc[t][j][2] = fmaf(accg[t][j][2], sf.y, acc[t][j][2]);
-          acc[t][j][3] = fmaf(accg[t][j][3], sf.y, acc[t][j][3]);
+          acc[t][j][0] = fmaf(accg[t][j][0] - corr[t][0], sf.x, acc[t][j][0]);
+          acc[t][j][1] = fmaf(accg[t][j][1] - corr[t][1], sf.x, acc[t][j][1]);
+          acc[t][j][2] = fmaf(accg[t][j][2] - corr[t][2], sf.y, acc[t][j][2]);
+          acc[t][j][3] = fmaf(accg[t][j][3] - corr[t][3], sf.y, acc[t][j][3]);
         }
       }
+      s_cur = s_next;
     }
-    s_cur = s_next;
+    if (++chunk_pos == p.GCH) chunk_pos = 0;
+    if (++slot == p.R) { slot = 0; parity ^= 1; }
   }
+  if (timed_out && lane == 0 && p.status_word) atomicOr(p.status_word, UNIQL_STATUS_WAIT_TIMEOUT);
 
   // ---- reduce the WK warp rows through shared memory (fixed order) ----
-  __syncthreads();   // everyone is done with the staged activations; reuse the space
+  __syncthreads();   // every copy issued has been consumed; rings and staged activations can be reused
   float* red = reinterpret_cast<float*>(smem_raw);
   {
     float* mine = red + (size_t)warp * (8 * MT) * kRedStride;
@@ -188,29 +289,56 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
   }
   __syncthreads();
 
-  const int cta_cols = p.WN * 64;
-  const int n_base = blockIdx.x * cta_cols;
-  const int total = p.M * cta_cols;
+  // Each work item is 4 adjacent columns of one batch row.
+  const int log_cols4 = p.log_wn + 4;                 // log2(WN*64/4)
+  const int n_base = blockIdx.x * (p.WN * 64);
+  const int items = p.M << log_cols4;
   const bool direct = (p.S_split == 1);
-  for (int idx = tid; idx < total; idx += kGemvThreads) {
-    const int m = idx / cta_cols, col = idx - m * cta_cols;
+  const bool vec_store = ((p.ldd & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 7u) == 0);
+
+  auto store_out = [&](int m, int n, float4 v) {
+    if (n >= p.n_out) return;
+    if (p.bias) {
+      if (n + 3 < p.n_out) {
+        v.x += __half2float(p.bias[n]); v.y += __half2float(p.bias[n + 1]);
+        v.z += __half2float(p.bias[n + 2]); v.w += __half2float(p.bias[n + 3]);
+      } else {
+        v.x += __half2float(p.bias[n]);
+        if (n + 1 < p.n_out) v.y += __half2float(p.bias[n + 1]);
+        if (n + 2 < p.n_out) v.z += __half2float(p.bias[n + 2]);
+      }
+    }
+    __half* d = p.D + (size_t)m * p.ldd + n;
+    if (vec_store && n + 3 < p.n_out) {
+      __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(d) = pk;
+    } else {
+      d[0] = __float2half_rn(v.x);
+      if (n + 1 < p.n_out) d[1] = __float2half_rn(v.y);
+      if (n + 2 < p.n_out) d[2] = __float2half_rn(v.z);
+      if (n + 3 < p.n_out) d[3] = __float2half_rn(v.w);
+    }
+  };
+
+  for (int idx = tid; idx < items; idx += kGemvThreads) {
+    const int m = idx >> log_cols4, col = (idx & ((1 << log_cols4) - 1)) * 4;
     const int n = n_base + col;
     if (n >= p.N) continue;
     const int wn_i = col >> 6, nl = col & 63;
-    float v = 0.f;
-    for (int k = 0; k < p.WK; ++k) v += red[((size_t)(k * p.WN + wn_i) * (8 * MT) + m) * kRedStride + nl];
-    if (direct) {
-      if (n < p.n_out) {
-        if (p.bias) v += __half2float(p.bias[n]);
-        p.D[(int64_t)m * p.ldd + n] = __float2half_rn(v);
-      }
-    } else {
-      p.partials[((size_t)blockIdx.y * p.M + m) * p.N + n] = v;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < p.WK; ++k) {
+      const float4 t4 = *reinterpret_cast<const float4*>(red + ((size_t)((k << p.log_wn) + wn_i) * (8 * MT) + m) * kRedStride + nl);
+      v.x += t4.x; v.y += t4.y; v.z += t4.z; v.w += t4.w;
     }
+    if (direct) store_out(m, n, v);
+    else *reinterpret_cast<float4*>(p.partials + ((size_t)blockIdx.y * p.M + m) * p.N + n) = v;
   }
   if (direct) return;
 
-  // ---- split-k: the last CTA of this column group to finish adds the partials ----
+  // ---- split-k: the last CTA of this column group to finish adds the partials (fixed order) ----
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -222,14 +350,22 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
   __syncthreads();
   if (!s_is_last) return;
   __threadfence();
-  for (int idx = tid; idx < total; idx += kGemvThreads) {
-    const int m = idx / cta_cols, col = idx - m * cta_cols;
+  const size_t slab4 = ((size_t)p.M * p.N) >> 2;
+  for (int idx = tid; idx < items; idx += kGemvThreads) {
+    const int m = idx >> log_cols4, col = (idx & ((1 << log_cols4) - 1)) * 4;
     const int n = n_base + col;
     if (n >= p.n_out) continue;
-    float v = 0.f;
-    for (int s = 0; s < p.S_split; ++s) v += __ldcg(p.partials + ((size_t)s * p.M + m) * p.N + n);
-    if (p.bias) v += __half2float(p.bias[n]);
-    p.D[(int64_t)m * p.ldd + n] = __float2half_rn(v);
+    const float4* src = reinterpret_cast<const float4*>(p.partials + (size_t)m * p.N + n);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < p.S_split; s += 8) {      // up to 8 independent L2 loads in flight, summed in order
+      float4 t4[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        t4[i] = (s + i < p.S_split) ? __ldcg(src + (size_t)(s + i) * slab4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { v.x += t4[i].x; v.y += t4[i].y; v.z += t4[i].z; v.w += t4[i].w; }
+    }
+    store_out(m, n, v);
   }
 }
 
@@ -267,15 +403,27 @@ GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k) {
   if (ov_s >= 1) best.S = ov_s;
   if (best.S > KT) best.S = KT;
   const int MT = m <= 8 ? 1 : 2;
-  // activation staging: WK warp rows x 8*MT batch rows x (GCH*128 + 8) halves, kept under ~40 KB
-  int gch = (int)((40960 / (best.WK * 8 * MT * 2) - 8) / 128);
+  // Shared memory per CTA (two CTAs per SM): rings = 8 warps x R slots x 4 KB, then the staged activations
+  // = WK warp rows x (rows + 1) x (GCH*128 + 8) halves.  Keep the total near 110 KB.
+  const int rows = (int)(m < 8 * MT ? m : 8 * MT) + 1;
+  const size_t budget = 110 * 1024;
+  const size_t xs_min = (size_t)best.WK * rows * (128 + 8) * 2;
+  int R = (int)((budget - xs_min) / (kGemvWarps * kSlotBytes));
+  if (R > 3) R = 3;
+  if (R < 1) R = 1;
+  const int ov_r = env_int("UNIQL_B200_GEMV_R", 0);
+  if (ov_r >= 1 && ov_r <= 4) R = ov_r;
+  const size_t ring_bytes = (size_t)kGemvWarps * R * kSlotBytes;
+  int gch = (int)(((budget > ring_bytes ? budget - ring_bytes : 0) / ((size_t)best.WK * rows * 2) - 8) / 128);
   if (gch < 1) gch = 1;
   if (gch > 8) gch = 8;
   best.GCH = gch;
   best.MT = MT;
-  const size_t xs_bytes = (size_t)best.WK * 8 * MT * (gch * 128 + 8) * 2;
+  best.R = R;
+  best.xs_rows = rows;
+  const size_t xs_bytes = (size_t)best.WK * rows * (gch * 128 + 8) * 2;
   const size_t red_bytes = (size_t)kGemvWarps * 8 * MT * kRedStride * 4;
-  best.smem = xs_bytes > red_bytes ? xs_bytes : red_bytes;
+  best.smem = ring_bytes + xs_bytes > red_bytes ? ring_bytes + xs_bytes : red_bytes;
   best.partial_bytes = best.S > 1 ? (size_t)best.S * (size_t)(m < 16 ? m : 16) * n * 4 : 0;
   return best;
 }
@@ -290,18 +438,19 @@ int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, in
   p.D = D; p.ldd = a.ldd;
   p.M = (int)m; p.N = (int)a.n; p.n_out = (int)a.n_out; p.KT = (int)(a.k / 16); p.nblk = (int)(a.n / 64);
   p.WN = plan.WN; p.WK = plan.WK; p.S_split = plan.S; p.GCH = plan.GCH;
+  p.log_wn = plan.WN == 1 ? 0 : plan.WN == 2 ? 1 : plan.WN == 4 ? 2 : 3;
   p.xs_stride = plan.GCH * 128 + 8;
+  p.R = plan.R; p.xs_rows = plan.xs_rows; p.status_word = a.status_word;
   p.counters = a.counters;
   p.partials = a.partials;
   if (plan.partial_bytes > a.partial_bytes) return UNIQL_ESCRATCH;
   if ((size_t)grid_x_of(p) * sizeof(int) > UNIQL_SCRATCH_COUNTER_BYTES) return UNIQL_ESHAPE;
-  p.pdl = pdl ? 1 : 0;
   dim3 grid(grid_x_of(p), p.S_split);
 
   auto kern = plan.MT == 1 ? w4a16_gemv_kernel<1> : w4a16_gemv_kernel<2>;
   static thread_local bool attr_set[2] = {false, false};
   if (plan.smem > 48 * 1024 && !attr_set[plan.MT - 1]) {
-    UNIQL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    UNIQL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     attr_set[plan.MT - 1] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -313,7 +462,8 @@ int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, in
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  (void)pdl;
+  cfg.numAttrs = 1;   // always: the kernel waits on its producer itself (griddepcontrol.wait)
   UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
   return UNIQL_OK;
 }
