@@ -35,7 +35,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: cannot build libuniql_b200.so")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH + ".tmp", *sources(), "-lcudart", "-lcuda"]
+    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH + ".tmp", *sources(), "-lcudart"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     res = subprocess.run(cmd, capture_output=True, text=True)

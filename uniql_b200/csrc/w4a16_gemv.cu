@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "linear_internal.cuh"
 
+#include <cuda.h>
 #include <stdlib.h>
 
 namespace uniql {
@@ -33,25 +34,29 @@ constexpr int kGemvWarps = 8;
 constexpr int kRedStride = 68;  // floats per row of a warp's 64-column reduction tile (+4: conflict-free scatter)
 
 constexpr int kSlotBytes = 4096;   // one quantisation group (8 packed rows) of one 64-column block
+#ifndef UNIQL_GEMV_CTAS_MT1
+#define UNIQL_GEMV_CTAS_MT1 2
+#endif
+constexpr int kCtasMt1 = UNIQL_GEMV_CTAS_MT1;   // resident CTAs per SM for the m <= 8 variant
+constexpr int kXsPad = 16;         // halves of padding per staged activation row (keeps LDS.64 conflict-free)
 
 struct GemvParams {
   const __half* A;
   int64_t lda;
-  const uint4* B;       // packed weights, row kt has n/2 uint4
   const uint4* S;       // permuted scales, row g has n/8 uint4
   const __half* bias;
   __half* D;
   int64_t ldd;
   int M, N, n_out, KT, nblk;
   int WN, WK, log_wn, S_split, GCH, R;
-  int xs_stride;        // halves per staged activation row (GCH*128 + 8)
+  int xs_stride;        // halves per staged activation row (GCH*128 + kXsPad)
   int xs_rows;          // staged rows per warp row: min(M, 8*MT) + 1 (the extra row stays zero)
   float* partials;      // [S_split][M][N]
   int* counters;        // [gridDim.x], zero on entry, zero on exit
   int* status_word;
 };
 
-// ---- mbarrier / bulk-copy (TMA engine, untiled) helpers -------------------------------------------
+// ---- mbarrier / TMA helpers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -75,10 +80,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+// One 2-D tile (128 words x 8 packed rows = one ring slot) from the packed weight matrix; no multicast.
+__device__ __forceinline__ void tma_load_slot(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar,
+                                              uint64_t pol) {
   asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol)
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(pol)
       : "memory");
 }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -86,29 +94,30 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
 
 // One quantisation group (8 packed rows) of one 64-column block, read from this warp's ring slot.
 // Nibbles are turned into fp16 values (1024 + q) and (64 + q) by a single LOP3 each; the offsets are taken
 // out again through `corr`, an extra MMA whose 16-row operand is the constant (1032 | 72):
 //   sum_k (off_k + q) x  -  sum_k (off_k + 8) x  =  sum_k (q - 8) x.
+// Activations are staged so that a lane's (b0, b1) fragment of packed row u is 8 contiguous bytes at xaddr + 32u.
 template <int MT, bool CHECK>
-__device__ __forceinline__ void gemv_group(uint32_t slot_addr, float (&accg)[MT][4][4], float (&corr)[MT][4],
-                                           const __half* xl, int xs_tile_stride, int kt_base, int w0, int w1) {
+__device__ __forceinline__ void gemv_group(const uint8_t* slot_ptr, float (&accg)[MT][4][4], float (&corr)[MT][4],
+                                           const uint8_t* xptr, uint32_t x_tile_stride, int kt_base, int w0, int w1) {
   const uint32_t kcorr[4] = {0x64086408u, 0x64086408u, 0x54805480u, 0x54805480u};   // 1032, 1032, 72, 72
 #pragma unroll
   for (int u = 0; u < 8; ++u) {
-    const int kt = kt_base + u;
-    if (!CHECK || (kt >= w0 && kt < w1)) {
-      const uint4 w4 = lds128(slot_addr + u * 512);
-      uint32_t b0[MT], b1[MT];
+    if (!CHECK || (kt_base + u >= w0 && kt_base + u < w1)) {
+      const uint4 w4 = *reinterpret_cast<const uint4*>(slot_ptr + u * 512);
+      uint2 b[MT];
 #pragma unroll
-      for (int t = 0; t < MT; ++t) {
-        const __half* xr = xl + (size_t)t * xs_tile_stride + u * 16;
-        b0[t] = *reinterpret_cast<const uint32_t*>(xr);
-        b1[t] = *reinterpret_cast<const uint32_t*>(xr + 8);
-      }
+      for (int t = 0; t < MT; ++t) b[t] = *reinterpret_cast<const uint2*>(xptr + t * x_tile_stride + u * 32);
 #pragma unroll
-      for (int t = 0; t < MT; ++t) mma_m16n8k16(corr[t], kcorr, b0[t], b1[t]);
+      for (int t = 0; t < MT; ++t) mma_m16n8k16(corr[t], kcorr, b[t].x, b[t].y);
       const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -119,14 +128,15 @@ __device__ __forceinline__ void gemv_group(uint32_t slot_addr, float (&accg)[MT]
         a[1] = lop3_and_or(qs, 0x000f000fu, 0x64006400u);    // n = 16j+g+8, k = 2c, 2c+1
         a[3] = lop3_and_or(qs, 0x00f000f0u, 0x54005400u);    // n = 16j+g+8, k = 2c+8, 2c+9
 #pragma unroll
-        for (int t = 0; t < MT; ++t) mma_m16n8k16(accg[t][j], a, b0[t], b1[t]);
+        for (int t = 0; t < MT; ++t) mma_m16n8k16(accg[t][j], a, b[t].x, b[t].y);
       }
     }
   }
 }
 
 template <int MT>
-__global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvThreads, MT == 1 ? kCtasMt1 : 2)
+w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ int s_is_last;
   __shared__ __align__(8) uint64_t s_bars[kGemvWarps * 4];
@@ -148,31 +158,14 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
   const bool has_work = w0 < w1;
 
   // ---- shared memory carve-up: [rings: 8 warps x R slots x 4 KB][staged activations] ----
-  uint8_t* ring = smem_raw + (size_t)warp * p.R * kSlotBytes;
-  const uint32_t ring_addr = smem_addr(ring) + lane * 16;
+  const uint32_t ring_base = smem_addr(smem_raw) + warp * p.R * kSlotBytes;
   const uint32_t bar0 = smem_addr(&s_bars[warp * 4]);
   __half* xs_all = reinterpret_cast<__half*>(smem_raw + (size_t)kGemvWarps * p.R * kSlotBytes);
   __half* xs = xs_all + (size_t)wk * p.xs_rows * p.xs_stride;
 
   const uint64_t pol = make_evict_first_policy();
-  const size_t row_bytes = (size_t)p.N * 8;                                   // bytes per packed row
-  const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(p.B) + (size_t)(active ? blk : 0) * 512;
   const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
   const uint4* sptr = p.S + (size_t)(active ? blk : 0) * 8 + g + (size_t)g0 * srow_u4;
-
-  // Issue the bulk copies of group gi into ring slot `slot` (one elected lane; 512 contiguous bytes per row).
-  auto issue_group = [&](int gi, int slot) {
-    if (lane == 0) {
-      const int k_lo = max(8 * gi, w0), k_hi = min(8 * gi + 8, w1);
-      if (k_hi > k_lo) {
-        const uint32_t bar = bar0 + slot * 8;
-        mbar_expect_tx(bar, (uint32_t)(k_hi - k_lo) * 512u);
-        const uint32_t dst = smem_addr(ring) + slot * kSlotBytes;
-        for (int kt = k_lo; kt < k_hi; ++kt)
-          bulk_g2s(dst + (kt - 8 * gi) * 512, wsrc + (size_t)kt * row_bytes, 512u, bar, pol);
-      }
-    }
-  };
 
   if (lane == 0) {
     for (int s = 0; s < p.R; ++s) mbar_init(bar0 + s * 8, 1);
@@ -180,13 +173,14 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncwarp();
-  // ---- start streaming weights before anything else ----
-  if (has_work)
+  // ---- start streaming weights before anything else: one TMA tile per group and 64-column block ----
+  if (has_work && lane == 0) {
     for (int s = 0; s < p.R; ++s)
-      if (g0 + s < g1) issue_group(g0 + s, s);
-  uint4 s_cur = make_uint4(0, 0, 0, 0);
-  if (has_work) s_cur = ld_nc16(sptr);
-
+      if (g0 + s < g1) {
+        mbar_expect_tx(bar0 + s * 8, kSlotBytes);
+        tma_load_slot(ring_base + s * kSlotBytes, &wmap, blk * 128, 8 * (g0 + s), bar0 + s * 8, pol);
+      }
+  }
   // Let the next kernel in the stream start its own weight prefetch, then wait for the producer of A.
   pdl_launch_dependents();
   pdl_wait();
@@ -197,10 +191,10 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
   // the extra row is read by MMA lanes whose batch row does not exist: clear it once
   for (int v = row_tid; v < p.xs_stride / 8; v += row_threads)
     *reinterpret_cast<uint4*>(xs + (size_t)m_staged * p.xs_stride + v * 8) = make_uint4(0, 0, 0, 0);
-  // this lane's B-fragment origin for batch tile 0 and the distance to tile 1
+  // this lane's B-fragment origin for batch tile 0 and the distance to tile 1 (bytes)
   const int row_t0 = min(g, m_staged), row_t1 = min(8 + g, m_staged);
-  const __half* xl = xs + (size_t)row_t0 * p.xs_stride + 2 * c;
-  const int xs_tile_stride = (row_t1 - row_t0) * p.xs_stride;
+  const uint8_t* xl = reinterpret_cast<const uint8_t*>(xs) + (size_t)row_t0 * p.xs_stride * 2 + c * 8;
+  const uint32_t x_tile_stride = (uint32_t)(row_t1 - row_t0) * p.xs_stride * 2;
 
   float acc[MT][4][4];
 #pragma unroll
@@ -216,18 +210,36 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
   bool timed_out = false;
   for (int gi = g0; gi < g1; ++gi) {
     // ---- stage the next chunk of activations for this warp row (GCH groups = GCH*128 k-values) ----
+    // Layout per row: packed row u occupies 32 bytes holding, for c = 0..3, the halves (2c, 2c+1, 2c+8, 2c+9).
     if (chunk_pos == 0) {
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
-      const int vec_per_row = (min(gi + p.GCH, g1) - gi) * 16;   // 16-byte vectors per row
+      const int blocks_per_row = (min(gi + p.GCH, g1) - gi) * 8;   // 16-value blocks per row
       const __half* src = p.A + (size_t)gi * 128;
-      for (int r = 0; r < m_staged; ++r)
-        for (int v = row_tid; v < vec_per_row; v += row_threads)
-          *reinterpret_cast<uint4*>(xs + (size_t)r * p.xs_stride + v * 8) = ld_nc16(src + (size_t)r * p.lda + v * 8);
+      for (int v = row_tid; v < blocks_per_row; v += row_threads) {
+        constexpr int RB = MT == 1 ? 2 : 4;   // rows loaded together (independent requests in flight)
+        for (int r0 = 0; r0 < m_staged; r0 += RB) {
+          uint4 lo[RB], hi[RB];
+#pragma unroll
+          for (int i = 0; i < RB; ++i)
+            if (r0 + i < m_staged) {
+              const __half* s16 = src + (size_t)(r0 + i) * p.lda + v * 16;
+              lo[i] = ld_nc16(s16);
+              hi[i] = ld_nc16(s16 + 8);
+            }
+#pragma unroll
+          for (int i = 0; i < RB; ++i)
+            if (r0 + i < m_staged) {
+              uint4* d = reinterpret_cast<uint4*>(xs + (size_t)(r0 + i) * p.xs_stride + v * 16);
+              d[0] = make_uint4(lo[i].x, hi[i].x, lo[i].y, hi[i].y);
+              d[1] = make_uint4(lo[i].z, hi[i].z, lo[i].w, hi[i].w);
+            }
+        }
+      }
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
     }
     if (has_work) {
-      uint4 s_next = make_uint4(0, 0, 0, 0);
-      if (gi + 1 < g1) s_next = ld_nc16(sptr + (size_t)(gi + 1 - g0) * srow_u4);
+      // this group's 8 scales; the load is covered by the group's MMAs
+      const uint4 s_cur = ld_nc16(sptr + (size_t)(gi - g0) * srow_u4);
 
       float accg[MT][4][4], corr[MT][4];
 #pragma unroll
@@ -241,15 +253,18 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
       }
 
       if (!mbar_wait(bar0 + slot * 8, parity)) timed_out = true;
-      const uint32_t slot_addr = ring_addr + slot * kSlotBytes;
-      const __half* xg = xl + chunk_pos * 128;
+      const uint8_t* slot_addr = smem_raw + (size_t)(warp * p.R + slot) * kSlotBytes + lane * 16;
+      const uint8_t* xg = xl + chunk_pos * 256;
       if (8 * gi >= w0 && 8 * gi + 8 <= w1)
-        gemv_group<MT, false>(slot_addr, accg, corr, xg, xs_tile_stride, 8 * gi, w0, w1);
+        gemv_group<MT, false>(slot_addr, accg, corr, xg, x_tile_stride, 8 * gi, w0, w1);
       else
-        gemv_group<MT, true>(slot_addr, accg, corr, xg, xs_tile_stride, 8 * gi, w0, w1);
+        gemv_group<MT, true>(slot_addr, accg, corr, xg, x_tile_stride, 8 * gi, w0, w1);
       // the slot has been read by every lane: hand it back to the copy engine
       __syncwarp();
-      if (gi + p.R < g1) issue_group(gi + p.R, slot);
+      if (lane == 0 && gi + p.R < g1) {
+        mbar_expect_tx(bar0 + slot * 8, kSlotBytes);
+        tma_load_slot(ring_base + slot * kSlotBytes, &wmap, blk * 128, 8 * (gi + p.R), bar0 + slot * 8, pol);
+      }
 
       // ---- apply this group's scales: lane holds s[64blk + 8g + 2j + b] for j=0..3, b=0..1 ----
       const __half2* sh = reinterpret_cast<const __half2*>(&s_cur);
@@ -264,7 +279,6 @@ __global__ void __launch_bounds__(kGemvThreads, 2) w4a16_gemv_kernel(const GemvP
           acc[t][j][3] = fmaf(accg[t][j][3] - corr[t][3], sf.y, acc[t][j][3]);
         }
       }
-      s_cur = s_next;
     }
     if (++chunk_pos == p.GCH) chunk_pos = 0;
     if (++slot == p.R) { slot = 0; parity ^= 1; }
@@ -375,10 +389,47 @@ static int env_int(const char* name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library does not link libcuda
+// (it must load on hosts without a driver for the symbol/argument checks).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// Packed weights as a 2-D uint32 tensor [KT rows][2N words]; one box = 128 words x 8 rows = one ring slot.
+static int make_weight_map(CUtensorMap* map, const void* B, int64_t n, int64_t kt) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return cuda_fail(cudaErrorNotSupported);
+  cuuint64_t dims[2] = {(cuuint64_t)(2 * n), (cuuint64_t)kt};
+  cuuint64_t strides[1] = {(cuuint64_t)(2 * n) * 4};
+  cuuint32_t box[2] = {128, 8};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(B), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  return UNIQL_OK;
+}
+
 GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k) {
   GemvPlan best{};
-  const int nblk = (int)(n / 64), KT = (int)(k / 16);
-  const int slots = device_info().sm_count * 2;
+  const int MT = m <= 8 ? 1 : 2;
+  const int nblk = (int)(n / 64), KT = (int)(k / 16), NG = KT / 8;
+  const int ctas_per_sm = MT == 1 ? kCtasMt1 : 2;
+  const int slots = device_info().sm_count * env_int("UNIQL_B200_GEMV_SLOTS", ctas_per_sm);
   double best_cost = 1e30;
   for (int WN = 8; WN >= 1; WN >>= 1) {
     const int WK = kGemvWarps / WN;
@@ -388,10 +439,14 @@ GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k) {
     for (int S = 1; S <= smax; ++S) {
       const int64_t ctas = (int64_t)groups * S;
       const int64_t waves = (ctas + slots - 1) / slots;
-      const int per_cta = (KT + S - 1) / S;
-      const int len = (per_cta + WK - 1) / WK;           // packed rows streamed by one warp
+      const int splits = S * WK;
+      // packed rows streamed by the busiest warp; a k-range that is not a whole number of quantisation
+      // groups pays for the partly used first/last group through the slower predicated path
+      const int len = (KT + splits - 1) / splits;
+      const bool aligned = (NG % splits) == 0;
+      const double eff_len = aligned ? len : len + 6.0;
       // cost in "packed rows per warp": streamed rows + fixed latency per wave + split-k reduction
-      double cost = (double)waves * (len + 10.0) * waste + (S > 1 ? 3.0 + 0.35 * S : 0.0);
+      double cost = (double)waves * (eff_len + 12.0) * waste + (S > 1 ? 6.0 + 0.35 * S : 0.0);
       if (cost < best_cost - 1e-9) {
         best_cost = cost;
         best.WN = WN; best.WK = WK; best.S = S;
@@ -402,26 +457,27 @@ GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k) {
   if (ov_wn == 1 || ov_wn == 2 || ov_wn == 4 || ov_wn == 8) { best.WN = ov_wn; best.WK = kGemvWarps / ov_wn; }
   if (ov_s >= 1) best.S = ov_s;
   if (best.S > KT) best.S = KT;
-  const int MT = m <= 8 ? 1 : 2;
-  // Shared memory per CTA (two CTAs per SM): rings = 8 warps x R slots x 4 KB, then the staged activations
-  // = WK warp rows x (rows + 1) x (GCH*128 + 8) halves.  Keep the total near 110 KB.
+  // Shared memory per CTA: rings = 8 warps x R slots x 4 KB, then the staged activations
+  // = WK warp rows x (rows + 1) x (GCH*128 + pad) halves.  Budget: 3 CTAs per SM for m <= 8, else 2.
   const int rows = (int)(m < 8 * MT ? m : 8 * MT) + 1;
-  const size_t budget = 110 * 1024;
-  const size_t xs_min = (size_t)best.WK * rows * (128 + 8) * 2;
+  const size_t budget = (MT == 1 && kCtasMt1 == 3 ? 74 : 110) * 1024;
+  const size_t xs_min = (size_t)best.WK * rows * (128 + kXsPad) * 2;
   int R = (int)((budget - xs_min) / (kGemvWarps * kSlotBytes));
   if (R > 3) R = 3;
   if (R < 1) R = 1;
   const int ov_r = env_int("UNIQL_B200_GEMV_R", 0);
   if (ov_r >= 1 && ov_r <= 4) R = ov_r;
   const size_t ring_bytes = (size_t)kGemvWarps * R * kSlotBytes;
-  int gch = (int)(((budget > ring_bytes ? budget - ring_bytes : 0) / ((size_t)best.WK * rows * 2) - 8) / 128);
+  const size_t left = budget > ring_bytes ? budget - ring_bytes : 0;
+  int gch = (int)(left / ((size_t)best.WK * rows * 2)) - kXsPad;
+  gch = gch > 0 ? gch / 128 : 0;
   if (gch < 1) gch = 1;
   if (gch > 8) gch = 8;
   best.GCH = gch;
   best.MT = MT;
   best.R = R;
   best.xs_rows = rows;
-  const size_t xs_bytes = (size_t)best.WK * rows * (gch * 128 + 8) * 2;
+  const size_t xs_bytes = (size_t)best.WK * rows * (gch * 128 + kXsPad) * 2;
   const size_t red_bytes = (size_t)kGemvWarps * 8 * MT * kRedStride * 4;
   best.smem = ring_bytes + xs_bytes > red_bytes ? ring_bytes + xs_bytes : red_bytes;
   best.partial_bytes = best.S > 1 ? (size_t)best.S * (size_t)(m < 16 ? m : 16) * n * 4 : 0;
@@ -432,24 +488,28 @@ static inline int grid_x_of(const GemvParams& p) { return (p.nblk + p.WN - 1) / 
 
 int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m, const GemvPlan& plan,
                 bool pdl, cudaStream_t stream) {
+  (void)pdl;
   GemvParams p;
   p.A = A; p.lda = lda;
-  p.B = (const uint4*)a.B; p.S = (const uint4*)a.s; p.bias = (const __half*)a.bias;
+  p.S = (const uint4*)a.s; p.bias = (const __half*)a.bias;
   p.D = D; p.ldd = a.ldd;
   p.M = (int)m; p.N = (int)a.n; p.n_out = (int)a.n_out; p.KT = (int)(a.k / 16); p.nblk = (int)(a.n / 64);
   p.WN = plan.WN; p.WK = plan.WK; p.S_split = plan.S; p.GCH = plan.GCH;
   p.log_wn = plan.WN == 1 ? 0 : plan.WN == 2 ? 1 : plan.WN == 4 ? 2 : 3;
-  p.xs_stride = plan.GCH * 128 + 8;
+  p.xs_stride = plan.GCH * 128 + kXsPad;
   p.R = plan.R; p.xs_rows = plan.xs_rows; p.status_word = a.status_word;
   p.counters = a.counters;
   p.partials = a.partials;
   if (plan.partial_bytes > a.partial_bytes) return UNIQL_ESCRATCH;
   if ((size_t)grid_x_of(p) * sizeof(int) > UNIQL_SCRATCH_COUNTER_BYTES) return UNIQL_ESHAPE;
+  CUtensorMap wmap;
+  int st = make_weight_map(&wmap, a.B, a.n, a.k / 16);
+  if (st != UNIQL_OK) return st;
   dim3 grid(grid_x_of(p), p.S_split);
 
   auto kern = plan.MT == 1 ? w4a16_gemv_kernel<1> : w4a16_gemv_kernel<2>;
   static thread_local bool attr_set[2] = {false, false};
-  if (plan.smem > 48 * 1024 && !attr_set[plan.MT - 1]) {
+  if (!attr_set[plan.MT - 1]) {
     UNIQL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     attr_set[plan.MT - 1] = true;
   }
@@ -459,12 +519,14 @@ int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, in
   cfg.dynamicSmemBytes = plan.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
+  // Every launch may start early behind its predecessor; the kernel itself waits (griddepcontrol.wait)
+  // before it touches anything another kernel could have written.
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  (void)pdl;
-  cfg.numAttrs = 1;   // always: the kernel waits on its producer itself (griddepcontrol.wait)
-  UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+  static const int pdl_on = env_int("UNIQL_B200_PDL", 1);
+  cfg.numAttrs = pdl_on ? 1 : 0;
+  UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, wmap));
   return UNIQL_OK;
 }
 
