@@ -1,0 +1,448 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 hot path on the Llama-3.1-8B decoder projection set (synthetic weights).
+
+    python bench.py --gpus N --steps K --warmup W            # this build (CUDA kernels)
+    python bench.py --impl reference --steps K --warmup W     # CPU dequantise + matmul (the reference's math)
+
+One step = one pass over the 32-layer stack of projections (qkv 6144x4096, o 4096x4096, gate and up
+14336x4096, down 4096x14336 with a 14336-point online Hadamard on its input) at decode batch M.
+With N > 1 the linears are tensor-parallel (column-parallel qkv/gate/up, row-parallel o/down + all-reduce).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, QKV, LAYERS = 4096, 14336, 6144, 32
+SHAPES = {"qkv": (QKV, HIDDEN), "o": (HIDDEN, HIDDEN), "gate": (INTER, HIDDEN), "up": (INTER, HIDDEN),
+          "down": (HIDDEN, INTER)}
+FALLBACK_HBM_GBS = 6650.0        # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+# dram__bytes_read+write of one 14336x4096 m=1 launch, from the ncu capture summarised in
+# profiles/w4a16_gemv_14336x4096_m1.md
+NCU_TRAFFIC_GATE_M1 = 30_331_136
+
+
+def linear_bytes(n, k, m):
+    """Algorithmic bytes of one W4A16 linear: packed weights + group scales + activations in + out."""
+    return k * n // 2 + (k // 128) * n * 2 + m * k * 2 + m * n * 2
+
+
+def step_bytes(m):
+    return LAYERS * sum(linear_bytes(n, k, m) for n, k in SHAPES.values())
+
+
+def step_flops(m):
+    return LAYERS * sum(2 * m * n * k for n, k in SHAPES.values())
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured", d
+    return FALLBACK_HBM_GBS, "fallback", {}
+
+
+class ClockSampler:
+    """nvidia-smi sampler running beside the timed region (read-only queries)."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                clocks.append(float(f[1])); maxes.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [c for c in clocks if c > 0.5 * max(clocks)] or clocks
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(maxes), "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ----------------------------------------------------------------------------------------- CPU arm
+def cpu_linear_sample(m, threads, budget_s):
+    """Time the reference's CPU path (unpack + un-permute + (q-8)*s dequantise, then matmul) on a bounded
+    sample of the workload.  Returns (bytes_processed, seconds_dequant, seconds_matmul, description)."""
+    import numpy as np
+    import torch
+
+    from oracle import uniql_oracle as orc
+    torch.set_num_threads(threads)
+    rng = np.random.default_rng(0)
+    # probe with one o_proj-sized linear, then decide how much of a layer fits the budget
+    def one(n, k):
+        packed = rng.integers(-2 ** 31, 2 ** 31 - 1, size=(k // 16, 2 * n), dtype=np.int64).astype(np.int32)
+        scales = (rng.random((k // 128, n), dtype=np.float32) * 0.01 + 0.001).astype(np.float16)
+        x = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32).astype(np.float16))
+        t0 = time.perf_counter()
+        w = orc.dequantize(packed, scales)
+        t1 = time.perf_counter()
+        wt = torch.from_numpy(w)
+        y = x.float() @ wt.float()
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1, float(y[0, 0])
+
+    td, tm, _ = one(HIDDEN, HIDDEN)
+    nbytes = linear_bytes(HIDDEN, HIDDEN, m)
+    desc = "o_proj 4096x4096"
+    per_weight = (td + tm) / (HIDDEN * HIDDEN)
+    layer_weights = sum(n * k for n, k in SHAPES.values())
+    if per_weight * layer_weights < budget_s:
+        td = tm = 0.0
+        nbytes = 0
+        for name, (n, k) in SHAPES.items():
+            a, b, _ = one(n, k)
+            td += a; tm += b
+            nbytes += linear_bytes(n, k, m)
+        desc = "one decoder layer (qkv, o, gate, up, down; Hadamard not included)"
+    return nbytes, td, tm, desc
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    m = args.batch
+    total = max(1, args.steps + args.warmup)
+    budget = max(2.0, 150.0 / total)
+    times, nbytes, desc, td_last, tm_last = [], 0, "", 0.0, 0.0
+    for i in range(total):
+        nbytes, td, tm, desc = cpu_linear_sample(m, threads, budget)
+        if i >= args.warmup:
+            times.append(td + tm)
+            td_last, tm_last = td, tm
+    t = sum(times) / len(times)
+    gbs = nbytes / t / 1e9
+    line = {
+        "impl": "reference", "metric": "w4a16_linear_m1_hbm_gbs", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16xint4->f32acc",
+        "data": "synthetic",
+        "config": {"workload": "Llama-3.1-8B decoder projection set, W4A16 g128, decode batch %d" % m,
+                   "sample_per_step": desc},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc,
+                         "dequant_s": td_last, "matmul_s": tm_last},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "decode_tok_s": m / (t * step_bytes(m) / nbytes),
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------- GPU arm
+def build_stack(m, rank, world, device, layers):
+    """Synthetic RTN-quantised layers (seeded), sharded for this rank."""
+    import torch
+
+    from uniql_b200 import tp
+    from uniql_b200.quantize import quantize_helpers as qh
+    from uniql_b200.quantize.quant_linear_layers import W4A16B16O16HadLinear, W4A16B16O16Linear
+
+    def quantised(seed, n, k, cls, col=None, row=None):
+        g = torch.Generator(device=device).manual_seed(seed)
+        w = (torch.randn(n, k, generator=g, device=device) * 0.02).to(torch.float16)
+        if col is not None:
+            w = w[col[0]:col[1]]
+        if row is not None:
+            w = w[:, row[0]:row[1]]
+        _, packed, scale = qh.w4a16_quantize(w.t().contiguous(), 4, 128, None, 0)
+        lin = cls(w.shape[1], w.shape[0], device="meta")
+        lin._buffers["weight"], lin._buffers["scale"] = packed, scale
+        lin._buffers["workspace"] = torch.zeros(lin.size_n // 64 * 16, dtype=torch.int32, device=device)
+        return lin
+
+    stack = []
+    for l in range(layers):
+        mods = {}
+        for j, (name, (n, k)) in enumerate(SHAPES.items()):
+            seed = 1000 * l + j
+            if name in ("qkv", "gate", "up"):
+                mods[name] = quantised(seed, n, k, W4A16B16O16Linear, col=tp.column_bounds(n, world)[rank])
+            elif name == "o":
+                mods[name] = quantised(seed, n, k, W4A16B16O16Linear, row=tp.row_bounds(k, world)[rank])
+            else:
+                cls = W4A16B16O16HadLinear if world == 1 else W4A16B16O16Linear
+                mods[name] = quantised(seed, n, k, cls, row=tp.row_bounds(k, world)[rank])
+        stack.append(mods)
+    return stack
+
+
+def make_step(stack, world, rank, group):
+    """Returns step(x) -> y running every projection of every layer once (no attention / activation maths:
+    q-shard stands in for the attention output and the gate shard for the MLP activation)."""
+    import torch
+    import torch.distributed as dist
+
+    from uniql_b200 import ops, tp
+    o_rows = tp.row_bounds(HIDDEN, world)[rank]
+    d_rows = tp.row_bounds(INTER, world)[rank]
+    sizes = [b - a for a, b in tp.column_bounds(INTER, world)]
+    had_scale = 1.0 / (INTER ** 0.5)
+
+    def step(x):
+        for mods in stack:
+            qkv = mods["qkv"](x)
+            att = qkv[:, :o_rows[1] - o_rows[0]]
+            y = mods["o"](att)
+            if world > 1:
+                dist.all_reduce(y, group=group)
+            gate = mods["gate"](y)
+            up = mods["up"](y)
+            if world == 1:
+                x = mods["down"](gate)                     # Hadamard fused into the call
+            else:
+                h = tp.all_gather_features(gate, sizes, group)
+                h = ops.hadamard(h, had_scale)
+                x = mods["down"](h[:, d_rows[0]:d_rows[1]])
+                dist.all_reduce(x, group=group)
+            del up
+        return x
+    return step
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: uniql_b200 has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+    import uniql_b200  # noqa: F401  (fails loudly if the library is missing)
+    from uniql_b200 import ops
+
+    m = args.batch
+    layers = args.layers
+    stack = build_stack(m, rank, world, device, layers)
+    step = make_step(stack, world, rank, group)
+    gen = torch.Generator(device=device).manual_seed(7)
+    x_dev = torch.randn(m, HIDDEN, generator=gen, device=device).to(torch.float16)
+    x_host = x_dev.cpu().pin_memory()
+    y_host = torch.empty((m, HIDDEN), dtype=torch.float16).pin_memory()
+    stream = torch.cuda.Stream(device=device)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    launches_per_step = layers * (len(SHAPES) + 1)      # 5 linears + 1 Hadamard per layer
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            y = step(x_dev)
+        torch.cuda.synchronize()
+        # ---- device-resident throughput: the step replayed from a CUDA graph (the reference's own
+        # profiling harness replays decode from a graph as well) ----
+        graph, mode = None, "cuda_graph"
+        try:
+            graph = torch.cuda.CUDAGraph()
+            static_x = x_dev.clone()
+            with torch.cuda.graph(graph, stream=stream):
+                static_y = step(static_x)
+        except Exception as e:  # pragma: no cover - depends on NCCL capture support
+            graph, mode = None, f"eager ({type(e).__name__})"
+            torch.cuda.synchronize()
+
+        def run_step():
+            if graph is not None:
+                graph.replay()
+            else:
+                step(x_dev)
+
+        for _ in range(max(3, args.warmup)):
+            run_step()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            run_step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+
+        # ---- end to end through the module API with host buffers (eager calls) ----
+        def e2e_step():
+            x_in = x_host.to(device, non_blocking=True)
+            y_out = step(x_in)
+            y_host.copy_(y_out, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e2e_steps = max(1, min(args.steps, 20))
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        f1.record(stream)
+        barrier()
+        ms_e2e = f0.elapsed_time(f1)
+        # same, with the step replayed from the captured graph between the two copies
+        ms_e2e_graph = None
+        if graph is not None:
+            f0.record(stream)
+            for _ in range(e2e_steps):
+                static_x.copy_(x_host, non_blocking=True)
+                graph.replay()
+                y_host.copy_(static_y, non_blocking=True)
+            f1.record(stream)
+            barrier()
+            ms_e2e_graph = f0.elapsed_time(f1)
+        clocks = sampler.stop() if rank == 0 else None
+
+        # ---- dominant kernel alone: gate projection (14336/world x 4096), one launch per layer so every
+        # launch streams different weights (L2-cold), timed with CUDA events on the launching stream ----
+        gate_mods = [mods["gate"] for mods in stack]
+        xg = torch.randn(m, HIDDEN, generator=gen, device=device).to(torch.float16)
+        og = torch.empty((m, gate_mods[0].out_features), dtype=torch.float16, device=device)
+
+        def gate_pass():
+            for g in gate_mods:
+                ops.w4a16_linear(xg, g.weight, g.scale, None, g.out_features, out=og)
+
+        gate_pass()
+        torch.cuda.synchronize()
+        ggraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(ggraph, stream=stream):
+            gate_pass()
+        for _ in range(3):
+            ggraph.replay()
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        g0.record(stream)
+        for _ in range(reps):
+            ggraph.replay()
+        g1.record(stream)
+        torch.cuda.synchronize()
+        gate_us = g0.elapsed_time(g1) * 1e3 / (reps * len(gate_mods))
+
+    def rank_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms = rank_max(ms)
+    ms_e2e = rank_max(ms_e2e)
+    if ms_e2e_graph is not None:
+        ms_e2e_graph = rank_max(ms_e2e_graph)
+    gate_us = rank_max(gate_us)
+    status = ops.read_and_clear_status(device)
+
+    if rank == 0:
+        t_step = ms / args.steps * 1e-3
+        scale_l = LAYERS / layers
+        nbytes = step_bytes(m) / scale_l
+        peak, peak_kind, _ = measured_peaks()
+        n_gate = SHAPES["gate"][0] // world
+        gate_bytes = linear_bytes(n_gate, HIDDEN, m)
+        achieved = gate_bytes / (gate_us * 1e-6) / 1e9
+        t_e2e = ms_e2e / e2e_steps * 1e-3
+        line = {
+            "metric": "w4a16_linear_m1_hbm_gbs", "value": nbytes / t_step / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": t_step * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16xint4->f32acc", "data": "synthetic",
+            "config": {"workload": f"Llama-3.1-8B decoder projection set x{layers} layers, W4A16 g128, "
+                                   f"decode batch {m}, 14336-pt online Hadamard on down_proj input",
+                       "parallelism": f"tp{world}", "launch": mode,
+                       "l2": "each step streams %.2f GB of distinct weights per GPU (> 126 MB L2): no flush needed"
+                             % (nbytes / world / 1e9)},
+            "decode_tok_s": m / (t_step * scale_l),
+            "pct_of_hbm_peak": {"of_measured_%.0f" % peak: nbytes / world / t_step / 1e9 / peak,
+                                "of_nominal_8000": nbytes / world / t_step / 1e9 / 8000.0},
+            "roofline": {"bound": "hbm", "kernel": f"w4a16_gemv_kernel<1> {n_gate}x{HIDDEN} m={m}",
+                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / peak, "us_per_launch": gate_us,
+                         "traffic": NCU_TRAFFIC_GATE_M1 if (world == 1 and m == 1) else None},
+            "e2e": {"value": nbytes / t_e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": m * HIDDEN * 2,
+                    "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": t_e2e * 1e3, "how": "eager module calls"},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "kernel_status_word": status,
+        }
+        if ms_e2e_graph is not None:
+            tg = ms_e2e_graph / e2e_steps * 1e-3
+            line["e2e_graph_replay"] = {"value": nbytes / tg / 1e9, "unit": "GB/s", "ms_per_step": tg * 1e3}
+        if world == 1:
+            cb, td, tm, desc = cpu_linear_sample(m, os.cpu_count() or 1, 25.0)
+            line["cpu_baseline"] = {"value": cb / (td + tm) / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1,
+                                    "kind": "port", "sample": desc, "dequant_s": td, "matmul_s": tm}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1, help="decode batch M")
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -53,10 +53,14 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
         raise RuntimeError(f"{name} must be a CUDA tensor (uniql_b200 has no CPU path)")
 
 
+_need_cache: dict = {}   # (m, n, k, hadamard_dim) -> scratch bytes
+
+
 def w4a16_linear(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, bias: torch.Tensor | None,
                  n_out: int, hadamard_dim: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
     """y[m, n_out] = x[m, k] @ dequant(weight, scale)[:, :n_out] (+ bias); x fp16 2-D, row-major."""
-    _require_cuda(x, "x"); _require_cuda(weight, "weight"); _require_cuda(scale, "scale")
+    if not (x.is_cuda and weight.is_cuda and scale.is_cuda):
+        raise RuntimeError("x, weight and scale must be CUDA tensors (uniql_b200 has no CPU path)")
     if x.dtype != torch.float16 or x.dim() != 2:
         raise RuntimeError("x must be a 2-D float16 tensor")
     if weight.dtype != torch.int32 or scale.dtype != torch.float16:
@@ -64,36 +68,60 @@ def w4a16_linear(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, bia
     if x.stride(1) != 1:
         x = x.contiguous()
     m, k = x.shape
-    if weight.shape[0] * 16 != k:
-        raise RuntimeError(f"size_k mismatch: x has {k} columns, packed weight covers {weight.shape[0] * 16}")
-    n = weight.shape[1] // 2
-    if scale.shape[0] == 1 and k != 128:
+    kt, n2 = weight.shape
+    if kt * 16 != k:
+        raise RuntimeError(f"size_k mismatch: x has {k} columns, packed weight covers {kt * 16}")
+    n = n2 // 2
+    groups = scale.shape[0]
+    if groups == 1 and k != 128:
         groupsize = -1
     else:
-        if k % scale.shape[0] != 0:
+        if k % groups != 0:
             raise RuntimeError("scale rows do not divide k")
-        groupsize = k // scale.shape[0]
+        groupsize = k // groups
     if scale.shape[1] != n:
         raise RuntimeError("scale width does not match the packed weight")
     if not weight.is_contiguous() or not scale.is_contiguous():
         raise RuntimeError("weight and scale must be contiguous")
+    bias_ptr = None
     if bias is not None:
         if bias.dtype != torch.float16 or bias.numel() < n_out or not bias.is_contiguous():
             raise RuntimeError("bias must be a contiguous float16 tensor with at least n_out elements")
+        bias_ptr = bias.data_ptr()
     if (m > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
         x = x.clone(memory_format=torch.contiguous_format)
     lda = x.stride(0) if m > 1 else k
-    if out is None:
-        out = torch.empty((m, n_out), dtype=torch.float16, device=x.device)
-    L = lib()
-    with torch.cuda.device(x.device):
-        nbytes = L.uniql_w4a16_scratch_bytes(m, n, k, hadamard_dim)
-        scratch = _scratch_for(x.device, nbytes)
+    dev = x.device
+    idx = dev.index
+    switch = torch.cuda.current_device() != idx
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(idx)
+    try:
+        if out is None:
+            out = torch.empty((m, n_out), dtype=torch.float16, device=dev)
+        L = lib()
+        key = (m, n, k, hadamard_dim)
+        nbytes = _need_cache.get(key)
+        if nbytes is None:
+            nbytes = _need_cache[key] = L.uniql_w4a16_scratch_bytes(m, n, k, hadamard_dim)
+        stream = torch.cuda.current_stream().cuda_stream
+        skey = (idx, stream)
+        scratch = _scratch.get(skey)
+        if scratch is None or scratch.numel() < nbytes:
+            scratch = _scratch_for(dev, nbytes)
+        st = _status.get(idx)
+        if st is None:
+            st = status_word(dev)
         code = L.uniql_w4a16_linear(
-            x.data_ptr(), lda, weight.data_ptr(), scale.data_ptr(), bias.data_ptr() if bias is not None else None,
+            x.data_ptr(), lda, weight.data_ptr(), scale.data_ptr(), bias_ptr,
             out.data_ptr(), out.stride(0), m, n, n_out, k, groupsize, hadamard_dim,
-            scratch.data_ptr(), scratch.numel(), status_word(x.device).data_ptr(), _stream_handle(x.device))
-    check(code, "uniql_w4a16_linear")
+            scratch.data_ptr(), scratch.numel(), st.data_ptr(), stream)
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
+    if code != 0:
+        check(code, "uniql_w4a16_linear")
     return out
 
 

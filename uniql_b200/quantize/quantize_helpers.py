@@ -247,10 +247,25 @@ def w4a16_quantize(w: torch.Tensor, num_bits: int, group_size: int = -1, scale: 
 
 
 @torch.no_grad()
+def unpermute_group_scales(permuted_scale: torch.Tensor) -> torch.Tensor:
+    """Group-128 scale rows back to natural column order, whatever the number of rows (the name-compatible
+    w4a16_unpermute_scales switches to the per-channel order when there is a single group)."""
+    inv = torch.argsort(torch.tensor(get_scale_perms()[0])).to(permuted_scale.device)
+    return permuted_scale.reshape(-1, 64)[:, inv].reshape(permuted_scale.shape).contiguous()
+
+
+@torch.no_grad()
+def permute_group_scales(scale: torch.Tensor) -> torch.Tensor:
+    """Inverse of unpermute_group_scales."""
+    perm = torch.tensor(get_scale_perms()[0], device=scale.device)
+    return scale.reshape(-1, 64)[:, perm].reshape(scale.shape).contiguous()
+
+
+@torch.no_grad()
 def w4a16_dequantize(q_packed: torch.Tensor, permuted_scale: torch.Tensor, group_size: int = 128) -> torch.Tensor:
     """Packed buffers -> fp16 [K, N], w = fp16((q - 8) * s): the inverse the reference applies when it
     re-slices weights at load time (modeling/modeling_helpers.py:632-640)."""
     size_k, size_n = q_packed.shape[0] * 16, q_packed.shape[1] // 2
     q = unpack_w4a16(q_packed).to(permuted_scale.dtype) - 8
-    s = w4a16_unpermute_scales(permuted_scale, size_k, size_n, group_size)
+    s = unpermute_group_scales(permuted_scale)
     return (q.reshape(-1, group_size, size_n) * s.unsqueeze(1)).reshape(size_k, size_n)

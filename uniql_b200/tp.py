@@ -1,0 +1,130 @@
+"""Tensor-parallel sharding of W4A16 linears across the GPUs of one node (one process per GPU).
+
+The reference has no distributed layer; this is the Megatron-style split its packed layout permits:
+
+* column-parallel (q/k/v, gate/up, in_proj, lm_head): shard the output features N.  The packed weight
+  permutes values only inside 16-row x 64-column blocks and the scales only inside 64-column blocks
+  (quantize/quantize_helpers.py:38-62, 145-180 in UniQL), so a shard that starts and ends on a multiple of
+  64 columns is a plain slice ``weight[:, 2*n0:2*n1]``, ``scale[:, n0:n1]``.  Other boundaries go through
+  unpack -> gather -> repack (the recipe of modeling/modeling_helpers.py:665-767).
+* row-parallel (o_proj, down_proj, out_proj): shard the input features K on multiples of 128
+  (8 packed rows = 1 scale row): ``weight[kt0:kt1]``, ``scale[g0:g1]``; every rank produces a partial
+  [M, N] that is summed with an all-reduce; the bias is added once, after the reduction.
+* an online Hadamard in front of a row-parallel linear mixes the whole K axis: the column-parallel
+  producers' shards are all-gathered, each rank transforms the full row and keeps its K slice.
+
+Collectives go through torch.distributed (NCCL on GPUs, gloo in CPU tests).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .quantize import quantize_helpers as qh
+from .quantize.quant_linear_layers import W4A16B16O16Linear
+
+
+def balanced_splits(units: int, world: int):
+    """[(start, end)] * world: contiguous, sizes differ by at most one unit."""
+    return [(units * r // world, units * (r + 1) // world) for r in range(world)]
+
+
+def column_bounds(n_stored: int, world: int, unit: int = 64):
+    """Column ranges (multiples of `unit`, default one 64-column packing block) for each rank."""
+    assert n_stored % unit == 0
+    return [(a * unit, b * unit) for a, b in balanced_splits(n_stored // unit, world)]
+
+
+def row_bounds(k_stored: int, world: int, unit: int = 128):
+    """Input-feature ranges (multiples of one quantisation group) for each rank."""
+    assert k_stored % unit == 0
+    return [(a * unit, b * unit) for a, b in balanced_splits(k_stored // unit, world)]
+
+
+def shard_columns(weight: torch.Tensor, scale: torch.Tensor, n0: int, n1: int):
+    """Packed buffers restricted to output columns [n0, n1); both multiples of 64."""
+    assert n0 % 64 == 0 and n1 % 64 == 0 and 0 <= n0 < n1 <= scale.shape[1]
+    return weight[:, 2 * n0:2 * n1].contiguous(), scale[:, n0:n1].contiguous()
+
+
+def shard_rows(weight: torch.Tensor, scale: torch.Tensor, k0: int, k1: int):
+    """Packed buffers restricted to input features [k0, k1); both multiples of 128."""
+    assert k0 % 128 == 0 and k1 % 128 == 0 and 0 <= k0 < k1 <= weight.shape[0] * 16
+    return weight[k0 // 16:k1 // 16].contiguous(), scale[k0 // 128:k1 // 128].contiguous()
+
+
+def gather_columns(weight: torch.Tensor, scale: torch.Tensor, cols: torch.Tensor):
+    """Arbitrary output-column selection (e.g. head or segment boundaries that are not multiples of 64):
+    unpack, gather, pad the width up to a multiple of 64 with zero codes/scales, repack."""
+    q = qh.unpack_w4a16(weight)[:, cols]
+    s = qh.unpermute_group_scales(scale)[:, cols]
+    pad = (-q.shape[1]) % 64
+    if pad:
+        q = torch.nn.functional.pad(q, (0, pad))
+        s = torch.nn.functional.pad(s, (0, pad))
+    return qh.pack_w4a16(q), qh.permute_group_scales(s)
+
+
+def _local_linear(weight, scale, bias, in_features, out_features, cls=W4A16B16O16Linear):
+    lin = cls(in_features, out_features, bias=bias is not None, device="meta")
+    lin.size_k, lin.size_n = weight.shape[0] * 16, weight.shape[1] // 2
+    lin.pad_in = lin.size_k - in_features
+    lin.pad_out = lin.size_n - out_features
+    lin._buffers["weight"] = weight
+    lin._buffers["scale"] = scale
+    lin._buffers["workspace"] = torch.zeros(lin.size_n // 64 * 16, dtype=torch.int32, device=weight.device)
+    if bias is not None:
+        lin.bias = nn.Parameter(bias, requires_grad=False)
+    return lin
+
+
+class ColumnParallelW4A16Linear(nn.Module):
+    """This rank's slice of the output features of a W4A16 linear; the output stays sharded."""
+
+    def __init__(self, full: W4A16B16O16Linear, rank: int, world: int, bounds=None):
+        super().__init__()
+        bounds = bounds or column_bounds(full.size_n, world)
+        n0, n1 = bounds[rank]
+        w, s = shard_columns(full.weight, full.scale, n0, n1)
+        n_real = max(0, min(n1, full.out_features) - n0)       # columns of this shard that are not padding
+        b = full.bias.data[n0:n0 + n_real].contiguous() if full.bias is not None else None
+        self.n0, self.n1, self.out_features_local = n0, n1, n_real
+        self.local = _local_linear(w, s, b, full.in_features, n_real, type(full))
+
+    def forward(self, x):
+        return self.local(x)
+
+
+class RowParallelW4A16Linear(nn.Module):
+    """This rank's slice of the input features; partial outputs are summed over the process group."""
+
+    def __init__(self, full: W4A16B16O16Linear, rank: int, world: int, group=None, bounds=None):
+        super().__init__()
+        bounds = bounds or row_bounds(full.size_k, world)
+        k0, k1 = bounds[rank]
+        w, s = shard_rows(full.weight, full.scale, k0, k1)
+        self.k0, self.k1 = k0, k1
+        self.group, self.world = group, world
+        self.bias = full.bias                                   # added once, after the reduction
+        self.local = _local_linear(w, s, None, k1 - k0, full.out_features)
+
+    def forward(self, x_local):
+        y = self.local(x_local)
+        if self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        if self.bias is not None:
+            y = y + self.bias
+        return y
+
+
+def all_gather_features(x_local: torch.Tensor, sizes, group=None) -> torch.Tensor:
+    """Concatenate column shards [.., sizes[r]] of every rank along the last axis (uneven sizes allowed)."""
+    world = len(sizes)
+    if world == 1:
+        return x_local
+    width = max(sizes)
+    padded = x_local if x_local.shape[-1] == width else torch.nn.functional.pad(x_local, (0, width - x_local.shape[-1]))
+    out = torch.empty((world, *padded.shape), dtype=padded.dtype, device=padded.device)
+    dist.all_gather_into_tensor(out, padded.contiguous(), group=group)
+    return torch.cat([out[r][..., :sizes[r]] for r in range(world)], dim=-1)
