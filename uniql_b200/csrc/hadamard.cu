@@ -17,7 +17,7 @@
 namespace uniql {
 
 struct HadSigns {
-  uint64_t row[40];   // bit a' of row[a] set  <=>  H[a][a'] = -1
+  uint64_t row[64];   // bit a' of row[a] set  <=>  H[a][a'] = -1
 };
 
 // ------------------------------------------------------------- base matrices (host, deterministic)
@@ -260,6 +260,67 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const T* __restrict__ x, 
   }
 }
 
+// Few-row variant (decode): the transform factorises as (M (x) H_P) with M = H_base (x) H_Q acting across the
+// B = base*Q segments of length P, and the two factors commute.  CTA (s, row) forms segment s of M x with
+// signed sums of the B input segments (each CTA re-reads the row from L2: B * dim * sizeof(T) bytes per row
+// in total, which is why this path is only used for a handful of rows) and then runs the P-point
+// Walsh-Hadamard transform on it locally.  B CTAs per row instead of one.
+template <typename T>
+__global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict__ x, int64_t ldx,
+                                                             T* __restrict__ y, int64_t ldy, int P, int B,
+                                                             float scale, const HadSigns signs, int pdl_trigger) {
+  __shared__ __align__(16) float buf[1024];
+  if (pdl_trigger) pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int seg = blockIdx.x;
+  const T* xr = x + (int64_t)blockIdx.y * ldx;
+  T* yr = y + (int64_t)blockIdx.y * ldy + (size_t)seg * P;
+  const uint64_t mask = signs.row[seg];
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = 0.f;
+  for (int a0 = 0; a0 < B; a0 += 4) {          // four independent 16/32-byte loads in flight
+    float t[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (a0 + i < B) Elem<T>::load8(xr + (size_t)(a0 + i) * P + tid * 8, t[i]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (a0 + i < B) {
+        const float sg = ((mask >> (a0 + i)) & 1ull) ? -1.f : 1.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = fmaf(sg, t[i][e], v[e]);
+      }
+  }
+  butterflies<8>(v);
+#pragma unroll
+  for (int s = 0; s < 5; ++s) {
+    if ((8 << s) < P) {
+      const bool upper = (lane >> s) & 1;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float o = __shfl_xor_sync(0xffffffffu, v[i], 1 << s);
+        v[i] = upper ? (o - v[i]) : (v[i] + o);
+      }
+    }
+  }
+  if (P > 256) {
+    float4* d = reinterpret_cast<float4*>(buf + tid * 8);
+    d[0] = make_float4(v[0], v[1], v[2], v[3]);
+    d[1] = make_float4(v[4], v[5], v[6], v[7]);
+    __syncthreads();
+    if (P == 512) strided_pass<2>(buf, P, 256, tid, blockDim.x);
+    else strided_pass<4>(buf, P, 256, tid, blockDim.x);
+    __syncthreads();
+    const float4* s4 = reinterpret_cast<const float4*>(buf + tid * 8);
+    const float4 a = s4[0], b = s4[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] *= scale;
+  Elem<T>::store8(yr + tid * 8, v);
+}
+
 int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
                     int dtype, bool pdl_trigger, cudaStream_t stream) {
   const int base = hadamard_base_of(dim);
@@ -268,10 +329,38 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
   if (P < 8 || dim > 40960) return UNIQL_ESHAPE;
   if (rows == 0) return UNIQL_OK;
   HadSigns signs;
-  for (int i = 0; i < 40; ++i) signs.row[i] = 0;
+  for (int i = 0; i < 64; ++i) signs.row[i] = 0;
+  int8_t h[1600];
+  if (base > 1) base_matrix(base, h);
+
+  // ---- few rows: one CTA per (segment, row) ----
+  if (rows <= 16 && P >= 256 && !(x == y)) {
+    int64_t Ps = P < 512 ? P : 512;
+    int64_t Q = P / Ps;
+    if (base * Q > 64) { Ps = 1024; Q = P / Ps; }
+    const int64_t B = base * Q;
+    if (B <= 64 && Ps <= 1024 && Q >= 1) {
+      for (int s1 = 0; s1 < B; ++s1)
+        for (int s2 = 0; s2 < B; ++s2) {
+          const int a1 = (int)(s1 / Q), h1 = (int)(s1 % Q), a2 = (int)(s2 / Q), h2 = (int)(s2 % Q);
+          int neg = (base > 1 && h[a1 * base + a2] < 0) ? 1 : 0;
+          neg ^= __builtin_popcount((unsigned)(h1 & h2)) & 1;
+          if (neg) signs.row[s1] |= (1ull << s2);
+        }
+      dim3 grid((unsigned)B, (unsigned)rows);
+      const int threads = (int)(Ps / 8);
+      if (dtype == UNIQL_F16)
+        hadamard_split_kernel<__half><<<grid, threads, 0, stream>>>((const __half*)x, ldx, (__half*)y, ldy, (int)Ps, (int)B, scale, signs, pdl_trigger ? 1 : 0);
+      else if (dtype == UNIQL_BF16)
+        hadamard_split_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)y, ldy, (int)Ps, (int)B, scale, signs, pdl_trigger ? 1 : 0);
+      else if (dtype == UNIQL_F32)
+        hadamard_split_kernel<float><<<grid, threads, 0, stream>>>((const float*)x, ldx, (float*)y, ldy, (int)Ps, (int)B, scale, signs, pdl_trigger ? 1 : 0);
+      else return UNIQL_EDTYPE;
+      return launch_status();
+    }
+  }
+
   if (base > 1) {
-    int8_t h[1600];
-    base_matrix(base, h);
     for (int i = 0; i < base; ++i)
       for (int j = 0; j < base; ++j)
         if (h[i * base + j] < 0) signs.row[i] |= (1ull << j);
