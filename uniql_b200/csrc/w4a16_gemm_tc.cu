@@ -1,8 +1,413 @@
-// placeholder until the tcgen05 kernel lands
+// Prefill-regime W4A16 linear (m > 16) for sm_100a: tcgen05 tensor cores with the accumulator in TMEM and
+// the int4 -> fp16 dequantisation done in shared memory in front of the MMA.
+//
+// Replaces the large-batch instantiations of UniQL's Marlin kernel (csrc/linear/marlin_gemm_kernel.cuh:176-740,
+// tile table :802-810), which run mma.sync with dequantisation on the same warps, while consuming the same
+// packed buffers (quantize/quantize_helpers.py:145-165 weight order, :54-62 scale order).
+//
+// Tile: 128 (batch rows) x 256 (output columns) x 64 (k) per pipeline stage, one persistent CTA per SM.
+//   warp 0      TMA producer: activation tile [128 x 64] fp16 (128B-swizzled, K-major) and the packed weight
+//               tile [4 packed rows x 512 words] (two boxes of 256 words); no multicast.
+//   warp 1      allocates TMEM (2 x 256 fp32 columns), issues tcgen05.mma kind::f16 (M=128, N=256, K=16) from one
+//               elected lane, commits stage-release and accumulator-ready barriers.
+//   warps 2-5   epilogue: tcgen05.ld (32 lanes x 32 columns), + bias, fp32 -> fp16, row-major stores; overlaps the
+//               next tile's main loop through the second TMEM accumulator.
+//   warps 6-13  dequantise: 16-byte reads of packed words, exact (q - 8) in fp16 via LOP3 + HSUB2/HFMA2, one
+//               HMUL2 by the group scale (bit-identical to the reference's dequantised weight), 32-bit stores
+//               into the K-major 128B-swizzled B tile (bank-conflict free), fence.proxy.async, arrive.
+// Roofline: tensor pipe (2*m*n*k flops); algorithmic bytes k*n/2 + (k/128)*n*2 + m*k*2 + m*n*2.
+// Every mbarrier wait is bounded; a wait that gives up sets UNIQL_STATUS_WAIT_TIMEOUT and the kernel drains.
 #include "common.cuh"
 #include "linear_internal.cuh"
+
+#include <cuda.h>
+
 namespace uniql {
-bool gemm_tc_supported(int64_t, int64_t, int64_t) { return false; }
-size_t gemm_tc_scratch_bytes(int64_t, int64_t, int64_t) { return 0; }
-int launch_gemm_tc(const LinearArgs&, const __half*, int64_t, __half*, int64_t, cudaStream_t) { return UNIQL_ESHAPE; }
+
+namespace tc {
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int AB_STAGES = 3, P_STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KB
+constexpr int B_BYTES = BN * BK * 2;          // 32 KB
+constexpr int P_BYTES = (BK / 16) * (2 * BN) * 4;   // 8 KB: 4 packed rows x 512 words
+constexpr int OFF_A = 0;
+constexpr int OFF_B = OFF_A + AB_STAGES * A_BYTES;
+constexpr int OFF_P = OFF_B + AB_STAGES * B_BYTES;
+constexpr int OFF_BAR = OFF_P + P_STAGES * P_BYTES;
+constexpr int NUM_BARS = 3 * AB_STAGES + 2 * P_STAGES + 4;
+constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;   // + slack to align the base to 1 KB
+constexpr int THREADS = 14 * 32;
+constexpr int DEQ_WARPS = 8;
+constexpr int TMEM_COLS = 512;
+// instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128
+constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+#ifndef UNIQL_TC_WAIT_POLLS
+#define UNIQL_TC_WAIT_POLLS (1 << 22)
+#endif
+constexpr int WAIT_POLLS = UNIQL_TC_WAIT_POLLS;
+}  // namespace tc
+
+struct TcParams {
+  const uint4* S;        // permuted scales, row g has n/8 uint4
+  const __half* bias;
+  __half* D;
+  int64_t ldd;
+  int M, N, n_out, K;
+  int mtiles, ntiles;
+  int* status_word;
+};
+
+__device__ __forceinline__ uint32_t tc_smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int it = 0; it < tc::WAIT_POLLS; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tc_tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr) {
+  // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart; descriptor version 1 (sm_100)
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(tc::THREADS, 1)
+w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
+                     const __grid_constant__ CUtensorMap wmap) {
+  using namespace tc;
+  extern __shared__ uint8_t smem_unaligned[];
+  // 1 KB alignment: the 128B-swizzled tiles must start on a swizzle-atom boundary
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = tc_smem_addr(smem);
+  const uint32_t bars = sbase + OFF_BAR;
+  const uint32_t bar_full_a = bars, bar_full_b = bars + 8 * AB_STAGES, bar_empty_ab = bars + 16 * AB_STAGES;
+  const uint32_t bar_full_p = bars + 24 * AB_STAGES, bar_empty_p = bar_full_p + 8 * P_STAGES;
+  const uint32_t bar_tmem_full = bar_empty_p + 8 * P_STAGES, bar_tmem_empty = bar_tmem_full + 16;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + NUM_BARS * 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KB = p.K / BK;
+  const int total_tiles = p.mtiles * p.ntiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < AB_STAGES; ++s) {
+      tc_mbar_init(bar_full_a + 8 * s, 1);
+      tc_mbar_init(bar_full_b + 8 * s, DEQ_WARPS);
+      tc_mbar_init(bar_empty_ab + 8 * s, 1);
+    }
+    for (int s = 0; s < P_STAGES; ++s) {
+      tc_mbar_init(bar_full_p + 8 * s, 1);
+      tc_mbar_init(bar_empty_p + 8 * s, DEQ_WARPS);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc_mbar_init(bar_tmem_full + 8 * b, 1);
+      tc_mbar_init(bar_tmem_empty + 8 * b, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_addr((const void*)tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool timed_out = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int it_ab = 0, it_p = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int mt = tile % p.mtiles, nt = tile / p.mtiles;
+        for (int kb = 0; kb < KB; ++kb, ++it_ab, ++it_p) {
+          const int sp = it_p % P_STAGES;
+          if (!timed_out && !tc_mbar_wait(bar_empty_p + 8 * sp, ((it_p / P_STAGES) & 1) ^ 1)) timed_out = true;
+          tc_mbar_expect_tx(bar_full_p + 8 * sp, P_BYTES);
+          tc_tma_2d(sbase + OFF_P + sp * P_BYTES, &wmap, nt * (2 * BN), kb * 4, bar_full_p + 8 * sp);
+          tc_tma_2d(sbase + OFF_P + sp * P_BYTES + P_BYTES / 2, &wmap, nt * (2 * BN) + 256, kb * 4,
+                    bar_full_p + 8 * sp);
+          const int s = it_ab % AB_STAGES;
+          if (!timed_out && !tc_mbar_wait(bar_empty_ab + 8 * s, ((it_ab / AB_STAGES) & 1) ^ 1)) timed_out = true;
+          tc_mbar_expect_tx(bar_full_a + 8 * s, A_BYTES);
+          tc_tma_2d(sbase + OFF_A + s * A_BYTES, &amap, kb * BK, mt * BM, bar_full_a + 8 * s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int it_ab = 0, it_tile = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it_tile) {
+        const int buf = it_tile & 1;
+        if (!timed_out && !tc_mbar_wait(bar_tmem_empty + 8 * buf, ((it_tile >> 1) & 1) ^ 1)) timed_out = true;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < KB; ++kb, ++it_ab) {
+          const int s = it_ab % AB_STAGES;
+          const uint32_t ph = (it_ab / AB_STAGES) & 1;
+          if (!timed_out && !tc_mbar_wait(bar_full_a + 8 * s, ph)) timed_out = true;
+          if (!timed_out && !tc_mbar_wait(bar_full_b + 8 * s, ph)) timed_out = true;
+          tc_fence_after();
+          const uint64_t adesc = tc_smem_desc(sbase + OFF_A + s * A_BYTES);
+          const uint64_t bdesc = tc_smem_desc(sbase + OFF_B + s * B_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4)
+            tc_mma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
+          tc_commit(bar_empty_ab + 8 * s);      // stage reusable once these MMAs have read it
+        }
+        tc_commit(bar_tmem_full + 8 * buf);     // accumulator complete
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;                     // TMEM lane quadrant this warp may access
+    int it_tile = 0;
+    const bool vec_ok = ((p.ldd & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it_tile) {
+      const int mt = tile % p.mtiles, nt = tile / p.mtiles;
+      const int buf = it_tile & 1;
+      if (!timed_out && !tc_mbar_wait(bar_tmem_full + 8 * buf, (it_tile >> 1) & 1)) timed_out = true;
+      tc_fence_after();
+      const int m = mt * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      __half* drow = p.D + (size_t)m * p.ldd;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tc_ld32(taddr + c0, r);
+        const int n0 = nt * BN + c0;
+        if (m < p.M && n0 < p.n_out) {
+          if (vec_ok && n0 + 32 <= p.n_out) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float f0 = __uint_as_float(r[8 * v + 2 * e]), f1 = __uint_as_float(r[8 * v + 2 * e + 1]);
+                if (p.bias) {
+                  f0 += __half2float(p.bias[n0 + 8 * v + 2 * e]);
+                  f1 += __half2float(p.bias[n0 + 8 * v + 2 * e + 1]);
+                }
+                __half2 h = __floats2half2_rn(f0, f1);
+                pk[e] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(drow + n0 + 8 * v) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (n0 + e < p.n_out) {
+                float f = __uint_as_float(r[e]);
+                if (p.bias) f += __half2float(p.bias[n0 + e]);
+                drow[n0 + e] = __float2half_rn(f);
+              }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc_mbar_arrive(bar_tmem_empty + 8 * buf);
+    }
+  } else {
+    // ------------------------------------------------------------------ dequantise
+    const int dw = warp - 6;
+    const int blk_local = dw & 3;               // 64-column block of the 256-column tile
+    const int kt_half = dw >> 2;                // packed rows {0,1} or {2,3} of the stage
+    const int g = lane >> 2, c = lane & 3;
+    const int nblk = p.N >> 6;
+    const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
+    int it_ab = 0, it_p = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int nt = tile / p.mtiles;
+      const int blk = nt * 4 + blk_local;
+      const bool valid = blk < nblk;
+      uint32_t sdup[8];                         // the lane's 8 group scales, each duplicated into a half2
+      int cur_group = -1;
+      for (int kb = 0; kb < KB; ++kb, ++it_ab, ++it_p) {
+        const int grp = kb >> 1;                // 128 k-values per scale group, 64 per stage
+        if (grp != cur_group) {
+          cur_group = grp;
+          uint4 sv = make_uint4(0, 0, 0, 0);
+          if (valid) sv = ld_nc16(p.S + (size_t)grp * srow_u4 + (size_t)blk * 8 + g);
+          const uint32_t s4[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            sdup[2 * j] = __byte_perm(s4[j], 0, 0x1010);       // low half  -> columns 16j+g
+            sdup[2 * j + 1] = __byte_perm(s4[j], 0, 0x3232);   // high half -> columns 16j+g+8
+          }
+        }
+        const int sp = it_p % P_STAGES, s = it_ab % AB_STAGES;
+        if (!timed_out && !tc_mbar_wait(bar_full_p + 8 * sp, (it_p / P_STAGES) & 1)) timed_out = true;
+        if (!timed_out && !tc_mbar_wait(bar_empty_ab + 8 * s, ((it_ab / AB_STAGES) & 1) ^ 1)) timed_out = true;
+        const uint8_t* pk = smem + OFF_P + sp * P_BYTES + (blk_local >> 1) * (P_BYTES / 2) + (blk_local & 1) * 512 +
+                            lane * 16;
+        uint8_t* btile = smem + OFF_B + s * B_BYTES + (size_t)(blk_local * 64 + g) * 128 + 4 * c;
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const int kt = kt_half * 2 + kk;      // packed row inside the stage -> k = 16 kt .. 16 kt + 15
+          uint4 w4 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+          if (valid) w4 = *reinterpret_cast<const uint4*>(pk + kt * 1024);
+          const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
+          const uint32_t ch_lo = (uint32_t)((2 * kt) ^ g) << 4, ch_hi = (uint32_t)((2 * kt + 1) ^ g) << 4;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t qw = wq[j], qs = wq[j] >> 8;
+            uint32_t v;
+            __half2 r;
+            v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 2c, 2c+1
+            r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
+            *reinterpret_cast<__half2*>(btile + (16 * j) * 128 + ch_lo) = r;
+            v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 2c+8, 2c+9
+            r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
+            *reinterpret_cast<__half2*>(btile + (16 * j) * 128 + ch_hi) = r;
+            v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 2c, 2c+1
+            r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
+            *reinterpret_cast<__half2*>(btile + (16 * j + 8) * 128 + ch_lo) = r;
+            v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 2c+8, 2c+9
+            r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
+            *reinterpret_cast<__half2*>(btile + (16 * j + 8) * 128 + ch_hi) = r;
+          }
+        }
+        // make the generic-proxy stores visible to the tensor core's async-proxy reads, then signal
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tc_mbar_arrive(bar_full_b + 8 * s);
+          tc_mbar_arrive(bar_empty_p + 8 * sp);
+        }
+      }
+    }
+  }
+
+  if (timed_out && p.status_word) atomicOr(p.status_word, UNIQL_STATUS_WAIT_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn tc_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+bool gemm_tc_supported(int64_t m, int64_t n, int64_t k) {
+  return m > 16 && n >= 128 && n % 64 == 0 && k % 128 == 0;
+}
+
+size_t gemm_tc_scratch_bytes(int64_t, int64_t, int64_t) { return 0; }
+
+int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m, cudaStream_t stream) {
+  using namespace tc;
+  EncodeTiledFn enc = tc_encode_fn();
+  if (!enc) return cuda_fail(cudaErrorNotSupported);
+  CUtensorMap amap, wmap;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(A), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cuda_fail(cudaErrorInvalidValue);
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)(2 * a.n), (cuuint64_t)(a.k / 16)};
+    cuuint64_t strides[1] = {(cuuint64_t)(2 * a.n) * 4};
+    cuuint32_t box[2] = {256, 4};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.B), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cuda_fail(cudaErrorInvalidValue);
+  }
+  TcParams p;
+  p.S = (const uint4*)a.s; p.bias = (const __half*)a.bias; p.D = D; p.ldd = a.ldd;
+  p.M = (int)m; p.N = (int)a.n; p.n_out = (int)a.n_out; p.K = (int)a.k;
+  p.mtiles = (int)((m + BM - 1) / BM);
+  p.ntiles = (int)((a.n + BN - 1) / BN);
+  p.status_word = a.status_word;
+  static thread_local bool attr_set = false;
+  if (!attr_set) {
+    UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set = true;
+  }
+  const int64_t tiles = (int64_t)p.mtiles * p.ntiles;
+  const int sms = device_info().sm_count;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  w4a16_gemm_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p, amap, wmap);
+  return launch_status();
+}
+
+}  // namespace uniql
