@@ -370,6 +370,22 @@ def run_ours(args):
         torch.cuda.synchronize()
         gate_us = g0.elapsed_time(g1) * 1e3 / (reps * len(gate_mods))
 
+        # ---- prefill regime: the same gate projection at m = 4096 through the tcgen05 kernel ----
+        mp = 4096
+        xp = torch.randn(mp, HIDDEN, generator=gen, device=device).to(torch.float16)
+        op = torch.empty((mp, gate_mods[0].out_features), dtype=torch.float16, device=device)
+        for g in gate_mods[:3]:
+            ops.w4a16_linear(xp, g.weight, g.scale, None, g.out_features, out=op)
+        torch.cuda.synchronize()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record(stream)
+        for g in gate_mods:
+            ops.w4a16_linear(xp, g.weight, g.scale, None, g.out_features, out=op)
+        p1.record(stream)
+        torch.cuda.synchronize()
+        prefill_us = p0.elapsed_time(p1) * 1e3 / len(gate_mods)
+        del xp, op
+
     def rank_max(v):
         if world == 1:
             return v
@@ -382,6 +398,7 @@ def run_ours(args):
     if ms_e2e_graph is not None:
         ms_e2e_graph = rank_max(ms_e2e_graph)
     gate_us = rank_max(gate_us)
+    prefill_us = rank_max(prefill_us)
     status = ops.read_and_clear_status(device)
 
     if rank == 0:
@@ -412,6 +429,11 @@ def run_ours(args):
                          "traffic": NCU_TRAFFIC_GATE_M1 if (world == 1 and m == 1) else None},
             "e2e": {"value": nbytes / t_e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": m * HIDDEN * 2,
                     "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": t_e2e * 1e3, "how": "eager module calls"},
+            "m4096_tflops": {"value": world * 2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12,
+                             "kernel": f"w4a16_gemm_tc_kernel {n_gate}x{HIDDEN} m=4096 per GPU", "us_per_launch": prefill_us,
+                             "frac_of_measured_bf16_burst": (2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12)
+                             / float(measured_peaks()[2].get("bf16_tflops", 1590.0)),
+                             "frac_of_nominal_2250": (2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12) / 2250.0},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "kernel_status_word": status,

@@ -152,3 +152,55 @@ def test_linearity_property_full_size():
         e[i, r] = 1
     y = _run(layer, e)
     assert np.array_equal(y, layer["w_deq"][rows][:, :14336])
+
+
+# ---------------------------------------------------------------------------------------------
+# prefill regime (m > 16): tcgen05 tensor-core kernel
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n,k", [(256, 128), (384, 256), (200, 384), (1792, 1024), (448, 512), (128, 4096)])
+@pytest.mark.parametrize("m", [17, 64, 127, 128, 129, 300])
+def test_prefill_small_shapes(n, k, m):
+    layer = quantized_layer(n * 3 + k + m, n, k, bias=(n % 256 == 0))
+    x = make_acts(m, m, k)
+    linear_tolerance_check(_run(layer, x), _ref(layer, x))
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (14336, 4096), (4096, 14336), (12160, 4096), (4096, 12160),
+                                 (5632, 4096), (4096, 3584), (18560, 4096), (4096, 8192)])
+@pytest.mark.parametrize("m", [1024, 4096])
+def test_baseline_shapes_prefill_sampled_rows(n, k, m):
+    """Full-size launch; 48 seeded rows of the output are compared with the oracle (the rest of the rows are
+    covered by the checksum below: column sums of y equal (sum of rows of x) @ W within fp16 accumulation noise)."""
+    layer = quantized_layer(n + k + 5, n, k)
+    x = make_acts(m + 3, m, k)
+    y = _run(layer, x)
+    rng = np.random.default_rng(m + n)
+    rows = np.sort(rng.choice(m, size=48, replace=False))
+    rows[0], rows[-1] = 0, m - 1
+    ref = orc.linear_ref(x.numpy()[rows], None, None, None, n, w_deq=layer["w_deq"])
+    linear_tolerance_check(y[rows], ref)
+    col_ref = orc.linear_ref(x.float().sum(0, keepdim=True).numpy(), None, None, None, n, w_deq=layer["w_deq"])
+    col_sum = y.astype(np.float64).sum(0, keepdims=True)
+    # each y element carries at most half an fp16 ulp of rounding; the sum of m of them stays far below this
+    tol = 2.0 ** -10 * np.abs(y).astype(np.float64).sum(0, keepdims=True) + 1e-3
+    assert (np.abs(col_sum - col_ref) <= tol).all()
+
+
+def test_prefill_strided_input_bias_and_batch_dims():
+    from uniql_b200.quantize.quant_linear_layers import W4A16B16O16Linear
+    lin = torch.nn.Linear(512, 328, bias=True).half()
+    q = W4A16B16O16Linear.from_fp16(lin).cuda()
+    x = make_acts(4, 96, 1024).cuda()[:, 256:768].reshape(4, 24, 512)
+    y = q(x)
+    assert y.shape == (4, 24, 328)
+    w_deq = orc.dequantize(q.weight.cpu().numpy(), q.scale.cpu().numpy())
+    want = orc.linear_ref(x.reshape(96, 512).cpu().numpy(), None, None, lin.bias.data.numpy(), 328, w_deq=w_deq)
+    linear_tolerance_check(y.reshape(96, 328).cpu().numpy(), want)
+
+
+def test_prefill_deterministic():
+    layer = quantized_layer(21, 1024, 2048)
+    x = make_acts(5, 200, 2048)
+    a = _run(layer, x)
+    for _ in range(2):
+        assert np.array_equal(a.view(np.uint16), _run(layer, x).view(np.uint16))

@@ -12,7 +12,7 @@
 //               elected lane, commits stage-release and accumulator-ready barriers.
 //   warps 2-5   epilogue: tcgen05.ld (32 lanes x 32 columns), + bias, fp32 -> fp16, row-major stores; overlaps the
 //               next tile's main loop through the second TMEM accumulator.
-//   warps 6-13  dequantise: 16-byte reads of packed words, exact (q - 8) in fp16 via LOP3 + HSUB2/HFMA2, one
+//   warps 6-21  dequantise: 16-byte reads of packed words, exact (q - 8) in fp16 via LOP3 + HSUB2/HFMA2, one
 //               HMUL2 by the group scale (bit-identical to the reference's dequantised weight), 32-bit stores
 //               into the K-major 128B-swizzled B tile (bank-conflict free), fence.proxy.async, arrive.
 // Roofline: tensor pipe (2*m*n*k flops); algorithmic bytes k*n/2 + (k/128)*n*2 + m*k*2 + m*n*2.
@@ -36,8 +36,8 @@ constexpr int OFF_P = OFF_B + AB_STAGES * B_BYTES;
 constexpr int OFF_BAR = OFF_P + P_STAGES * P_BYTES;
 constexpr int NUM_BARS = 3 * AB_STAGES + 2 * P_STAGES + 4;
 constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;   // + slack to align the base to 1 KB
-constexpr int THREADS = 14 * 32;
-constexpr int DEQ_WARPS = 8;
+constexpr int DEQ_WARPS = 16;
+constexpr int THREADS = (6 + DEQ_WARPS) * 32;
 constexpr int TMEM_COLS = 512;
 // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128
 constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -106,6 +106,31 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 tc_lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+// Wait used by warps that sit idle for most of a tile: back off between polls to leave issue slots to the others.
+__device__ __forceinline__ bool tc_mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
+  for (int it = 0; it < tc::WAIT_POLLS; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    __nanosleep(64);
+  }
+  return false;
+}
 
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -220,7 +245,7 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it_tile) {
       const int mt = tile % p.mtiles, nt = tile / p.mtiles;
       const int buf = it_tile & 1;
-      if (!timed_out && !tc_mbar_wait(bar_tmem_full + 8 * buf, (it_tile >> 1) & 1)) timed_out = true;
+      if (!timed_out && !tc_mbar_wait_relaxed(bar_tmem_full + 8 * buf, (it_tile >> 1) & 1)) timed_out = true;
       tc_fence_after();
       const int m = mt * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
@@ -266,7 +291,7 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
     // ------------------------------------------------------------------ dequantise
     const int dw = warp - 6;
     const int blk_local = dw & 3;               // 64-column block of the 256-column tile
-    const int kt_half = dw >> 2;                // packed rows {0,1} or {2,3} of the stage
+    const int kt = dw >> 2;                     // packed row of the stage this warp converts -> k = 16 kt .. 16 kt + 15
     const int g = lane >> 2, c = lane & 3;
     const int nblk = p.N >> 6;
     const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
@@ -293,16 +318,14 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
         const int sp = it_p % P_STAGES, s = it_ab % AB_STAGES;
         if (!timed_out && !tc_mbar_wait(bar_full_p + 8 * sp, (it_p / P_STAGES) & 1)) timed_out = true;
         if (!timed_out && !tc_mbar_wait(bar_empty_ab + 8 * s, ((it_ab / AB_STAGES) & 1) ^ 1)) timed_out = true;
-        const uint8_t* pk = smem + OFF_P + sp * P_BYTES + (blk_local >> 1) * (P_BYTES / 2) + (blk_local & 1) * 512 +
+        const uint32_t pk = sbase + OFF_P + sp * P_BYTES + (blk_local >> 1) * (P_BYTES / 2) + (blk_local & 1) * 512 +
                             lane * 16;
-        uint8_t* btile = smem + OFF_B + s * B_BYTES + (size_t)(blk_local * 64 + g) * 128 + 4 * c;
-#pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
-          const int kt = kt_half * 2 + kk;      // packed row inside the stage -> k = 16 kt .. 16 kt + 15
+        const uint32_t btile = sbase + OFF_B + s * B_BYTES + (uint32_t)(blk_local * 64 + g) * 128 + 4 * c;
+        {
           uint4 w4 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-          if (valid) w4 = *reinterpret_cast<const uint4*>(pk + kt * 1024);
+          if (valid) w4 = tc_lds128(pk + kt * 1024);
           const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
-          const uint32_t ch_lo = (uint32_t)((2 * kt) ^ g) << 4, ch_hi = (uint32_t)((2 * kt + 1) ^ g) << 4;
+          const uint32_t a_lo = btile + ((uint32_t)((2 * kt) ^ g) << 4), a_hi = btile + ((uint32_t)((2 * kt + 1) ^ g) << 4);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint32_t qw = wq[j], qs = wq[j] >> 8;
@@ -310,16 +333,16 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
             __half2 r;
             v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 2c, 2c+1
             r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
-            *reinterpret_cast<__half2*>(btile + (16 * j) * 128 + ch_lo) = r;
+            tc_sts32(a_lo + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
             v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 2c+8, 2c+9
             r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
-            *reinterpret_cast<__half2*>(btile + (16 * j) * 128 + ch_hi) = r;
+            tc_sts32(a_hi + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
             v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 2c, 2c+1
             r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
-            *reinterpret_cast<__half2*>(btile + (16 * j + 8) * 128 + ch_lo) = r;
+            tc_sts32(a_lo + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
             v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 2c+8, 2c+9
             r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
-            *reinterpret_cast<__half2*>(btile + (16 * j + 8) * 128 + ch_hi) = r;
+            tc_sts32(a_hi + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
           }
         }
         // make the generic-proxy stores visible to the tensor core's async-proxy reads, then signal
