@@ -30,7 +30,8 @@ enum {
   UNIQL_ESHAPE = -3,       /* n % 64 != 0, k % 128 != 0, dim not a supported size, ...  */
   UNIQL_ESCRATCH = -4,     /* scratch buffer missing or too small                       */
   UNIQL_ECUDA = -5,        /* a CUDA runtime call failed (see uniql_last_cuda_error)    */
-  UNIQL_EDTYPE = -6        /* unsupported element type code                             */
+  UNIQL_EDTYPE = -6,       /* unsupported element type code                             */
+  UNIQL_ESTATIC = -7       /* problem needs more than the built-in scratch of uniql_w4a16_linear_static */
 };
 
 /* Element type codes for uniql_hadamard. */
@@ -79,6 +80,29 @@ int uniql_w4a16_linear(const void* A, int64_t lda, const void* B, const void* s,
 
 /* Scratch requirement of uniql_w4a16_linear for this problem on the current device. */
 size_t uniql_w4a16_scratch_bytes(int64_t m, int64_t n, int64_t k, int64_t hadamard_dim);
+
+/*
+ * Decode-size W4A16 linear (m <= 16, no Hadamard) for callers that have no way to hand over device scratch.
+ * This entry point has no counterpart in the reference.  It exists for hosts that may not allocate device
+ * memory at the point where they call into this library: a plugin running inside someone else's memory
+ * plan, a real-time loop that forbids allocator calls after start-up, code that only receives the tensors of
+ * the op and nothing else.  Same arguments and results as uniql_w4a16_linear minus the scratch pointer; the
+ * split-k counters and partial sums live in a UNIQL_STATIC_SCRATCH_BYTES array inside the library image
+ * instead (every GPU that loads the library keeps that much memory until the process exits).
+ *
+ *  - Nothing is allocated or freed, by this function or by anything it calls.
+ *  - Problems whose partial sums do not fit the array are refused with UNIQL_ESTATIC (nothing is enqueued);
+ *    m > 16 returns UNIQL_ESHAPE.  uniql_w4a16_scratch_bytes(m, n, k, 0) tells what a problem needs.
+ *  - The first call on each device looks up the array's device address and clears its counter region
+ *    (one memset enqueued on `stream`); make that first call outside of any stream capture.
+ *  - All calls on a device share the one array, and it keeps whatever the last call left in it (the counters
+ *    are always left at zero).  Two calls that can run at the same time on the GPU (different streams) would
+ *    race on it: serialise them.
+ */
+#define UNIQL_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int uniql_w4a16_linear_static(const void* A, int64_t lda, const void* B, const void* s, const void* bias,
+                              void* D, int64_t ldd, int64_t m, int64_t n, int64_t n_out, int64_t k,
+                              int groupsize, int* status_word, void* stream);
 
 /*
  * 4-bit embedding gather: out[t, :] = fp16((q - 8) * scales[ids[t]]), bit-exact with

@@ -1,0 +1,67 @@
+"""GPU: the scratch-free entry point `uniql_w4a16_linear_static`, called through the C ABI.
+
+Some callers cannot give this library device scratch: they run inside a memory plan they do not own, or in a
+loop where allocator calls are forbidden after start-up.  For them the decode kernel can use a fixed array
+built into the library.  This test drives that entry point with raw pointers, twice in a row (the array is
+shared and keeps the previous call's contents), and checks the results against the regular entry point, which
+runs the same kernel with caller-supplied scratch.  It is collected last on purpose.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import linear_tolerance_check, make_acts, quantized_layer
+from oracle import uniql_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _static_call(x, packed, scales, bias, n_out):
+    from uniql_b200._lib import check, lib
+    m, k = x.shape
+    n = scales.shape[1]
+    out = torch.empty((m, n_out), dtype=torch.float16, device=x.device)
+    stream = torch.cuda.current_stream().cuda_stream
+    code = lib().uniql_w4a16_linear_static(
+        x.data_ptr(), x.stride(0), packed.data_ptr(), scales.data_ptr(), bias.data_ptr() if bias is not None else None,
+        out.data_ptr(), out.stride(0), m, n, n_out, k, 128, None, stream)
+    check(code, "uniql_w4a16_linear_static")
+    return out
+
+
+@pytest.mark.parametrize("n,k,m", [(4096, 4096, 1), (1024, 1536, 5), (14336, 4096, 16)])
+def test_static_scratch_matches_regular_entry_point(n, k, m):
+    from uniql_b200 import ops
+    layer = quantized_layer(n + k + m, n, k, bias=True)
+    packed = torch.from_numpy(layer["packed"]).cuda()
+    scales = torch.from_numpy(layer["scales"]).cuda()
+    bias = torch.from_numpy(layer["bias"]).cuda()
+    ref = None
+    for call in range(2):                      # two calls in a row share the built-in array
+        x = make_acts(100 * call + m, m, k).cuda()
+        got = _static_call(x, packed, scales, bias, n)
+        want = ops.w4a16_linear(x, packed, scales, bias, n)
+        torch.cuda.synchronize()
+        # same kernel, same split: identical bits, and inside the oracle tolerance used by the other linear tests
+        assert torch.equal(got, want)
+        ref = orc.linear_ref(x.cpu().numpy(), None, None, layer["bias"], n, w_deq=layer["w_deq"])
+        linear_tolerance_check(got.cpu().numpy(), ref)
+    assert ref is not None
+
+
+def test_static_scratch_limits_are_reported():
+    from uniql_b200._lib import lib
+    L = lib()
+    x = torch.zeros(17, 256, dtype=torch.float16, device="cuda")
+    w = torch.zeros(16, 512, dtype=torch.int32, device="cuda")
+    s = torch.zeros(2, 256, dtype=torch.float16, device="cuda")
+    out = torch.zeros(17, 256, dtype=torch.float16, device="cuda")
+    args = (w.data_ptr(), s.data_ptr(), None, out.data_ptr(), 256)
+    assert L.uniql_w4a16_linear_static(x.data_ptr(), 256, *args, 17, 256, 256, 256, 128, None, None) == -3   # m > 16
+    assert L.uniql_w4a16_linear_static(x.data_ptr(), 256, *args, 1, 256, 256, 256, -1, None, None) == -2    # per-channel
+    # a width whose split-k partials cannot fit the built-in array is refused, nothing is launched
+    big_n, big_k = 16384, 32768
+    assert L.uniql_w4a16_scratch_bytes(16, big_n, big_k, 0) > 8 * 1024 * 1024
+    args_big = (w.data_ptr(), s.data_ptr(), None, out.data_ptr(), big_n)
+    assert L.uniql_w4a16_linear_static(x.data_ptr(), big_k, *args_big, 16, big_n, big_n, big_k, 128, None, None) == -7
+    assert b"built-in scratch" in L.uniql_strerror(-7)

@@ -123,6 +123,7 @@ extern "C" const char* uniql_strerror(int code) {
     case UNIQL_ESCRATCH: return "scratch buffer missing, misaligned or too small";
     case UNIQL_ECUDA: return "CUDA runtime error (see uniql_last_cuda_error)";
     case UNIQL_EDTYPE: return "unsupported element type";
+    case UNIQL_ESTATIC: return "problem too large for the built-in scratch of uniql_w4a16_linear_static";
     default: return "unknown error";
   }
 }

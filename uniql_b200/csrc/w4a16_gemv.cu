@@ -27,6 +27,8 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <mutex>
+
 namespace uniql {
 
 constexpr int kGemvThreads = 256;
@@ -530,4 +532,62 @@ int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, in
   return UNIQL_OK;
 }
 
+// ------------------------------------------------------------------ entry point without allocation
+// Scratch for uniql_w4a16_linear_static: ticket counters followed by split-k partial sums.  It lives in the
+// library image: every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[UNIQL_STATIC_SCRATCH_BYTES];
+
+struct StaticScratchState {
+  void* ptr;      // device address of g_static_scratch on that device
+  bool ready;
+};
+static StaticScratchState g_static_state[64];
+static std::mutex g_static_mutex;
+
+// Resolves the device address of the array (its name is only a host-side handle) once per device, with that
+// device current, and clears the counter region through the caller's stream.
+static int static_scratch_for_current_device(void** out, cudaStream_t stream) {
+  int dev = 0;
+  UNIQL_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return UNIQL_EINVAL;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticScratchState& st = g_static_state[dev];
+  if (!st.ready) {
+    void* ptr = nullptr;
+    UNIQL_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    UNIQL_CUDA_TRY(cudaMemsetAsync(ptr, 0, UNIQL_SCRATCH_COUNTER_BYTES, stream));
+    st.ptr = ptr;
+    st.ready = true;
+  }
+  *out = st.ptr;
+  return UNIQL_OK;
+}
+
 }  // namespace uniql
+
+extern "C" int uniql_w4a16_linear_static(const void* A, int64_t lda, const void* B, const void* s, const void* bias,
+                                         void* D, int64_t ldd, int64_t m, int64_t n, int64_t n_out, int64_t k,
+                                         int groupsize, int* status_word, void* stream_) {
+  using namespace uniql;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (groupsize != 128) return groupsize == -1 ? UNIQL_EGROUPSIZE : UNIQL_EINVAL;
+  if (m < 0 || n <= 0 || k <= 0 || n_out <= 0 || n_out > n) return UNIQL_EINVAL;
+  if (m > 16) return UNIQL_ESHAPE;                       // decode kernel only
+  if (n % 64 != 0 || k % 128 != 0 || n > (int64_t)1 << 22 || k > (int64_t)1 << 22) return UNIQL_ESHAPE;
+  if (lda < k || ldd < n_out || lda % 8 != 0) return UNIQL_EINVAL;
+  if (m == 0) return UNIQL_OK;
+  if (!A || !B || !s || !D) return UNIQL_EINVAL;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(s) || (reinterpret_cast<uintptr_t>(D) & 1u)) return UNIQL_EINVAL;
+  const GemvPlan plan = plan_gemv(m, n, k);
+  if (UNIQL_SCRATCH_COUNTER_BYTES + plan.partial_bytes > (size_t)UNIQL_STATIC_SCRATCH_BYTES) return UNIQL_ESTATIC;
+  void* scratch = nullptr;
+  int st = static_scratch_for_current_device(&scratch, stream);
+  if (st != UNIQL_OK) return st;
+  LinearArgs a;
+  a.B = B; a.s = s; a.bias = bias; a.ldd = ldd; a.n = n; a.n_out = n_out; a.k = k;
+  a.counters = (int*)scratch;
+  a.partials = (float*)((char*)scratch + UNIQL_SCRATCH_COUNTER_BYTES);
+  a.partial_bytes = (size_t)UNIQL_STATIC_SCRATCH_BYTES - UNIQL_SCRATCH_COUNTER_BYTES;
+  a.status_word = status_word;
+  return launch_gemv(a, (const __half*)A, lda, (__half*)D, m, plan, false, stream);
+}
