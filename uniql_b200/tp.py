@@ -126,5 +126,5 @@ def all_gather_features(x_local: torch.Tensor, sizes, group=None) -> torch.Tenso
     width = max(sizes)
     padded = x_local if x_local.shape[-1] == width else torch.nn.functional.pad(x_local, (0, width - x_local.shape[-1]))
     out = torch.empty((world, *padded.shape), dtype=padded.dtype, device=padded.device)
-    dist.all_gather_into_tensor(out, padded.contiguous(), group=group)
+    dist.all_gather([out[r] for r in range(world)], padded.contiguous(), group=group)
     return torch.cat([out[r][..., :sizes[r]] for r in range(world)], dim=-1)
