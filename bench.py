@@ -247,11 +247,37 @@ def make_step(stack, world, rank, group):
     return step
 
 
+def _log(msg):
+    if os.environ.get("UNIQL_BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')} {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
+
+
+def _arm_deadline(seconds):
+    """Hard stop for a run that stopped making progress (a collective that never completes): the process exits
+    by itself instead of sitting on the GPUs until an outer limit kills it."""
+    import threading
+
+    def fire():
+        print(f"bench.py: no result after {seconds} s, giving up", file=sys.stderr, flush=True)
+        os._exit(3)
+
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+    return t
+
+
 def run_ours(args):
+    _arm_deadline(args.deadline)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        # whole-step CUDA-graph capture of NCCL collectives needs the process group's asynchronous error
+        # handling (a watchdog thread that polls CUDA events) switched off before the group is created
+        os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")
+        os.environ.setdefault("NCCL_ASYNC_ERROR_HANDLING", "0")
     import torch
     import torch.distributed as dist
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
@@ -260,14 +286,17 @@ def run_ours(args):
     device = torch.device("cuda", local_rank)
     group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
         group = dist.group.WORLD
     import uniql_b200  # noqa: F401  (fails loudly if the library is missing)
     from uniql_b200 import ops
 
     m = args.batch
     layers = args.layers
+    _log("process group up, building the synthetic stack")
     stack = build_stack(m, rank, world, device, layers)
+    _log("stack built")
     step = make_step(stack, world, rank, group)
     gen = torch.Generator(device=device).manual_seed(7)
     x_dev = torch.randn(m, HIDDEN, generator=gen, device=device).to(torch.float16)
@@ -286,10 +315,14 @@ def run_ours(args):
         for _ in range(2):
             y = step(x_dev)
         torch.cuda.synchronize()
+        _log("eager warm-up done")
         # ---- device-resident throughput: the step replayed from a CUDA graph (the reference's own
         # profiling harness replays decode from a graph as well) ----
         graph, mode = None, "cuda_graph"
+        use_graph = os.environ.get("UNIQL_BENCH_GRAPH", "1") != "0"
         try:
+            if not use_graph:
+                raise RuntimeError("graph replay disabled by UNIQL_BENCH_GRAPH=0")
             graph = torch.cuda.CUDAGraph()
             static_x = x_dev.clone()
             with torch.cuda.graph(graph, stream=stream):
@@ -297,6 +330,11 @@ def run_ours(args):
         except Exception as e:  # pragma: no cover - depends on NCCL capture support
             graph, mode = None, f"eager ({type(e).__name__})"
             torch.cuda.synchronize()
+        if world > 1:      # every rank must take the same path
+            flag = torch.tensor([1 if graph is not None else 0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0 and graph is not None:
+                graph, mode = None, "eager (capture failed on another rank)"
 
         def run_step():
             if graph is not None:
@@ -304,9 +342,11 @@ def run_ours(args):
             else:
                 step(x_dev)
 
+        _log(f"launch mode: {mode}")
         for _ in range(max(3, args.warmup)):
             run_step()
         barrier()
+        _log("warm-up done")
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
@@ -318,6 +358,7 @@ def run_ours(args):
         e1.record(stream)
         barrier()
         ms = e0.elapsed_time(e1)
+        _log(f"timed region done: {ms / args.steps:.3f} ms/step")
 
         # ---- end to end through the module API with host buffers (eager calls) ----
         def e2e_step():
@@ -348,6 +389,7 @@ def run_ours(args):
             barrier()
             ms_e2e_graph = f0.elapsed_time(f1)
         clocks = sampler.stop() if rank == 0 else None
+        _log("e2e done")
 
         # ---- dominant kernel alone: gate projection (14336/world x 4096), one launch per layer so every
         # launch streams different weights (L2-cold), timed with CUDA events on the launching stream ----
@@ -453,8 +495,13 @@ def run_ours(args):
                                     "kind": "port", "sample": desc, "dequant_s": td, "matmul_s": tm}
         print(json.dumps(line))
     if world > 1:
+        # Leave without tearing the communicator down: destroying a process group whose collectives live in
+        # instantiated CUDA graphs was seen to block; every rank has finished its GPU work at this point.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
@@ -465,6 +512,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="decode batch M")
     ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--deadline", type=int, default=900, help="seconds after which a stuck run exits by itself")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
