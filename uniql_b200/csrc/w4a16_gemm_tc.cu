@@ -26,7 +26,7 @@ namespace uniql {
 
 namespace tc {
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int AB_STAGES = 3, P_STAGES = 4;
+constexpr int AB_STAGES = 4, P_STAGES = 3;
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB
 constexpr int B_BYTES = BN * BK * 2;          // 32 KB
 constexpr int P_BYTES = (BK / 16) * (2 * BN) * 4;   // 8 KB: 4 packed rows x 512 words
@@ -301,19 +301,18 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
       const int blk = nt * 4 + blk_local;
       const bool valid = blk < nblk;
       uint32_t sdup[8];                         // the lane's 8 group scales, each duplicated into a half2
-      int cur_group = -1;
+      const uint4* srow = p.S + (size_t)blk * 8 + g;
+      uint4 snext = make_uint4(0, 0, 0, 0);     // scales of the next group, requested one group ahead
+      if (valid) snext = ld_nc16(srow);
       for (int kb = 0; kb < KB; ++kb, ++it_ab, ++it_p) {
-        const int grp = kb >> 1;                // 128 k-values per scale group, 64 per stage
-        if (grp != cur_group) {
-          cur_group = grp;
-          uint4 sv = make_uint4(0, 0, 0, 0);
-          if (valid) sv = ld_nc16(p.S + (size_t)grp * srow_u4 + (size_t)blk * 8 + g);
-          const uint32_t s4[4] = {sv.x, sv.y, sv.z, sv.w};
+        if ((kb & 1) == 0) {                    // 128 k-values per scale group, 64 per stage
+          const uint32_t s4[4] = {snext.x, snext.y, snext.z, snext.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             sdup[2 * j] = __byte_perm(s4[j], 0, 0x1010);       // low half  -> columns 16j+g
             sdup[2 * j + 1] = __byte_perm(s4[j], 0, 0x3232);   // high half -> columns 16j+g+8
           }
+          if (valid && kb + 2 < KB) snext = ld_nc16(srow + (size_t)((kb >> 1) + 1) * srow_u4);
         }
         const int sp = it_p % P_STAGES, s = it_ab % AB_STAGES;
         if (!timed_out && !tc_mbar_wait(bar_full_p + 8 * sp, (it_p / P_STAGES) & 1)) timed_out = true;
