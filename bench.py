@@ -475,8 +475,7 @@ def run_ours(args):
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "us_per_launch": gate_us,
                          "traffic": NCU_TRAFFIC_GATE_M1 if (world == 1 and m == 1) else None},
-            "e2e": {"value": nbytes / t_e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": m * HIDDEN * 2,
-                    "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": t_e2e * 1e3, "how": "eager module calls"},
+            "e2e": None,
             "m4096_tflops": {"value": world * 2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12,
                              "kernel": f"w4a16_gemm_tc_kernel {n_gate}x{HIDDEN} m=4096 per GPU", "us_per_launch": prefill_us,
                              "frac_of_measured_bf16_burst": (2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12)
@@ -486,9 +485,19 @@ def run_ours(args):
             "clocks": clocks,
             "kernel_status_word": status,
         }
+        eager = {"value": nbytes / t_e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": m * HIDDEN * 2,
+                 "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": t_e2e * 1e3,
+                 "how": "pinned host x -> device, eager Python module calls, result -> pinned host"}
         if ms_e2e_graph is not None:
+            # headline end-to-end number: host input copied in, the module stack replayed from its CUDA graph
+            # (how the reference's own decode profiling runs, profile_model.py:540-553), result copied out
             tg = ms_e2e_graph / e2e_steps * 1e-3
-            line["e2e_graph_replay"] = {"value": nbytes / tg / 1e9, "unit": "GB/s", "ms_per_step": tg * 1e3}
+            line["e2e"] = {"value": nbytes / tg / 1e9, "unit": "GB/s", "h2d_bytes_per_step": m * HIDDEN * 2,
+                           "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": tg * 1e3,
+                           "how": "pinned host x -> device, module stack replayed from a CUDA graph, result -> pinned host"}
+            line["e2e_eager_module_calls"] = eager
+        else:
+            line["e2e"] = eager
         if world == 1:
             cb, td, tm, desc = cpu_linear_sample(m, os.cpu_count() or 1, 25.0)
             line["cpu_baseline"] = {"value": cb / (td + tm) / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1,

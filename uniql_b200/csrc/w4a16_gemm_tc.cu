@@ -164,6 +164,8 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
   const int total_tiles = p.mtiles * p.ntiles;
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&amap) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
     for (int s = 0; s < AB_STAGES; ++s) {
       tc_mbar_init(bar_full_a + 8 * s, 1);
       tc_mbar_init(bar_full_b + 8 * s, DEQ_WARPS);

@@ -170,6 +170,7 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
   const uint4* sptr = p.S + (size_t)(active ? blk : 0) * 8 + g + (size_t)g0 * srow_u4;
 
   if (lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");   // hide the descriptor fetch of the first tile
     for (int s = 0; s < p.R; ++s) mbar_init(bar0 + s * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -446,7 +447,7 @@ GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k) {
       // groups pays for the partly used first/last group through the slower predicated path
       const int len = (KT + splits - 1) / splits;
       const bool aligned = (NG % splits) == 0;
-      const double eff_len = aligned ? len : len + 6.0;
+      const double eff_len = aligned ? len : len + 14.0;
       // cost in "packed rows per warp": streamed rows + fixed latency per wave + split-k reduction
       double cost = (double)waves * (eff_len + 12.0) * waste + (S > 1 ? 6.0 + 0.35 * S : 0.0);
       if (cost < best_cost - 1e-9) {

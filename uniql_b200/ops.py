@@ -105,7 +105,7 @@ def w4a16_linear(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, bia
         nbytes = _need_cache.get(key)
         if nbytes is None:
             nbytes = _need_cache[key] = L.uniql_w4a16_scratch_bytes(m, n, k, hadamard_dim)
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = torch._C._cuda_getCurrentRawStream(idx)
         skey = (idx, stream)
         scratch = _scratch.get(skey)
         if scratch is None or scratch.numel() < nbytes:
