@@ -214,7 +214,7 @@ def build_stack(m, rank, world, device, layers):
     return stack
 
 
-def make_step(stack, world, rank, group):
+def make_step(stack, world, rank, group, push=None):
     """Returns step(x) -> y running every projection of every layer once (no attention / activation maths:
     q-shard stands in for the attention output and the gate shard for the MLP activation)."""
     import torch
@@ -232,16 +232,22 @@ def make_step(stack, world, rank, group):
             att = qkv[:, :o_rows[1] - o_rows[0]]
             y = mods["o"](att)
             if world > 1:
-                dist.all_reduce(y, group=group)
+                if push is not None:
+                    push.all_reduce(y)
+                else:
+                    dist.all_reduce(y, group=group)
             gate = mods["gate"](y)
             up = mods["up"](y)
             if world == 1:
                 x = mods["down"](gate)                     # Hadamard fused into the call
             else:
-                h = tp.all_gather_features(gate, sizes, group)
+                h = push.all_gather_features(gate, sizes) if push is not None else tp.all_gather_features(gate, sizes, group)
                 h = ops.hadamard(h, had_scale)
                 x = mods["down"](h[:, d_rows[0]:d_rows[1]])
-                dist.all_reduce(x, group=group)
+                if push is not None:
+                    push.all_reduce(x)
+                else:
+                    dist.all_reduce(x, group=group)
             del up
         return x
     return step
@@ -297,7 +303,14 @@ def run_ours(args):
     _log("process group up, building the synthetic stack")
     stack = build_stack(m, rank, world, device, layers)
     _log("stack built")
-    step = make_step(stack, world, rank, group)
+    push, collective = None, "none"
+    if world > 1:
+        collective = os.environ.get("UNIQL_TP_COLLECTIVE", "push")
+        if collective == "push":
+            from uniql_b200 import tp
+            push = tp.PushAllReduce(group, max_elems=max(16 * 16384, m * INTER), device=device)
+        _log(f"collective: {collective}")
+    step = make_step(stack, world, rank, group, push)
     gen = torch.Generator(device=device).manual_seed(7)
     x_dev = torch.randn(m, HIDDEN, generator=gen, device=device).to(torch.float16)
     x_host = x_dev.cpu().pin_memory()
@@ -466,6 +479,8 @@ def run_ours(args):
             "config": {"workload": f"Llama-3.1-8B decoder projection set x{layers} layers, W4A16 g128, "
                                    f"decode batch {m}, 14336-pt online Hadamard on down_proj input",
                        "parallelism": f"tp{world}", "launch": mode,
+                       "collective": {"push": "uniql_allreduce_push (peer stores over NVLink, one kernel)",
+                                      "nccl": "NCCL all_reduce / all_gather", "none": "none"}[collective],
                        "l2": "each step streams %.2f GB of distinct weights per GPU (> 126 MB L2): no flush needed"
                              % (nbytes / world / 1e9)},
             "decode_tok_s": m / (t_step * scale_l),

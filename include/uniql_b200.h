@@ -133,6 +133,26 @@ int uniql_hadamard(const void* x, void* y, int64_t rows, int64_t dim, float scal
  * base in {12, 20, 28, 40}; `out` is a HOST pointer.  Returns UNIQL_ESHAPE for other orders. */
 int uniql_hadamard_base_matrix(int base, int8_t* out);
 
+/*
+ * One-shot push all-reduce (sum) of fp16 vectors across the GPUs of one node, for the row-parallel linears of a
+ * tensor-parallel model at decode sizes.  No counterpart in the reference (it is single-GPU).  One process per GPU.
+ *
+ *   uniql_comm_create   allocates this rank's staging block (cudaMalloc, once, at set-up) and writes its CUDA IPC
+ *                       handle (uniql_comm_handle_bytes() bytes) to `handle_out` (HOST pointer).  max_elems: largest
+ *                       message in fp16 elements (multiple of 8, at most 524288).
+ *   uniql_comm_connect  `all_handles` (HOST pointer) = the handles of ranks 0..world-1 concatenated in rank order
+ *                       (exchange them with any host-side channel); opens the peers' blocks.
+ *   uniql_allreduce_push  out[i] = sum over ranks of in[i], summed in rank order in fp32, identical on every rank;
+ *                       in/out are DEVICE pointers (may alias), count a multiple of 8.  Every rank must issue the same
+ *                       sequence of calls.  Peer data is stored into the consumer's memory; waits are bounded
+ *                       (UNIQL_STATUS_WAIT_TIMEOUT in *status_word on give-up).  Safe to capture in a CUDA graph.
+ */
+size_t uniql_comm_handle_bytes(void);
+int uniql_comm_create(int rank, int world, int64_t max_elems, void** comm_out, void* handle_out);
+int uniql_comm_connect(void* comm, const void* all_handles);
+int uniql_comm_destroy(void* comm);
+int uniql_allreduce_push(void* comm, const void* in, void* out, int64_t count, int* status_word, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

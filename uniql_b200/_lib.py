@@ -31,6 +31,11 @@ SYMBOLS = {
     "uniql_hadamard": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_float, _c.c_int, _c.c_void_p]),
     "uniql_hadamard_base_matrix": (_c.c_int, [_c.c_int, _c.c_void_p]),
+    "uniql_comm_handle_bytes": (_c.c_size_t, []),
+    "uniql_comm_create": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int64, _c.POINTER(_c.c_void_p), _c.c_void_p]),
+    "uniql_comm_connect": (_c.c_int, [_c.c_void_p, _c.c_void_p]),
+    "uniql_comm_destroy": (_c.c_int, [_c.c_void_p]),
+    "uniql_allreduce_push": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p]),
 }
 
 

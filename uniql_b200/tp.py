@@ -128,3 +128,61 @@ def all_gather_features(x_local: torch.Tensor, sizes, group=None) -> torch.Tenso
     out = torch.empty((world, *padded.shape), dtype=padded.dtype, device=padded.device)
     dist.all_gather([out[r] for r in range(world)], padded.contiguous(), group=group)
     return torch.cat([out[r][..., :sizes[r]] for r in range(world)], dim=-1)
+
+
+class PushAllReduce:
+    """Latency-optimised all-reduce (sum) of fp16 tensors for decode-size messages, backed by
+    `uniql_allreduce_push`: every rank stores its partial into each peer's staging buffer over NVLink and sums
+    locally.  Set-up exchanges CUDA IPC handles through the (host side of the) process group.  Messages that
+    do not fit (or are not fp16 / not a multiple of 8 elements) go through `dist.all_reduce`."""
+
+    def __init__(self, group=None, max_elems: int = 16 * 16384, device=None):
+        import ctypes
+
+        from ._lib import check, lib
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.max_elems = max_elems
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._lib = lib()
+        self._comm = ctypes.c_void_p()
+        nbytes = self._lib.uniql_comm_handle_bytes()
+        handle = ctypes.create_string_buffer(nbytes)
+        with torch.cuda.device(self.device):
+            check(self._lib.uniql_comm_create(self.rank, self.world, max_elems, ctypes.byref(self._comm), handle),
+                  "uniql_comm_create")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            blob = ctypes.create_string_buffer(b"".join(handles), nbytes * self.world)
+            check(self._lib.uniql_comm_connect(self._comm, blob), "uniql_comm_connect")
+        dist.barrier(group=group)
+        from . import ops
+        self._status = ops.status_word(self.device)
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """In-place sum over the group; returns t."""
+        n = t.numel()
+        if (t.dtype != torch.float16 or not t.is_contiguous() or n % 8 != 0 or n > self.max_elems
+                or t.data_ptr() % 16 != 0):
+            dist.all_reduce(t, group=self.group)
+            return t
+        from ._lib import check
+        code = self._lib.uniql_allreduce_push(self._comm, t.data_ptr(), t.data_ptr(), n, self._status.data_ptr(),
+                                              torch._C._cuda_getCurrentRawStream(self.device.index))
+        check(code, "uniql_allreduce_push")
+        return t
+
+    def all_gather_features(self, x_local: torch.Tensor, sizes) -> torch.Tensor:
+        """Concatenation of the ranks' column shards, done as a sum of zero-padded rows (one push all-reduce)."""
+        offs = [0]
+        for s in sizes:
+            offs.append(offs[-1] + s)
+        full = torch.zeros((*x_local.shape[:-1], offs[-1]), dtype=x_local.dtype, device=x_local.device)
+        full[..., offs[self.rank]:offs[self.rank + 1]] = x_local
+        return self.all_reduce(full)
+
+    def close(self):
+        if self._comm:
+            self._lib.uniql_comm_destroy(self._comm)
+            self._comm = None
