@@ -214,7 +214,7 @@ def build_stack(m, rank, world, device, layers):
     return stack
 
 
-def make_step(stack, world, rank, group, push=None):
+def make_step(stack, world, rank, group, push=None, fused=None):
     """Returns step(x) -> y running every projection of every layer once (no attention / activation maths:
     q-shard stands in for the attention output and the gate shard for the MLP activation)."""
     import torch
@@ -230,8 +230,12 @@ def make_step(stack, world, rank, group, push=None):
         for mods in stack:
             qkv = mods["qkv"](x)
             att = qkv[:, :o_rows[1] - o_rows[0]]
-            y = mods["o"](att)
-            if world > 1:
+            if fused is not None:
+                o = mods["o"]
+                y = fused[0].linear_all_reduce(att, o.weight, o.scale, None, o.out_features)
+            else:
+                y = mods["o"](att)
+            if world > 1 and fused is None:
                 if push is not None:
                     push.all_reduce(y)
                 else:
@@ -243,11 +247,15 @@ def make_step(stack, world, rank, group, push=None):
             else:
                 h = push.all_gather_features(gate, sizes) if push is not None else tp.all_gather_features(gate, sizes, group)
                 h = ops.hadamard(h, had_scale)
-                x = mods["down"](h[:, d_rows[0]:d_rows[1]])
-                if push is not None:
-                    push.all_reduce(x)
+                if fused is not None:
+                    d = mods["down"]
+                    x = fused[1].linear_all_reduce(h[:, d_rows[0]:d_rows[1]], d.weight, d.scale, None, d.out_features)
                 else:
-                    dist.all_reduce(x, group=group)
+                    x = mods["down"](h[:, d_rows[0]:d_rows[1]])
+                    if push is not None:
+                        push.all_reduce(x)
+                    else:
+                        dist.all_reduce(x, group=group)
             del up
         return x
     return step
@@ -303,14 +311,17 @@ def run_ours(args):
     _log("process group up, building the synthetic stack")
     stack = build_stack(m, rank, world, device, layers)
     _log("stack built")
-    push, collective = None, "none"
+    push, fused, collective = None, None, "none"
     if world > 1:
-        collective = os.environ.get("UNIQL_TP_COLLECTIVE", "push")
-        if collective == "push":
+        collective = os.environ.get("UNIQL_TP_COLLECTIVE", "fused" if m <= 16 else "push")
+        if collective in ("push", "fused"):
             from uniql_b200 import tp
             push = tp.PushAllReduce(group, max_elems=max(16 * 16384, m * INTER), device=device)
+        if collective == "fused":
+            # one channel per call-site shape (o_proj, down_proj): their epochs advance independently
+            fused = [tp.PushAllReduce(group, max_elems=16 * HIDDEN, device=device) for _ in range(2)]
         _log(f"collective: {collective}")
-    step = make_step(stack, world, rank, group, push)
+    step = make_step(stack, world, rank, group, push, fused)
     gen = torch.Generator(device=device).manual_seed(7)
     x_dev = torch.randn(m, HIDDEN, generator=gen, device=device).to(torch.float16)
     x_host = x_dev.cpu().pin_memory()
@@ -479,7 +490,9 @@ def run_ours(args):
             "config": {"workload": f"Llama-3.1-8B decoder projection set x{layers} layers, W4A16 g128, "
                                    f"decode batch {m}, 14336-pt online Hadamard on down_proj input",
                        "parallelism": f"tp{world}", "launch": mode,
-                       "collective": {"push": "uniql_allreduce_push (peer stores over NVLink, one kernel)",
+                       "collective": {"fused": "sum over ranks fused into the row-parallel decode kernel "
+                                               "(uniql_w4a16_linear_allreduce); feature gather by uniql_allreduce_push",
+                                      "push": "uniql_allreduce_push (peer stores over NVLink, one kernel)",
                                       "nccl": "NCCL all_reduce / all_gather", "none": "none"}[collective],
                        "l2": "each step streams %.2f GB of distinct weights per GPU (> 126 MB L2): no flush needed"
                              % (nbytes / world / 1e9)},

@@ -153,6 +153,21 @@ int uniql_comm_connect(void* comm, const void* all_handles);
 int uniql_comm_destroy(void* comm);
 int uniql_allreduce_push(void* comm, const void* in, void* out, int64_t count, int* status_word, void* stream);
 
+/*
+ * Row-parallel W4A16 linear with the cross-GPU sum fused into the kernel (decode sizes, m <= 16, m*n within the
+ * communicator's max_elems): D = sum over ranks of (A_rank * dequant(B_rank)) (+ bias), identical on every rank.
+ * The CTA that finishes a column group stores its fp16 partial, tagged with an epoch, straight into every rank's
+ * staging block over NVLink and then adds up the partials that arrived in its own block (rank order, fp32) —
+ * the same arithmetic as uniql_w4a16_linear followed by uniql_allreduce_push, in one launch.  No counterpart in
+ * the reference.  Use one communicator per call site shape (e.g. one for o_proj, one for down_proj): calls through a
+ * communicator must have the same (m, n, k) on all ranks and the same sequence of calls.  Other arguments as for
+ * uniql_w4a16_linear (no Hadamard option).
+ */
+int uniql_w4a16_linear_allreduce(void* comm, const void* A, int64_t lda, const void* B, const void* s,
+                                 const void* bias, void* D, int64_t ldd, int64_t m, int64_t n, int64_t n_out,
+                                 int64_t k, int groupsize, void* scratch, size_t scratch_bytes, int* status_word,
+                                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,24 @@ def main():
     for r, sz in enumerate(sizes):
         ok &= bool((gathered[:, off:off + sz] == r + 1).all())
         off += sz
+    # ---- fused row-parallel linear + all-reduce equals linear followed by the stand-alone push all-reduce ----
+    from uniql_b200.quantize.quant_linear_layers import W4A16B16O16Linear
+    torch.manual_seed(5)                                    # same full layer on every rank
+    for n, k, m in [(4096, 4096, 1), (1024, 2048, 16), (4096, 14336, 4)]:
+        full = W4A16B16O16Linear.from_fp16(torch.nn.Linear(k, n, bias=True).half()).to(dev)
+        chan = tp.PushAllReduce(max_elems=16 * 4096)          # one channel per call-site shape
+        row_fused = tp.RowParallelW4A16Linear(full, rank, world, fused=chan)
+        row_plain = tp.RowParallelW4A16Linear(full, rank, world)
+        g = torch.Generator(device=dev).manual_seed(77)
+        xin = torch.randn(m, k, device=dev, generator=g).half()[:, row_plain.k0:row_plain.k1]
+        for call in range(3):
+            y_f = row_fused(xin * (call + 1))
+            part = row_plain.local(xin * (call + 1))
+            y_p = ar.all_reduce(part.clone().view(-1)).view_as(part)
+            torch.cuda.synchronize()
+            ok &= bool(torch.allclose(y_f.float(), (y_p.float() + full.bias.float()), rtol=2e-3, atol=2e-3))
+            y_full = full(torch.randn(m, k, device=dev, generator=torch.Generator(device=dev).manual_seed(77)).half() * (call + 1))
+            ok &= bool(torch.allclose(y_f.float(), y_full.float(), rtol=2e-2, atol=2e-2 * float(y_full.float().abs().max())))
     ok &= ops.read_and_clear_status(dev) == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

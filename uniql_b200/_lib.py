@@ -24,6 +24,9 @@ SYMBOLS = {
     "uniql_w4a16_linear_static": (_c.c_int, [
         _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64,
         _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "uniql_w4a16_linear_allreduce": (_c.c_int, [
+        _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64,
+        _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "uniql_w4a16_scratch_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64]),
     "uniql_w4_embedding": (_c.c_int, [
         _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64,

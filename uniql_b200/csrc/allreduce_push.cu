@@ -14,6 +14,7 @@
 //   epoch  [kMaxCtas] u32                per-CTA call counter kept on the device (CUDA-graph replay safe)
 // CTA c handles elements [c*kChunk, (c+1)*kChunk) and never talks to other CTAs.
 #include "common.cuh"
+#include "linear_internal.cuh"
 
 #include <stdio.h>
 
@@ -26,8 +27,10 @@ constexpr int kArMaxWorld = 8;
 constexpr int kArSpinLimit = 1 << 22;
 
 struct ArLayout {
-  size_t staging_bytes;   // 2 * world * max_elems * 2
-  size_t flags_off, epoch_off, total;
+  size_t staging_bytes;   // 2 parities * world slots * max_elems/2 words * 8 bytes
+  size_t flags_off, epoch_off;
+  size_t fused_staging_off, fused_epoch_off;   // same again for the all-reduce fused into the decode linear
+  size_t total;
 };
 
 static ArLayout ar_layout(int world, int64_t max_elems) {
@@ -35,7 +38,9 @@ static ArLayout ar_layout(int world, int64_t max_elems) {
   L.staging_bytes = (size_t)2 * world * max_elems * 4;   // 8-byte words {2 halves, epoch}
   L.flags_off = (L.staging_bytes + 255) / 256 * 256;
   L.epoch_off = L.flags_off;
-  L.total = L.epoch_off + (size_t)kArMaxCtas * 4;
+  L.fused_staging_off = (L.epoch_off + (size_t)kArMaxCtas * 4 + 255) / 256 * 256;
+  L.fused_epoch_off = L.fused_staging_off + L.staging_bytes;
+  L.total = L.fused_epoch_off + (size_t)4096 * 4;      // one epoch counter per column group of the fused linear
   return L;
 }
 
@@ -173,6 +178,23 @@ extern "C" int uniql_comm_destroy(void* comm) {
   delete c;
   return UNIQL_OK;
 }
+
+namespace uniql {
+int comm_fuse_desc(void* comm, int64_t m, int64_t n, ArFuse* out) {
+  uniql_comm* c = (uniql_comm*)comm;
+  if (!c || !out) return UNIQL_EINVAL;
+  if (m * n > c->max_elems || n / 64 > 4096) return UNIQL_ESHAPE;
+  for (int r = 0; r < 8; ++r) out->bufs[r] = c->bufs[r];
+  for (int r = 0; r < c->world; ++r)
+    if (!c->bufs[r]) return UNIQL_EINVAL;            // uniql_comm_connect has not run
+  out->rank = c->rank; out->world = c->world;
+  out->staging_off = c->layout.fused_staging_off;
+  out->epoch_off = c->layout.fused_epoch_off;
+  out->words_per_slot = c->max_elems / 2;
+  out->enabled = 1;
+  return UNIQL_OK;
+}
+}  // namespace uniql
 
 extern "C" int uniql_allreduce_push(void* comm, const void* in, void* out, int64_t count, int* status_word,
                                     void* stream) {

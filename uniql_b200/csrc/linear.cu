@@ -86,6 +86,7 @@ extern "C" int uniql_w4a16_linear(const void* A, int64_t lda, const void* B, con
   a.partials = (float*)((char*)scratch + L.part_off);
   a.partial_bytes = L.part_bytes;
   a.status_word = status_word;
+  a.ar = nullptr;
 
   const __half* Ain = (const __half*)A;
   const bool decode = !(m > 16 && gemm_tc_supported(m, n, k));
@@ -108,6 +109,36 @@ extern "C" int uniql_w4a16_linear(const void* A, int64_t lda, const void* B, con
     if (st != UNIQL_OK) return st;
   }
   return UNIQL_OK;
+}
+
+extern "C" int uniql_w4a16_linear_allreduce(void* comm, const void* A, int64_t lda, const void* B, const void* s,
+                                            const void* bias, void* D, int64_t ldd, int64_t m, int64_t n,
+                                            int64_t n_out, int64_t k, int groupsize, void* scratch,
+                                            size_t scratch_bytes, int* status_word, void* stream_) {
+  using namespace uniql;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (groupsize != 128) return groupsize == -1 ? UNIQL_EGROUPSIZE : UNIQL_EINVAL;
+  if (!comm || m < 0 || n <= 0 || k <= 0 || n_out <= 0 || n_out > n) return UNIQL_EINVAL;
+  if (m > 16) return UNIQL_ESHAPE;                       // decode sizes only: larger batches reduce separately
+  if (n % 64 != 0 || k % 128 != 0 || n > (int64_t)1 << 22 || k > (int64_t)1 << 22) return UNIQL_ESHAPE;
+  if (lda < k || ldd < n_out || lda % 8 != 0) return UNIQL_EINVAL;
+  if (m == 0) return UNIQL_OK;
+  if (!A || !B || !s || !D) return UNIQL_EINVAL;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(s) || (reinterpret_cast<uintptr_t>(D) & 1u)) return UNIQL_EINVAL;
+  ArFuse ar;
+  int st = comm_fuse_desc(comm, m, n, &ar);
+  if (st != UNIQL_OK) return st;
+  const ScratchLayout L = scratch_layout(m, n, k, 0);
+  if (!scratch || scratch_bytes < L.total || (reinterpret_cast<uintptr_t>(scratch) & 255u)) return UNIQL_ESCRATCH;
+  LinearArgs a;
+  a.B = B; a.s = s; a.bias = bias; a.ldd = ldd; a.n = n; a.n_out = n_out; a.k = k;
+  a.counters = (int*)scratch;
+  a.partials = (float*)((char*)scratch + L.part_off);
+  a.partial_bytes = L.part_bytes;
+  a.status_word = status_word;
+  a.ar = &ar;
+  const GemvPlan plan = plan_gemv(m, n, k);
+  return launch_gemv(a, (const __half*)A, lda, (__half*)D, m, plan, false, stream);
 }
 
 extern "C" int uniql_abi_version(void) { return UNIQL_ABI_VERSION; }

@@ -56,6 +56,7 @@ struct GemvParams {
   float* partials;      // [S_split][M][N]
   int* counters;        // [gridDim.x], zero on entry, zero on exit
   int* status_word;
+  ArFuse ar;            // cross-GPU sum fused into the final store (enabled = 0: plain store)
 };
 
 // ---- mbarrier / TMA helpers ------------------------------------------------------------------------
@@ -136,11 +137,55 @@ __device__ __forceinline__ void gemv_group(const uint8_t* slot_ptr, float (&accg
   }
 }
 
+constexpr int kFuseSpinLimit = 1 << 22;
+
+__device__ __forceinline__ void fuse_st_word(uint2* p, uint32_t data, uint32_t flag) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(flag) : "memory");
+}
+__device__ __forceinline__ uint2 fuse_ld_word(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// Four adjacent columns of one batch row: round this rank's partial to fp16 and store it, tagged with the epoch,
+// into slot `rank` of every rank's staging block (peer stores over NVLink).
+__device__ __forceinline__ void fuse_push(const ArFuse& ar, uint32_t epoch, size_t word, float4 v) {
+  const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+  const uint32_t d0 = *reinterpret_cast<const uint32_t*>(&lo), d1 = *reinterpret_cast<const uint32_t*>(&hi);
+  const size_t slot = ((size_t)(epoch & 1u) * ar.world + ar.rank) * ar.words_per_slot + word;
+  for (int r = 0; r < ar.world; ++r) {
+    uint2* dst = reinterpret_cast<uint2*>(ar.bufs[r] + ar.staging_off) + slot;
+    fuse_st_word(dst, d0, epoch);
+    fuse_st_word(dst + 1, d1, epoch);
+  }
+}
+// Wait (bounded) for the same four columns from every rank in this GPU's own block and add them in rank order.
+__device__ __forceinline__ float4 fuse_gather(const ArFuse& ar, uint32_t epoch, size_t word, bool& fail) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const uint2* base = reinterpret_cast<const uint2*>(ar.bufs[ar.rank] + ar.staging_off) +
+                      (size_t)(epoch & 1u) * ar.world * ar.words_per_slot + word;
+  for (int r = 0; r < ar.world; ++r) {
+    const uint2* src = base + (size_t)r * ar.words_per_slot;
+    uint2 w0 = fuse_ld_word(src), w1 = fuse_ld_word(src + 1);
+    int it = 0;
+    while ((w0.y != epoch || w1.y != epoch) && !fail) {
+      if (++it > kFuseSpinLimit) { fail = true; break; }
+      w0 = fuse_ld_word(src);
+      w1 = fuse_ld_word(src + 1);
+    }
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w0.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w1.x));
+    acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+  }
+  return acc;
+}
+
 template <int MT>
 __global__ void __launch_bounds__(kGemvThreads, MT == 1 ? kCtasMt1 : 2)
 w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ int s_is_last;
+  __shared__ uint32_t s_epoch;
   __shared__ __align__(8) uint64_t s_bars[kGemvWarps * 4];
 
   const int tid = threadIdx.x;
@@ -340,6 +385,29 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
     }
   };
 
+  // Fused cross-GPU sum: the CTA that produces the final values of a column group pushes them to every rank,
+  // then collects the other ranks' values for the same columns.  One epoch counter per column group.
+  const bool fuse = p.ar.enabled != 0;
+  uint32_t* fuse_ctr = fuse ? reinterpret_cast<uint32_t*>(p.ar.bufs[p.ar.rank] + p.ar.epoch_off) + blockIdx.x : nullptr;
+  auto fuse_finish = [&](uint32_t epoch) {
+    bool fail = false;
+    for (int idx = tid; idx < items; idx += kGemvThreads) {
+      const int m = idx >> log_cols4, col = (idx & ((1 << log_cols4) - 1)) * 4;
+      const int n = n_base + col;
+      if (n >= p.n_out) continue;
+      store_out(m, n, fuse_gather(p.ar, epoch, ((size_t)m * p.N + n) >> 1, fail));
+    }
+    if (fail && p.status_word) atomicOr(p.status_word, UNIQL_STATUS_WAIT_TIMEOUT);
+    __syncthreads();
+    if (tid == 0) *fuse_ctr = epoch;
+  };
+  uint32_t epoch = 0;
+  if (fuse && direct) {
+    if (tid == 0) s_epoch = *fuse_ctr + 1;
+    __syncthreads();
+    epoch = s_epoch;
+  }
+
   for (int idx = tid; idx < items; idx += kGemvThreads) {
     const int m = idx >> log_cols4, col = (idx & ((1 << log_cols4) - 1)) * 4;
     const int n = n_base + col;
@@ -350,10 +418,17 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
       const float4 t4 = *reinterpret_cast<const float4*>(red + ((size_t)((k << p.log_wn) + wn_i) * (8 * MT) + m) * kRedStride + nl);
       v.x += t4.x; v.y += t4.y; v.z += t4.z; v.w += t4.w;
     }
-    if (direct) store_out(m, n, v);
-    else *reinterpret_cast<float4*>(p.partials + ((size_t)blockIdx.y * p.M + m) * p.N + n) = v;
+    if (direct) {
+      if (!fuse) store_out(m, n, v);
+      else if (n < p.n_out) fuse_push(p.ar, epoch, ((size_t)m * p.N + n) >> 1, v);
+    } else {
+      *reinterpret_cast<float4*>(p.partials + ((size_t)blockIdx.y * p.M + m) * p.N + n) = v;
+    }
   }
-  if (direct) return;
+  if (direct) {
+    if (fuse) fuse_finish(epoch);
+    return;
+  }
 
   // ---- split-k: the last CTA of this column group to finish adds the partials (fixed order) ----
   __threadfence();
@@ -367,6 +442,11 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
   __syncthreads();
   if (!s_is_last) return;
   __threadfence();
+  if (fuse) {
+    if (tid == 0) s_epoch = *fuse_ctr + 1;
+    __syncthreads();
+    epoch = s_epoch;
+  }
   const size_t slab4 = ((size_t)p.M * p.N) >> 2;
   for (int idx = tid; idx < items; idx += kGemvThreads) {
     const int m = idx >> log_cols4, col = (idx & ((1 << log_cols4) - 1)) * 4;
@@ -382,8 +462,10 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
 #pragma unroll
       for (int i = 0; i < 8; ++i) { v.x += t4[i].x; v.y += t4[i].y; v.z += t4[i].z; v.w += t4[i].w; }
     }
-    store_out(m, n, v);
+    if (!fuse) store_out(m, n, v);
+    else fuse_push(p.ar, epoch, ((size_t)m * p.N + n) >> 1, v);
   }
+  if (fuse) fuse_finish(epoch);
 }
 
 // ------------------------------------------------------------------ host side
@@ -503,6 +585,7 @@ int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, in
   p.R = plan.R; p.xs_rows = plan.xs_rows; p.status_word = a.status_word;
   p.counters = a.counters;
   p.partials = a.partials;
+  if (a.ar) p.ar = *a.ar; else p.ar.enabled = 0;
   if (plan.partial_bytes > a.partial_bytes) return UNIQL_ESCRATCH;
   if ((size_t)grid_x_of(p) * sizeof(int) > UNIQL_SCRATCH_COUNTER_BYTES) return UNIQL_ESHAPE;
   CUtensorMap wmap;
@@ -590,5 +673,6 @@ extern "C" int uniql_w4a16_linear_static(const void* A, int64_t lda, const void*
   a.partials = (float*)((char*)scratch + UNIQL_SCRATCH_COUNTER_BYTES);
   a.partial_bytes = (size_t)UNIQL_STATIC_SCRATCH_BYTES - UNIQL_SCRATCH_COUNTER_BYTES;
   a.status_word = status_word;
+  a.ar = nullptr;
   return launch_gemv(a, (const __half*)A, lda, (__half*)D, m, plan, false, stream);
 }

@@ -57,8 +57,10 @@ _need_cache: dict = {}   # (m, n, k, hadamard_dim) -> scratch bytes
 
 
 def w4a16_linear(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, bias: torch.Tensor | None,
-                 n_out: int, hadamard_dim: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
-    """y[m, n_out] = x[m, k] @ dequant(weight, scale)[:, :n_out] (+ bias); x fp16 2-D, row-major."""
+                 n_out: int, hadamard_dim: int = 0, out: torch.Tensor | None = None, comm=None) -> torch.Tensor:
+    """y[m, n_out] = x[m, k] @ dequant(weight, scale)[:, :n_out] (+ bias); x fp16 2-D, row-major.
+    With `comm` (a communicator handle from uniql_comm_create) the result is summed over the ranks inside the
+    kernel (row-parallel linear, m <= 16)."""
     if not (x.is_cuda and weight.is_cuda and scale.is_cuda):
         raise RuntimeError("x, weight and scale must be CUDA tensors (uniql_b200 has no CPU path)")
     if x.dtype != torch.float16 or x.dim() != 2:
@@ -113,10 +115,16 @@ def w4a16_linear(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, bia
         st = _status.get(idx)
         if st is None:
             st = status_word(dev)
-        code = L.uniql_w4a16_linear(
-            x.data_ptr(), lda, weight.data_ptr(), scale.data_ptr(), bias_ptr,
-            out.data_ptr(), out.stride(0), m, n, n_out, k, groupsize, hadamard_dim,
-            scratch.data_ptr(), scratch.numel(), st.data_ptr(), stream)
+        if comm is not None:
+            code = L.uniql_w4a16_linear_allreduce(
+                comm, x.data_ptr(), lda, weight.data_ptr(), scale.data_ptr(), bias_ptr,
+                out.data_ptr(), out.stride(0), m, n, n_out, k, groupsize,
+                scratch.data_ptr(), scratch.numel(), st.data_ptr(), stream)
+        else:
+            code = L.uniql_w4a16_linear(
+                x.data_ptr(), lda, weight.data_ptr(), scale.data_ptr(), bias_ptr,
+                out.data_ptr(), out.stride(0), m, n, n_out, k, groupsize, hadamard_dim,
+                scratch.data_ptr(), scratch.numel(), st.data_ptr(), stream)
     finally:
         if switch:
             torch.cuda.set_device(prev)

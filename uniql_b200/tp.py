@@ -99,8 +99,11 @@ class ColumnParallelW4A16Linear(nn.Module):
 class RowParallelW4A16Linear(nn.Module):
     """This rank's slice of the input features; partial outputs are summed over the process group."""
 
-    def __init__(self, full: W4A16B16O16Linear, rank: int, world: int, group=None, bounds=None):
+    def __init__(self, full: W4A16B16O16Linear, rank: int, world: int, group=None, bounds=None, fused=None):
+        """fused: a PushAllReduce dedicated to this call-site shape; when given, decode-size calls (m <= 16) do
+        the cross-GPU sum inside the linear kernel instead of a separate collective."""
         super().__init__()
+        self.fused = fused
         bounds = bounds or row_bounds(full.size_k, world)
         k0, k1 = bounds[rank]
         w, s = shard_rows(full.weight, full.scale, k0, k1)
@@ -110,6 +113,12 @@ class RowParallelW4A16Linear(nn.Module):
         self.local = _local_linear(w, s, None, k1 - k0, full.out_features)
 
     def forward(self, x_local):
+        if self.world > 1 and self.fused is not None:
+            x2 = x_local.reshape(-1, x_local.shape[-1])
+            if self.fused.fits_fused(x2.shape[0], self.local.size_n):
+                y = self.fused.linear_all_reduce(x2, self.local.weight, self.local.scale, self.bias,
+                                                 self.local.out_features)
+                return y.view(*x_local.shape[:-1], self.local.out_features)
         y = self.local(x_local)
         if self.world > 1:
             dist.all_reduce(y, group=self.group)
@@ -181,6 +190,15 @@ class PushAllReduce:
         full = torch.zeros((*x_local.shape[:-1], offs[-1]), dtype=x_local.dtype, device=x_local.device)
         full[..., offs[self.rank]:offs[self.rank + 1]] = x_local
         return self.all_reduce(full)
+
+    def fits_fused(self, m: int, n_stored: int) -> bool:
+        return m <= 16 and m * n_stored <= self.max_elems
+
+    def linear_all_reduce(self, x, weight, scale, bias, n_out):
+        """Row-parallel W4A16 linear + sum over ranks in one kernel launch (uniql_w4a16_linear_allreduce).
+        Keep one PushAllReduce per call-site shape: the epochs of its staging area advance per call."""
+        from . import ops
+        return ops.w4a16_linear(x, weight, scale, bias, n_out, comm=self._comm)
 
     def close(self):
         if self._comm:
