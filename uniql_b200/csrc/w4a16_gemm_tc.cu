@@ -5,7 +5,10 @@
 // tile table :802-810), which run mma.sync with dequantisation on the same warps, while consuming the same
 // packed buffers (quantize/quantize_helpers.py:145-165 weight order, :54-62 scale order).
 //
-// Tile: 128 (batch rows) x 256 (output columns) x 64 (k) per pipeline stage, one persistent CTA per SM.
+// Tile: (128 * H) batch rows x 256 output columns x 64 k per pipeline stage, one persistent CTA per SM.  H = 2 for
+// m > 128: the two 128-row halves are separate M=128 MMAs that read the same dequantised weight tile, which halves
+// the dequantisation work and the shared-memory writes per tensor-core cycle; their accumulators are the two 256-column
+// halves of TMEM.  H = 1 (m <= 128) double-buffers one accumulator across tiles instead.
 //   warp 0      TMA producer: activation tile [128 x 64] fp16 (128B-swizzled, K-major) and the packed weight
 //               tile [4 packed rows x 512 words] (two boxes of 256 words); no multicast.
 //   warp 1      allocates TMEM (2 x 256 fp32 columns), issues tcgen05.mma kind::f16 (M=128, N=256, K=16) from one
@@ -25,22 +28,27 @@
 namespace uniql {
 
 namespace tc {
-constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int AB_STAGES = 4, P_STAGES = 3;
-constexpr int A_BYTES = BM * BK * 2;          // 16 KB
+constexpr int BMH = 128, BN = 256, BK = 64;   // BMH: rows of one MMA (one "half")
+constexpr int A_BYTES = BMH * BK * 2;         // 16 KB per half
 constexpr int B_BYTES = BN * BK * 2;          // 32 KB
 constexpr int P_BYTES = (BK / 16) * (2 * BN) * 4;   // 8 KB: 4 packed rows x 512 words
-constexpr int OFF_A = 0;
-constexpr int OFF_B = OFF_A + AB_STAGES * A_BYTES;
-constexpr int OFF_P = OFF_B + AB_STAGES * B_BYTES;
-constexpr int OFF_BAR = OFF_P + P_STAGES * P_BYTES;
-constexpr int NUM_BARS = 3 * AB_STAGES + 2 * P_STAGES + 4;
-constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;   // + slack to align the base to 1 KB
+constexpr int P_STAGES = 3;
 constexpr int DEQ_WARPS = 16;
-constexpr int THREADS = (6 + DEQ_WARPS) * 32;
 constexpr int TMEM_COLS = 512;
+template <int H> struct Cfg {
+  static constexpr int AB_STAGES = H == 1 ? 4 : 3;
+  static constexpr int STAGE_A = H * A_BYTES;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + AB_STAGES * STAGE_A;
+  static constexpr int OFF_P = OFF_B + AB_STAGES * B_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_STAGES * P_BYTES;
+  static constexpr int NUM_BARS = 3 * AB_STAGES + 2 * P_STAGES + 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;   // + slack to align the base to 1 KB
+  static constexpr int EPI_WARPS = 4 * H;
+  static constexpr int THREADS = (2 + EPI_WARPS + DEQ_WARPS) * 32;
+};
 // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128
-constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BMH >> 4) << 24);
 #ifndef UNIQL_TC_WAIT_POLLS
 #define UNIQL_TC_WAIT_POLLS (1 << 22)
 #endif
@@ -145,10 +153,14 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(tc::THREADS, 1)
+template <int H>
+__global__ void __launch_bounds__(tc::Cfg<H>::THREADS, 1)
 w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
                      const __grid_constant__ CUtensorMap wmap) {
   using namespace tc;
+  constexpr int AB_STAGES = Cfg<H>::AB_STAGES, STAGE_A = Cfg<H>::STAGE_A;
+  constexpr int OFF_A = Cfg<H>::OFF_A, OFF_B = Cfg<H>::OFF_B, OFF_P = Cfg<H>::OFF_P, OFF_BAR = Cfg<H>::OFF_BAR;
+  constexpr int NUM_BARS = Cfg<H>::NUM_BARS, EPI_WARPS = Cfg<H>::EPI_WARPS;
   extern __shared__ uint8_t smem_unaligned[];
   // 1 KB alignment: the 128B-swizzled tiles must start on a swizzle-atom boundary
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
@@ -209,8 +221,11 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
                     bar_full_p + 8 * sp);
           const int s = it_ab % AB_STAGES;
           if (!timed_out && !tc_mbar_wait(bar_empty_ab + 8 * s, ((it_ab / AB_STAGES) & 1) ^ 1)) timed_out = true;
-          tc_mbar_expect_tx(bar_full_a + 8 * s, A_BYTES);
-          tc_tma_2d(sbase + OFF_A + s * A_BYTES, &amap, kb * BK, mt * BM, bar_full_a + 8 * s);
+          tc_mbar_expect_tx(bar_full_a + 8 * s, STAGE_A);
+#pragma unroll
+          for (int h = 0; h < H; ++h)
+            tc_tma_2d(sbase + OFF_A + s * STAGE_A + h * A_BYTES, &amap, kb * BK, (mt * H + h) * BMH,
+                      bar_full_a + 8 * s);
         }
       }
     }
@@ -219,37 +234,48 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
     if (lane == 0) {
       int it_ab = 0, it_tile = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it_tile) {
-        const int buf = it_tile & 1;
-        if (!timed_out && !tc_mbar_wait(bar_tmem_empty + 8 * buf, ((it_tile >> 1) & 1) ^ 1)) timed_out = true;
+        // H == 1: one accumulator per tile, alternating between the two TMEM halves (epilogue of tile t overlaps
+        // the main loop of tile t+1).  H == 2: both halves belong to this tile.
+        const int buf0 = H == 1 ? (it_tile & 1) : 0;
+        const uint32_t empty_parity = (H == 1 ? ((it_tile >> 1) & 1) : (it_tile & 1)) ^ 1;
+#pragma unroll
+        for (int h = 0; h < H; ++h)
+          if (!timed_out && !tc_mbar_wait(bar_tmem_empty + 8 * (buf0 + h), empty_parity)) timed_out = true;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * BN;
         for (int kb = 0; kb < KB; ++kb, ++it_ab) {
           const int s = it_ab % AB_STAGES;
           const uint32_t ph = (it_ab / AB_STAGES) & 1;
           if (!timed_out && !tc_mbar_wait(bar_full_a + 8 * s, ph)) timed_out = true;
           if (!timed_out && !tc_mbar_wait(bar_full_b + 8 * s, ph)) timed_out = true;
           tc_fence_after();
-          const uint64_t adesc = tc_smem_desc(sbase + OFF_A + s * A_BYTES);
           const uint64_t bdesc = tc_smem_desc(sbase + OFF_B + s * B_BYTES);
 #pragma unroll
-          for (int k4 = 0; k4 < BK / 16; ++k4)
-            tc_mma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
+          for (int h = 0; h < H; ++h) {
+            const uint64_t adesc = tc_smem_desc(sbase + OFF_A + s * STAGE_A + h * A_BYTES);
+            const uint32_t tmem_d = tmem_base + (buf0 + h) * BN;
+#pragma unroll
+            for (int k4 = 0; k4 < BK / 16; ++k4)
+              tc_mma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
+          }
           tc_commit(bar_empty_ab + 8 * s);      // stage reusable once these MMAs have read it
         }
-        tc_commit(bar_tmem_full + 8 * buf);     // accumulator complete
+#pragma unroll
+        for (int h = 0; h < H; ++h) tc_commit(bar_tmem_full + 8 * (buf0 + h));   // accumulators complete
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + EPI_WARPS) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;                     // TMEM lane quadrant this warp may access
+    const int half = (warp - 2) >> 2;           // which 128-row half of the tile (always 0 when H == 1)
     int it_tile = 0;
     const bool vec_ok = ((p.ldd & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it_tile) {
       const int mt = tile % p.mtiles, nt = tile / p.mtiles;
-      const int buf = it_tile & 1;
-      if (!timed_out && !tc_mbar_wait_relaxed(bar_tmem_full + 8 * buf, (it_tile >> 1) & 1)) timed_out = true;
+      const int buf = H == 1 ? (it_tile & 1) : half;
+      const uint32_t full_parity = H == 1 ? ((it_tile >> 1) & 1) : (it_tile & 1);
+      if (!timed_out && !tc_mbar_wait_relaxed(bar_tmem_full + 8 * buf, full_parity)) timed_out = true;
       tc_fence_after();
-      const int m = mt * BM + q * 32 + lane;
+      const int m = (mt * H + half) * BMH + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
       __half* drow = p.D + (size_t)m * p.ldd;
 #pragma unroll 1
@@ -291,7 +317,7 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
     }
   } else {
     // ------------------------------------------------------------------ dequantise
-    const int dw = warp - 6;
+    const int dw = warp - 2 - EPI_WARPS;
     const int blk_local = dw & 3;               // 64-column block of the 256-column tile
     const int kt = dw >> 2;                     // packed row of the stage this warp converts -> k = 16 kt .. 16 kt + 15
     const int g = lane >> 2, c = lane & 3;
@@ -399,7 +425,7 @@ int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D,
   {
     cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)m};
     cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BMH};
     cuuint32_t estr[2] = {1, 1};
     if (enc(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(A), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -419,18 +445,27 @@ int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D,
   TcParams p;
   p.S = (const uint4*)a.s; p.bias = (const __half*)a.bias; p.D = D; p.ldd = a.ldd;
   p.M = (int)m; p.N = (int)a.n; p.n_out = (int)a.n_out; p.K = (int)a.k;
-  p.mtiles = (int)((m + BM - 1) / BM);
+  // 256-row tiles share each dequantised weight tile between two MMAs; use them once they still fill the GPU
   p.ntiles = (int)((a.n + BN - 1) / BN);
+  const int sms_ = device_info().sm_count;
+  const int H = (m > BMH && ((m + 2 * BMH - 1) / (2 * BMH)) * (int64_t)p.ntiles >= sms_) ? 2 : 1;
+  p.mtiles = (int)((m + H * BMH - 1) / (H * BMH));
   p.status_word = a.status_word;
   static thread_local bool attr_set = false;
   if (!attr_set) {
-    UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg<1>::SMEM_BYTES));
+    UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg<2>::SMEM_BYTES));
     attr_set = true;
   }
   const int64_t tiles = (int64_t)p.mtiles * p.ntiles;
   const int sms = device_info().sm_count;
   const int grid = (int)(tiles < sms ? tiles : sms);
-  w4a16_gemm_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p, amap, wmap);
+  if (H == 1)
+    w4a16_gemm_tc_kernel<1><<<grid, Cfg<1>::THREADS, Cfg<1>::SMEM_BYTES, stream>>>(p, amap, wmap);
+  else
+    w4a16_gemm_tc_kernel<2><<<grid, Cfg<2>::THREADS, Cfg<2>::SMEM_BYTES, stream>>>(p, amap, wmap);
   return launch_status();
 }
 
