@@ -32,6 +32,7 @@ struct LinearArgs {
 
 struct GemvPlan {
   int WN, WK, S, GCH, MT, R, xs_rows;
+  int cluster, ctile_off;
   size_t smem;
   size_t partial_bytes;
 };

@@ -57,6 +57,8 @@ struct GemvParams {
   int* counters;        // [gridDim.x], zero on entry, zero on exit
   int* status_word;
   ArFuse ar;            // cross-GPU sum fused into the final store (enabled = 0: plain store)
+  int cluster;          // 1: the S_split CTAs of a column group form a thread-block cluster and reduce through DSMEM
+  int ctile_off;        // byte offset of this CTA's reduced tile in shared memory (cluster mode)
 };
 
 // One quantisation group (8 packed rows) of one 64-column block, read from this warp's ring slot.
@@ -91,6 +93,22 @@ __device__ __forceinline__ void gemv_group(const uint8_t* slot_ptr, float (&accg
       }
     }
   }
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 16 bytes from the shared memory of CTA `rank` of this cluster (distributed shared memory)
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
 }
 
 constexpr int kFuseSpinLimit = 1 << 22;
@@ -357,6 +375,57 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
     __syncthreads();
     if (tid == 0) *fuse_ctr = epoch;
   };
+  // ---- split-k inside a thread-block cluster: partial tiles stay in shared memory, every CTA of the cluster adds
+  // up one slice of the tile by reading its peers' shared memory in rank order (no global scratch, no ticket) ----
+  if (p.cluster && !direct) {
+    float* ctile = reinterpret_cast<float*>(smem_raw + p.ctile_off);
+    const int cta_cols = p.WN * 64;
+    for (int idx = tid; idx < items; idx += kGemvThreads) {
+      const int m = idx >> log_cols4, col = (idx & ((1 << log_cols4) - 1)) * 4;
+      const int wn_i = col >> 6, nl = col & 63;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < p.WK; ++k) {
+        const float4 t4 = *reinterpret_cast<const float4*>(red + ((size_t)((k << p.log_wn) + wn_i) * (8 * MT) + m) * kRedStride + nl);
+        v.x += t4.x; v.y += t4.y; v.z += t4.z; v.w += t4.w;
+      }
+      *reinterpret_cast<float4*>(ctile + (size_t)m * cta_cols + col) = v;
+    }
+    uint32_t cepoch = 0;
+    if (fuse) {
+      if (tid == 0) s_epoch = *fuse_ctr + 1;      // nobody advances the counter before the final cluster barrier
+    }
+    cluster_sync_all();
+    if (fuse) cepoch = s_epoch;
+    const int rank = blockIdx.y;                  // cluster = the S_split CTAs with the same blockIdx.x
+    const int i0 = (int)((int64_t)items * rank / p.S_split), i1 = (int)((int64_t)items * (rank + 1) / p.S_split);
+    const uint32_t ctile_addr = smem_addr(ctile);
+    for (int idx = i0 + tid; idx < i1; idx += kGemvThreads) {
+      const int m = idx >> log_cols4, col = (idx & ((1 << log_cols4) - 1)) * 4;
+      const int n = n_base + col;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      const uint32_t off = ctile_addr + (uint32_t)((m * cta_cols + col) * 4);
+      for (int r = 0; r < p.S_split; ++r) {
+        const float4 t4 = ld_dsmem_f4(off, (uint32_t)r);
+        v.x += t4.x; v.y += t4.y; v.z += t4.z; v.w += t4.w;
+      }
+      if (!fuse) store_out(m, n, v);
+      else if (n < p.n_out) fuse_push(p.ar, cepoch, ((size_t)m * p.N + n) >> 1, v);
+    }
+    if (fuse) {
+      bool fail = false;
+      for (int idx = i0 + tid; idx < i1; idx += kGemvThreads) {
+        const int m = idx >> log_cols4, col = (idx & ((1 << log_cols4) - 1)) * 4;
+        const int n = n_base + col;
+        if (n >= p.n_out) continue;
+        store_out(m, n, fuse_gather(p.ar, cepoch, ((size_t)m * p.N + n) >> 1, fail));
+      }
+      if (fail && p.status_word) atomicOr(p.status_word, UNIQL_STATUS_WAIT_TIMEOUT);
+    }
+    cluster_sync_all();                           // peers may still be reading this CTA's tile
+    if (fuse && rank == 0 && tid == 0) *fuse_ctr = cepoch;
+    return;
+  }
+
   uint32_t epoch = 0;
   if (fuse && direct) {
     if (tid == 0) s_epoch = *fuse_ctr + 1;
@@ -514,7 +583,15 @@ GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k) {
   const size_t xs_bytes = (size_t)best.WK * rows * (gch * 128 + kXsPad) * 2;
   const size_t red_bytes = (size_t)kGemvWarps * 8 * MT * kRedStride * 4;
   best.smem = ring_bytes + xs_bytes > red_bytes ? ring_bytes + xs_bytes : red_bytes;
-  best.partial_bytes = best.S > 1 ? (size_t)best.S * (size_t)(m < 16 ? m : 16) * n * 4 : 0;
+  // cluster mode (2 <= S <= 8): the CTA's reduced tile lives behind the warp reduction buffer
+  static const int cluster_on = env_int("UNIQL_B200_CLUSTER", 1);
+  best.cluster = (cluster_on && best.S >= 2 && best.S <= 8) ? 1 : 0;
+  best.ctile_off = (int)((red_bytes + 1023) / 1024 * 1024);
+  if (best.cluster) {
+    const size_t need = (size_t)best.ctile_off + (size_t)(m < 16 ? m : 16) * best.WN * 64 * 4;
+    if (best.smem < need) best.smem = need;
+  }
+  best.partial_bytes = (best.S > 1 && !best.cluster) ? (size_t)best.S * (size_t)(m < 16 ? m : 16) * n * 4 : 0;
   return best;
 }
 
@@ -535,6 +612,7 @@ int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, in
   p.counters = a.counters;
   p.partials = a.partials;
   if (a.ar) p.ar = *a.ar; else p.ar.enabled = 0;
+  p.cluster = plan.cluster; p.ctile_off = plan.ctile_off;
   if (plan.partial_bytes > a.partial_bytes) return UNIQL_ESCRATCH;
   if ((size_t)grid_x_of(p) * sizeof(int) > UNIQL_SCRATCH_COUNTER_BYTES) return UNIQL_ESHAPE;
   CUtensorMap wmap;
@@ -553,14 +631,25 @@ int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, in
   cfg.blockDim = dim3(kGemvThreads);
   cfg.dynamicSmemBytes = plan.smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int nattr = 0;
   // Every launch may start early behind its predecessor; the kernel itself waits (griddepcontrol.wait)
   // before it touches anything another kernel could have written.
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
   static const int pdl_on = env_int("UNIQL_B200_PDL", 1);
-  cfg.numAttrs = pdl_on ? 1 : 0;
+  if (pdl_on) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  if (plan.cluster) {
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = 1;
+    attr[nattr].val.clusterDim.y = (unsigned)plan.S;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
   UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, wmap));
   return UNIQL_OK;
 }
