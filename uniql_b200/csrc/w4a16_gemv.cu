@@ -62,17 +62,60 @@ struct GemvParams {
 };
 
 // One quantisation group (8 packed rows) of one 64-column block, read from this warp's ring slot.
-// Nibbles are turned into fp16 values (1024 + q) and (64 + q) by a single LOP3 each; the offsets are taken
-// out again through `corr`, an extra MMA whose 16-row operand is the constant (1032 | 72):
+// Nibbles are turned into fp16 values (1024 + q) and (64 + q) by a single LOP3 each; the offsets are taken out again
+// by starting the group's accumulators at  -sum_k (off_k + 8) x_k  (off_k = 1024 for k % 16 < 8, else 64):
 //   sum_k (off_k + q) x  -  sum_k (off_k + 8) x  =  sum_k (q - 8) x.
-// Activations are staged so that a lane's (b0, b1) fragment of packed row u is 8 contiguous bytes at xaddr + 32u.
-template <int MT, bool CHECK>
-__device__ __forceinline__ void gemv_group(const uint8_t* slot_ptr, float (&accg)[MT][4][4], float (&corr)[MT][4],
-                                           const uint8_t* xptr, uint32_t x_tile_stride, int kt_base, int w0, int w1) {
-  const uint32_t kcorr[4] = {0x64086408u, 0x64086408u, 0x54805480u, 0x54805480u};   // 1032, 1032, 72, 72
+// That starting value depends only on the activations; it is computed once per group when they are staged (ncorr).
+// Activations are staged so that a lane's (b0, b1) fragment of packed row u is 8 contiguous bytes at xptr + 32u.
+template <int MT>
+__device__ __forceinline__ void gemv_group_full(const uint8_t* slot_ptr, float (&accg)[MT][4][4], const uint8_t* xptr,
+                                                uint32_t x_tile_stride, const float* ncorr_lane) {
+  float2 nc[MT];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) nc[t] = *reinterpret_cast<const float2*>(ncorr_lane + 8 * t);
 #pragma unroll
   for (int u = 0; u < 8; ++u) {
-    if (!CHECK || (kt_base + u >= w0 && kt_base + u < w1)) {
+    const uint4 w4 = *reinterpret_cast<const uint4*>(slot_ptr + u * 512);
+    uint2 b[MT];
+#pragma unroll
+    for (int t = 0; t < MT; ++t) b[t] = *reinterpret_cast<const uint2*>(xptr + t * x_tile_stride + u * 32);
+    const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t a[4];
+      const uint32_t q = wq[j], qs = wq[j] >> 8;
+      a[0] = lop3_and_or(q, 0x000f000fu, 0x64006400u);     // n = 16j+g,   k = 2c, 2c+1    : 1024 + q
+      a[2] = lop3_and_or(q, 0x00f000f0u, 0x54005400u);     // n = 16j+g,   k = 2c+8, 2c+9  :   64 + q
+      a[1] = lop3_and_or(qs, 0x000f000fu, 0x64006400u);    // n = 16j+g+8, k = 2c, 2c+1
+      a[3] = lop3_and_or(qs, 0x00f000f0u, 0x54005400u);    // n = 16j+g+8, k = 2c+8, 2c+9
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        if (u == 0) mma_m16n8k16_init(accg[t][j], a, b[t].x, b[t].y, nc[t].x, nc[t].y);
+        else mma_m16n8k16(accg[t][j], a, b[t].x, b[t].y);
+      }
+    }
+  }
+}
+
+// Same for a group that is only partly inside the warp's k-range [w0, w1): rows are predicated and the offset term
+// is accumulated for the rows actually used, with an MMA whose 16-row operand is the constant (1032 | 72).
+template <int MT>
+__device__ __forceinline__ void gemv_group_partial(const uint8_t* slot_ptr, float (&accg)[MT][4][4], const uint8_t* xptr,
+                                                   uint32_t x_tile_stride, int kt_base, int w0, int w1) {
+  const uint32_t kcorr[4] = {0x64086408u, 0x64086408u, 0x54805480u, 0x54805480u};   // 1032, 1032, 72, 72
+  float corr[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) corr[t][r] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) accg[t][j][r] = 0.f;
+  }
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    if (kt_base + u >= w0 && kt_base + u < w1) {
       const uint4 w4 = *reinterpret_cast<const uint4*>(slot_ptr + u * 512);
       uint2 b[MT];
 #pragma unroll
@@ -84,15 +127,21 @@ __device__ __forceinline__ void gemv_group(const uint8_t* slot_ptr, float (&accg
       for (int j = 0; j < 4; ++j) {
         uint32_t a[4];
         const uint32_t q = wq[j], qs = wq[j] >> 8;
-        a[0] = lop3_and_or(q, 0x000f000fu, 0x64006400u);     // n = 16j+g,   k = 2c, 2c+1    : 1024 + q
-        a[2] = lop3_and_or(q, 0x00f000f0u, 0x54005400u);     // n = 16j+g,   k = 2c+8, 2c+9  :   64 + q
-        a[1] = lop3_and_or(qs, 0x000f000fu, 0x64006400u);    // n = 16j+g+8, k = 2c, 2c+1
-        a[3] = lop3_and_or(qs, 0x00f000f0u, 0x54005400u);    // n = 16j+g+8, k = 2c+8, 2c+9
+        a[0] = lop3_and_or(q, 0x000f000fu, 0x64006400u);
+        a[2] = lop3_and_or(q, 0x00f000f0u, 0x54005400u);
+        a[1] = lop3_and_or(qs, 0x000f000fu, 0x64006400u);
+        a[3] = lop3_and_or(qs, 0x00f000f0u, 0x54005400u);
 #pragma unroll
         for (int t = 0; t < MT; ++t) mma_m16n8k16(accg[t][j], a, b[t].x, b[t].y);
       }
     }
   }
+#pragma unroll
+  for (int t = 0; t < MT; ++t)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) accg[t][j][r] -= corr[t][r];
 }
 
 __device__ __forceinline__ void cluster_sync_all() {
@@ -170,10 +219,11 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
   const bool active = blk < p.nblk;
 
   // k-range of this CTA, then of this warp row (contiguous, balanced to one packed row).
-  const int cta_k0 = (int)((int64_t)p.KT * blockIdx.y / p.S_split);
-  const int cta_k1 = (int)((int64_t)p.KT * (blockIdx.y + 1) / p.S_split);
-  const int rw0 = cta_k0 + (cta_k1 - cta_k0) * wk / p.WK;
-  const int rw1 = cta_k0 + (cta_k1 - cta_k0) * (wk + 1) / p.WK;
+  const unsigned ukt = (unsigned)p.KT, us = (unsigned)p.S_split, uwk = (unsigned)p.WK;   // KT * S_split < 2^31
+  const int cta_k0 = (int)(ukt * blockIdx.y / us);
+  const int cta_k1 = (int)(ukt * (blockIdx.y + 1) / us);
+  const int rw0 = cta_k0 + (int)((unsigned)(cta_k1 - cta_k0) * (unsigned)wk / uwk);
+  const int rw1 = cta_k0 + (int)((unsigned)(cta_k1 - cta_k0) * (unsigned)(wk + 1) / uwk);
   const int g0 = rw0 >> 3, g1 = (rw1 + 7) >> 3;   // quantisation groups touched (8 packed rows each)
   const int w0 = active ? rw0 : 0, w1 = active ? rw1 : 0;   // empty range for warps past the last block
   const bool has_work = w0 < w1;
@@ -183,6 +233,8 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
   const uint32_t bar0 = smem_addr(&s_bars[warp * 4]);
   __half* xs_all = reinterpret_cast<__half*>(smem_raw + (size_t)kGemvWarps * p.R * kSlotBytes);
   __half* xs = xs_all + (size_t)wk * p.xs_rows * p.xs_stride;
+  // per warp row: -(offset term) of every staged group and batch row, [GCH][16] floats (rows >= M stay zero)
+  float* ncorr = reinterpret_cast<float*>(xs_all + (size_t)p.WK * p.xs_rows * p.xs_stride) + (size_t)wk * p.GCH * 16;
 
   const uint64_t pol = make_evict_first_policy();
   const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
@@ -213,6 +265,7 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
   // the extra row is read by MMA lanes whose batch row does not exist: clear it once
   for (int v = row_tid; v < p.xs_stride / 8; v += row_threads)
     *reinterpret_cast<uint4*>(xs + (size_t)m_staged * p.xs_stride + v * 8) = make_uint4(0, 0, 0, 0);
+  for (int v = row_tid; v < p.GCH * 16; v += row_threads) ncorr[v] = 0.f;
   // this lane's B-fragment origin for batch tile 0 and the distance to tile 1 (bytes)
   const int row_t0 = min(g, m_staged), row_t1 = min(8 + g, m_staged);
   const uint8_t* xl = reinterpret_cast<const uint8_t*>(xs) + (size_t)row_t0 * p.xs_stride * 2 + c * 8;
@@ -237,24 +290,48 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
       const int blocks_per_row = (min(gi + p.GCH, g1) - gi) * 8;   // 16-value blocks per row
       const __half* src = p.A + (size_t)gi * 128;
-      for (int v = row_tid; v < blocks_per_row; v += row_threads) {
+      // every lane takes part in the shuffles below: warp-uniform trip count, out-of-range blocks contribute zero
+      for (int v0 = 0; v0 < blocks_per_row; v0 += row_threads) {
+        const int v = v0 + row_tid;
+        const bool vin = v < blocks_per_row;
         constexpr int RB = MT == 1 ? 2 : 4;   // rows loaded together (independent requests in flight)
         for (int r0 = 0; r0 < m_staged; r0 += RB) {
           uint4 lo[RB], hi[RB];
 #pragma unroll
-          for (int i = 0; i < RB; ++i)
-            if (r0 + i < m_staged) {
+          for (int i = 0; i < RB; ++i) {
+            lo[i] = make_uint4(0, 0, 0, 0);
+            hi[i] = make_uint4(0, 0, 0, 0);
+            if (vin && r0 + i < m_staged) {
               const __half* s16 = src + (size_t)(r0 + i) * p.lda + v * 16;
               lo[i] = ld_nc16(s16);
               hi[i] = ld_nc16(s16 + 8);
             }
+          }
 #pragma unroll
-          for (int i = 0; i < RB; ++i)
-            if (r0 + i < m_staged) {
+          for (int i = 0; i < RB; ++i) {
+            if (vin && r0 + i < m_staged) {
               uint4* d = reinterpret_cast<uint4*>(xs + (size_t)(r0 + i) * p.xs_stride + v * 16);
               d[0] = make_uint4(lo[i].x, hi[i].x, lo[i].y, hi[i].y);
               d[1] = make_uint4(lo[i].z, hi[i].z, lo[i].w, hi[i].w);
             }
+            if (MT != 1) continue;   // two batch tiles: the offset term comes from an MMA instead (gemv_group_partial)
+            // offset term of this 16-value block: 1032 * (sum of k % 16 < 8) + 72 * (sum of k % 16 >= 8)
+            const __half2* hl = reinterpret_cast<const __half2*>(&lo[i]);
+            const __half2* hh = reinterpret_cast<const __half2*>(&hi[i]);
+            float sl = 0.f, sh = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 fl = __half22float2(hl[e]), fh = __half22float2(hh[e]);
+              sl += fl.x + fl.y;
+              sh += fh.x + fh.y;
+            }
+            float part = 1032.f * sl + 72.f * sh;
+            // the 8 blocks of a group sit in 8 consecutive lanes: fixed-order butterfly sum
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            part += __shfl_xor_sync(0xffffffffu, part, 4);
+            if (vin && (lane & 7) == 0 && r0 + i < m_staged) ncorr[(v >> 3) * 16 + r0 + i] = -part;
+          }
         }
       }
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
@@ -263,24 +340,16 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
       // this group's 8 scales; the load is covered by the group's MMAs
       const uint4 s_cur = ld_nc16(sptr + (size_t)(gi - g0) * srow_u4);
 
-      float accg[MT][4][4], corr[MT][4];
-#pragma unroll
-      for (int t = 0; t < MT; ++t) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r) corr[t][r] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int r = 0; r < 4; ++r) accg[t][j][r] = 0.f;
-      }
-
+      float accg[MT][4][4];
       if (!mbar_wait(bar0 + slot * 8, parity)) timed_out = true;
       const uint8_t* slot_addr = smem_raw + (size_t)(warp * p.R + slot) * kSlotBytes + lane * 16;
       const uint8_t* xg = xl + chunk_pos * 256;
-      if (8 * gi >= w0 && 8 * gi + 8 <= w1)
-        gemv_group<MT, false>(slot_addr, accg, corr, xg, x_tile_stride, 8 * gi, w0, w1);
+      // m <= 8: the offset term was computed while staging; m > 8: staging 16 rows is already the longer part of
+      // the prologue, so the offset term rides on the tensor pipe there
+      if (MT == 1 && 8 * gi >= w0 && 8 * gi + 8 <= w1)
+        gemv_group_full<MT>(slot_addr, accg, xg, x_tile_stride, ncorr + chunk_pos * 16 + 2 * c);
       else
-        gemv_group<MT, true>(slot_addr, accg, corr, xg, x_tile_stride, 8 * gi, w0, w1);
+        gemv_group_partial<MT>(slot_addr, accg, xg, x_tile_stride, 8 * gi, w0, w1);
       // the slot has been read by every lane: hand it back to the copy engine
       __syncwarp();
       if (lane == 0 && gi + p.R < g1) {
@@ -295,10 +364,10 @@ w4a16_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap wmap) 
         const float2 sf = __half22float2(sh[j]);   // .x -> columns 16j+g, .y -> 16j+g+8
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
-          acc[t][j][0] = fmaf(accg[t][j][0] - corr[t][0], sf.x, acc[t][j][0]);
-          acc[t][j][1] = fmaf(accg[t][j][1] - corr[t][1], sf.x, acc[t][j][1]);
-          acc[t][j][2] = fmaf(accg[t][j][2] - corr[t][2], sf.y, acc[t][j][2]);
-          acc[t][j][3] = fmaf(accg[t][j][3] - corr[t][3], sf.y, acc[t][j][3]);
+          acc[t][j][0] = fmaf(accg[t][j][0], sf.x, acc[t][j][0]);
+          acc[t][j][1] = fmaf(accg[t][j][1], sf.x, acc[t][j][1]);
+          acc[t][j][2] = fmaf(accg[t][j][2], sf.y, acc[t][j][2]);
+          acc[t][j][3] = fmaf(accg[t][j][3], sf.y, acc[t][j][3]);
         }
       }
     }
@@ -564,23 +633,26 @@ GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k) {
   // = WK warp rows x (rows + 1) x (GCH*128 + pad) halves.  Budget: 3 CTAs per SM for m <= 8, else 2.
   const int rows = (int)(m < 8 * MT ? m : 8 * MT) + 1;
   const size_t budget = (MT == 1 && kCtasMt1 == 3 ? 74 : 110) * 1024;
-  const size_t xs_min = (size_t)best.WK * rows * (128 + kXsPad) * 2;
+  const size_t xs_min = (size_t)best.WK * rows * (128 + kXsPad) * 2 + (size_t)best.WK * 8 * 64;
   int R = (int)((budget - xs_min) / (kGemvWarps * kSlotBytes));
-  if (R > 3) R = 3;
+  // two slots per warp measured faster than three for m <= 8 (39.1 vs 41.6 us per Llama-3.1-8B layer)
+  const int r_max = MT == 1 ? 2 : 3;
+  if (R > r_max) R = r_max;
   if (R < 1) R = 1;
   const int ov_r = env_int("UNIQL_B200_GEMV_R", 0);
   if (ov_r >= 1 && ov_r <= 4) R = ov_r;
   const size_t ring_bytes = (size_t)kGemvWarps * R * kSlotBytes;
   const size_t left = budget > ring_bytes ? budget - ring_bytes : 0;
-  int gch = (int)(left / ((size_t)best.WK * rows * 2)) - kXsPad;
-  gch = gch > 0 ? gch / 128 : 0;
+  // per group and warp row: rows * 128 halves of activations + 16 floats of offset terms
+  int gch = (int)((left > (size_t)best.WK * rows * 2 * kXsPad ? left - (size_t)best.WK * rows * 2 * kXsPad : 0) /
+                  ((size_t)best.WK * (rows * 256 + 64)));
   if (gch < 1) gch = 1;
   if (gch > 8) gch = 8;
   best.GCH = gch;
   best.MT = MT;
   best.R = R;
   best.xs_rows = rows;
-  const size_t xs_bytes = (size_t)best.WK * rows * (gch * 128 + kXsPad) * 2;
+  const size_t xs_bytes = (size_t)best.WK * rows * (gch * 128 + kXsPad) * 2 + (size_t)best.WK * gch * 64;
   const size_t red_bytes = (size_t)kGemvWarps * 8 * MT * kRedStride * 4;
   best.smem = ring_bytes + xs_bytes > red_bytes ? ring_bytes + xs_bytes : red_bytes;
   // cluster mode (2 <= S <= 8): the CTA's reduced tile lives behind the warp reduction buffer
