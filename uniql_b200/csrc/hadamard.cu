@@ -97,11 +97,13 @@ int hadamard_base_of(int64_t dim) {
 // ------------------------------------------------------------- element access
 template <typename T> struct Elem;
 template <> struct Elem<__half> {
-  static __device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
-    uint4 r = *reinterpret_cast<const uint4*>(p);
+  static __device__ __forceinline__ void unpack8(const uint4& r, float (&v)[8]) {
     const __half2* h = reinterpret_cast<const __half2*>(&r);
 #pragma unroll
     for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+    unpack8(*reinterpret_cast<const uint4*>(p), v);
   }
   static __device__ __forceinline__ void store8(__half* p, const float (&v)[8]) {
     uint4 r;
@@ -113,11 +115,13 @@ template <> struct Elem<__half> {
   static __device__ __forceinline__ void store1(__half* p, float v) { *p = __float2half_rn(v); }
 };
 template <> struct Elem<__nv_bfloat16> {
-  static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
-    uint4 r = *reinterpret_cast<const uint4*>(p);
+  static __device__ __forceinline__ void unpack8(const uint4& r, float (&v)[8]) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
     for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    unpack8(*reinterpret_cast<const uint4*>(p), v);
   }
   static __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
     uint4 r;
@@ -129,6 +133,7 @@ template <> struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ void store1(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 };
 template <> struct Elem<float> {
+  static __device__ __forceinline__ void unpack8(const uint4&, float (&)[8]) {}   // 16-bit types only
   static __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
     float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
@@ -279,18 +284,35 @@ __global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict
   float v[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = 0.f;
-  for (int a0 = 0; a0 < B; a0 += 4) {          // four independent 16/32-byte loads in flight
-    float t[4][8];
+  // The B segment loads are independent; they are issued 16 at a time (raw 16-byte vectors for 16-bit types)
+  // so that a row costs two memory round trips instead of one per segment.
+  constexpr int kBatch = 16;
+  for (int a0 = 0; a0 < B; a0 += kBatch) {
+    if constexpr (sizeof(T) == 2) {
+      uint4 raw[kBatch];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      if (a0 + i < B) Elem<T>::load8(xr + (size_t)(a0 + i) * P + tid * 8, t[i]);
+      for (int i = 0; i < kBatch; ++i)
+        if (a0 + i < B) raw[i] = *reinterpret_cast<const uint4*>(xr + (size_t)(a0 + i) * P + tid * 8);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      if (a0 + i < B) {
-        const float sg = ((mask >> (a0 + i)) & 1ull) ? -1.f : 1.f;
+      for (int i = 0; i < kBatch; ++i)
+        if (a0 + i < B) {
+          float t[8];
+          Elem<T>::unpack8(raw[i], t);
+          const float sg = ((mask >> (a0 + i)) & 1ull) ? -1.f : 1.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = fmaf(sg, t[i][e], v[e]);
-      }
+          for (int e = 0; e < 8; ++e) v[e] = fmaf(sg, t[e], v[e]);
+        }
+    } else {
+#pragma unroll 4
+      for (int i = 0; i < kBatch; ++i)
+        if (a0 + i < B) {
+          float t[8];
+          Elem<T>::load8(xr + (size_t)(a0 + i) * P + tid * 8, t);
+          const float sg = ((mask >> (a0 + i)) & 1ull) ? -1.f : 1.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = fmaf(sg, t[e], v[e]);
+        }
+    }
   }
   butterflies<8>(v);
 #pragma unroll
