@@ -186,6 +186,26 @@ def test_baseline_shapes_prefill_sampled_rows(n, k, m):
     assert (np.abs(col_sum - col_ref) <= tol).all()
 
 
+# ---------------------------------------------------------------------------------------------
+# batches of 17..128 rows: operand-swapped tcgen05 kernel, with a cluster split over k when there are few column tiles
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n,k", [(4096, 4096), (14336, 4096), (4096, 14336), (1024, 4096), (6144, 4096), (18944, 3584),
+                                 (3584, 18944), (512, 2048), (192, 640)])
+@pytest.mark.parametrize("m", [17, 48, 64, 100, 128])
+def test_baseline_shapes_mid_batch(n, k, m):
+    layer = quantized_layer(n + k + m, n, k, bias=(n == 1024))
+    x = make_acts(m + 7, m, k)
+    linear_tolerance_check(_run(layer, x), _ref(layer, x))
+
+
+def test_mid_batch_deterministic():
+    layer = quantized_layer(23, 1024, 4096)          # 8 column tiles -> split over k inside a cluster
+    x = make_acts(6, 96, 4096)
+    a = _run(layer, x)
+    for _ in range(2):
+        assert np.array_equal(a.view(np.uint16), _run(layer, x).view(np.uint16))
+
+
 def test_prefill_strided_input_bias_and_batch_dims():
     from uniql_b200.quantize.quant_linear_layers import W4A16B16O16Linear
     lin = torch.nn.Linear(512, 328, bias=True).half()

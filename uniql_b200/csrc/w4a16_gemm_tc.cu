@@ -24,6 +24,7 @@
 #include "linear_internal.cuh"
 
 #include <cuda.h>
+#include <stdlib.h>
 
 namespace uniql {
 
@@ -392,6 +393,374 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Small-batch variant (16 < m <= 128): operands swapped.  The dequantised weight tile [128 columns x 64 k] is the
+// 128-row MMA operand (TMEM lane = output column), the activation tile [Mb x 64 k] (Mb = m rounded up to 16) the
+// N operand, so the MMA is 128 x Mb x 16 and no tensor work is spent on padding rows; a CTA dequantises 128 columns
+// instead of 256, which doubles the number of tiles for these launches that are bound by the dequantise rate.
+// The accumulator holds D^T: the epilogue stores, per batch row, 32 adjacent columns per warp (64-byte segments).
+namespace tcs {
+constexpr int BNW = 128, BK = 64;
+constexpr int W_BYTES = BNW * BK * 2;           // 16 KB dequantised weight tile
+constexpr int P_BYTES = (BK / 16) * (2 * BNW) * 4;   // 4 KB: 4 packed rows x 256 words
+constexpr int STAGES = 4, P_STAGES = 16;
+constexpr int NSETS = 2;                // dequantise warp sets; set t converts k-blocks t, t + NSETS, ...
+constexpr int DEQ_WARPS = 8;                    // warps per set: 2 column blocks x 4 packed rows
+constexpr int FIRST_DEQ_WARP = 7;
+constexpr int OFF_W = 0;
+constexpr int OFF_P = OFF_W + STAGES * W_BYTES;
+constexpr int OFF_BAR = OFF_P + P_STAGES * P_BYTES;
+constexpr int NUM_BARS = 2 * STAGES + 2 * P_STAGES + 4;
+constexpr int OFF_X = OFF_BAR + 1024;           // activation ring: STAGES stages of Mb x 128 bytes
+constexpr int THREADS = (FIRST_DEQ_WARP + NSETS * DEQ_WARPS) * 32;
+constexpr int TMEM_COLS = 256;                  // two accumulators of up to 128 columns
+static_assert(NUM_BARS * 8 + 16 <= 1024, "barrier block");
+static_assert(THREADS <= 1024, "block size");
+inline int smem_bytes(int Mb) { return OFF_X + STAGES * Mb * 128 + 1024; }
+}  // namespace tcs
+
+struct TcSwapParams {
+  const uint4* S;
+  const __half* bias;
+  __half* D;
+  int64_t ldd;
+  int M, Mb, N, n_out, K;
+  int ntiles;
+  int split;                                    // CTAs of a cluster that share one column tile, each a slice of k
+  int* status_word;
+};
+
+__device__ __forceinline__ void tcs_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// One poll of two barriers at once, so that the two shared-memory round trips overlap: bit 0 / bit 1 of the result
+// say which phase has completed.
+__device__ __forceinline__ uint32_t tcs_try_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred pa, pb;\n\t.reg .u32 ra, rb;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 pa, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 pb, [%3], %4;\n\t"
+      "selp.u32 ra, 1, 0, pa;\n\t"
+      "selp.u32 rb, 2, 0, pb;\n\t"
+      "or.b32 %0, ra, rb;\n\t}"
+      : "=r"(ok)
+      : "r"(bar_a), "r"(par_a), "r"(bar_b), "r"(par_b)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool tcs_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b) {
+  uint32_t done = 0;
+  for (int it = 0; it < tc::WAIT_POLLS; ++it) {
+    done |= tcs_try_wait2(bar_a, par_a, bar_b, par_b);
+    if (done == 3) return true;
+  }
+  return false;
+}
+
+// The four MMAs of one 64-k stage, the commit that releases the stage, and one poll of the NEXT stage's barrier, in one
+// block: the poll is issued first and its result read last, so its latency hides behind the issue of the MMAs instead
+// of adding to the single issuing thread's serial time per stage.  Returns whether the next stage was already full.
+__device__ __forceinline__ uint32_t tcs_issue_stage(uint32_t tmem_d, uint64_t wdesc, uint64_t xdesc, uint32_t idesc,
+                                                    uint32_t accumulate, uint32_t bar_release, uint32_t bar_next,
+                                                    uint32_t par_next) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 q, [%7], %8;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "add.u64 a1, %2, 2;\n\tadd.u64 a2, %2, 4;\n\tadd.u64 a3, %2, 6;\n\t"
+      "add.u64 b1, %3, 2;\n\tadd.u64 b2, %3, 4;\n\tadd.u64 b3, %3, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %4, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %4, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %4, t;\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(ok)
+      : "r"(tmem_d), "l"(wdesc), "l"(xdesc), "r"(idesc), "r"(accumulate), "r"(bar_release), "r"(bar_next), "r"(par_next)
+      : "memory");
+  return ok;
+}
+
+__global__ void __launch_bounds__(tcs::THREADS, 1)
+w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensorMap xmap,
+                          const __grid_constant__ CUtensorMap wmap) {
+  using namespace tcs;
+  extern __shared__ uint8_t smem_unaligned[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = tc_smem_addr(smem);
+  const uint32_t bars = sbase + OFF_BAR;
+  // full[s]: the activation tile has landed (TMA bytes) AND the set's warps have written the weight tile;
+  // empty[s]: the MMAs that read stage s have completed
+  const uint32_t bar_full = bars, bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_full_p = bar_empty + 8 * STAGES, bar_empty_p = bar_full_p + 8 * P_STAGES;
+  const uint32_t bar_tmem_full = bar_empty_p + 8 * P_STAGES, bar_tmem_empty = bar_tmem_full + 16;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + NUM_BARS * 8);
+  const uint32_t x_bytes = (uint32_t)p.Mb * (BK * 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // a cluster of p.split CTAs owns one column tile at a time; CTA `rank` of it reduces k-blocks [kb0, kb0 + KB),
+  // cut on scale-group boundaries (two k-blocks per group)
+  const int rank = (int)blockIdx.x % p.split;
+  const int tile0 = (int)blockIdx.x / p.split, tile_step = (int)gridDim.x / p.split;
+  const int groups = p.K / 128;
+  const int kb0 = 2 * (int)((long long)groups * rank / p.split);
+  const int KB = 2 * (int)((long long)groups * (rank + 1) / p.split) - kb0;
+  const int my_tiles = (tile0 < p.ntiles) ? (p.ntiles - 1 - tile0) / tile_step + 1 : 0;
+  const int total_it = my_tiles * KB;
+  // instruction descriptor: D fp32, A/B fp16, both K-major, M = 128 (weight columns), N = Mb (batch rows)
+  const uint32_t idesc = (1u << 4) | ((uint32_t)(p.Mb >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&xmap) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+    for (int s = 0; s < STAGES; ++s) {
+      tc_mbar_init(bar_full + 8 * s, 1 + DEQ_WARPS);
+      tc_mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < P_STAGES; ++s) {
+      tc_mbar_init(bar_full_p + 8 * s, 1);
+      tc_mbar_init(bar_empty_p + 8 * s, DEQ_WARPS);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc_mbar_init(bar_tmem_full + 8 * b, 1);
+      tc_mbar_init(bar_tmem_empty + 8 * b, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_addr((const void*)tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool timed_out = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ packed-weight producer (the HBM stream)
+    if (lane == 0) {
+      int it = 0;
+      for (int nt = tile0; nt < p.ntiles; nt += tile_step) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int sp = it % P_STAGES;
+          if (!timed_out && !tc_mbar_wait(bar_empty_p + 8 * sp, ((it / P_STAGES) & 1) ^ 1)) timed_out = true;
+          tc_mbar_expect_tx(bar_full_p + 8 * sp, P_BYTES);
+          tc_tma_2d(sbase + OFF_P + sp * P_BYTES, &wmap, nt * (2 * BNW), (kb0 + kb) * 4, bar_full_p + 8 * sp);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ activation producer (re-reads, L2 hits)
+    if (lane == 0) {
+      int kb = 0;
+      for (int it = 0; it < total_it; ++it) {
+        const int s = it % STAGES;
+        if (!timed_out && !tc_mbar_wait(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1)) timed_out = true;
+        tc_mbar_expect_tx(bar_full + 8 * s, x_bytes);
+        tc_tma_2d(sbase + OFF_X + s * x_bytes, &xmap, (kb0 + kb) * BK, 0, bar_full + 8 * s);
+        if (++kb == KB) kb = 0;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int it = 0, it_tile = 0;
+      uint32_t ready = 0;                        // the current stage's full barrier was seen complete by the last poll
+      for (int nt = tile0; nt < p.ntiles; nt += tile_step, ++it_tile) {
+        const int buf = it_tile & 1;
+        if (!timed_out && !tc_mbar_wait(bar_tmem_empty + 8 * buf, ((it_tile >> 1) & 1) ^ 1)) timed_out = true;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * 128;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!ready && !timed_out && !tc_mbar_wait(bar_full + 8 * s, (it / STAGES) & 1)) timed_out = true;
+          tc_fence_after();
+          const int s1 = (s + 1 == STAGES) ? 0 : s + 1;
+          ready = tcs_issue_stage(tmem_d, tc_smem_desc(sbase + OFF_W + s * W_BYTES), tc_smem_desc(sbase + OFF_X + s * x_bytes),
+                                  idesc, kb != 0 ? 1u : 0u, bar_empty + 8 * s, bar_full + 8 * s1, ((it + 1) / STAGES) & 1);
+          if (it + 1 >= total_it) ready = 0;      // that poll looked at a phase nobody will complete
+        }
+        tc_commit(bar_tmem_full + 8 * buf);
+      }
+    }
+  } else if (warp < FIRST_DEQ_WARP) {
+    // ------------------------------------------------------------------ epilogue (D^T: lane = column, TMEM column = batch row)
+    const int q = warp & 3;
+    int it_tile = 0;
+    if (p.split > 1) {
+      // one tile per cluster: ranks other than 0 park their partial accumulator in shared memory (the weight ring,
+      // idle once the last MMA has completed) as part[batch row][column]; rank 0 sums after the cluster barrier
+      if (tile0 < p.ntiles) {
+        if (!timed_out && !tc_mbar_wait_relaxed(bar_tmem_full, 0)) timed_out = true;
+        tc_fence_after();
+        if (rank != 0) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+          const uint32_t part = sbase + OFF_W + (uint32_t)(q * 32 + lane) * 4;
+#pragma unroll 1
+          for (int c0 = 0; c0 < p.Mb; c0 += 32) {
+            uint32_t r[32];
+            tc_ld32(taddr + c0, r);
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (c0 + e < p.M) tc_sts32(part + (uint32_t)(c0 + e) * (BNW * 4), r[e]);
+          }
+        }
+      }
+    } else
+    for (int nt = tile0; nt < p.ntiles; nt += tile_step, ++it_tile) {
+      const int buf = it_tile & 1;
+      if (!timed_out && !tc_mbar_wait_relaxed(bar_tmem_full + 8 * buf, (it_tile >> 1) & 1)) timed_out = true;
+      tc_fence_after();
+      const int n = nt * BNW + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 128;
+      const float bv = (p.bias && n < p.n_out) ? __half2float(p.bias[n]) : 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < p.Mb; c0 += 32) {
+        uint32_t r[32];
+        tc_ld32(taddr + c0, r);
+        if (n < p.n_out) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c0 + e < p.M) p.D[(size_t)(c0 + e) * p.ldd + n] = __float2half_rn(__uint_as_float(r[e]) + bv);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc_mbar_arrive(bar_tmem_empty + 8 * buf);
+    }
+  } else {
+    // ------------------------------------------------------------------ dequantise: per set, 2 blocks x 4 packed rows per stage
+    const int dw = warp - FIRST_DEQ_WARP;
+    const int set = dw / DEQ_WARPS;
+    const int blk_local = dw & 1;
+    const int kt = (dw >> 1) & 3;
+    const int g = lane >> 2, c = lane & 3;
+    const int nblk = p.N >> 6;
+    const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
+    const uint4* sbase_g = p.S + g;
+    // position of the k-block this warp converts next, and of the one after it (whose scales are requested early)
+    int ti = 0, kb = set;
+    while (kb >= KB && ti < my_tiles) { kb -= KB; ++ti; }
+    int ti2 = ti, kb2 = kb + NSETS;
+    while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
+    uint4 snext = make_uint4(0, 0, 0, 0);
+    if (set < total_it) {
+      const int blk = (tile0 + ti * tile_step) * 2 + blk_local;
+      if (blk < nblk) snext = ld_nc16(sbase_g + (size_t)blk * 8 + (size_t)((kb0 + kb) >> 1) * srow_u4);
+    }
+    for (int it = set; it < total_it; it += NSETS) {
+      const int blk = (tile0 + ti * tile_step) * 2 + blk_local;
+      const bool valid = blk < nblk;
+      uint32_t sdup[8];
+      {
+        const uint32_t s4[4] = {snext.x, snext.y, snext.z, snext.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          sdup[2 * j] = __byte_perm(s4[j], 0, 0x1010);       // low half  -> columns 16j+g
+          sdup[2 * j + 1] = __byte_perm(s4[j], 0, 0x3232);   // high half -> columns 16j+g+8
+        }
+        if (it + NSETS < total_it) {
+          const int blk2 = (tile0 + ti2 * tile_step) * 2 + blk_local;
+          if (blk2 < nblk) snext = ld_nc16(sbase_g + (size_t)blk2 * 8 + (size_t)((kb0 + kb2) >> 1) * srow_u4);
+        }
+        ti = ti2; kb = kb2;
+        kb2 += NSETS;
+        while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
+      }
+      const int sp = it % P_STAGES, s = it % STAGES;
+      if (!timed_out && !tcs_wait2(bar_full_p + 8 * sp, (it / P_STAGES) & 1, bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1))
+        timed_out = true;
+      uint4 w4 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+      if (valid) w4 = tc_lds128(sbase + OFF_P + sp * P_BYTES + blk_local * 512 + lane * 16 + kt * 1024);
+      const uint32_t wtile = sbase + OFF_W + s * W_BYTES + (uint32_t)(blk_local * 64 + g) * 128 + 4 * c;
+      {
+        const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
+        const uint32_t a_lo = wtile + ((uint32_t)((2 * kt) ^ g) << 4), a_hi = wtile + ((uint32_t)((2 * kt + 1) ^ g) << 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t qw = wq[j], qs = wq[j] >> 8;
+          uint32_t v;
+          __half2 r;
+          v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 2c, 2c+1
+          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
+          tc_sts32(a_lo + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
+          v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 2c+8, 2c+9
+          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
+          tc_sts32(a_hi + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
+          v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 2c, 2c+1
+          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
+          tc_sts32(a_lo + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
+          v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 2c+8, 2c+9
+          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
+          tc_sts32(a_hi + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
+        }
+      }
+      // make the generic-proxy stores visible to the tensor core's async-proxy reads, then signal
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        tc_mbar_arrive(bar_full + 8 * s);
+        tc_mbar_arrive(bar_empty_p + 8 * sp);
+      }
+    }
+  }
+
+  if (p.split > 1) {
+    __syncwarp();
+    tcs_cluster_sync();                         // every rank's partial is in its shared memory
+    if (rank == 0 && warp >= 3 && warp < FIRST_DEQ_WARP && tile0 < p.ntiles) {
+      const int q = warp & 3;
+      const int n = tile0 * BNW + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+      const uint32_t part = sbase + OFF_W + (uint32_t)(q * 32 + lane) * 4;
+      const float bv = (p.bias && n < p.n_out) ? __half2float(p.bias[n]) : 0.f;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < p.Mb; c0 += 32) {
+        uint32_t r[32];
+        tc_ld32(taddr + c0, r);
+        float acc[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(r[e]);
+        for (int rr = 1; rr < p.split; ++rr) {   // fixed order: the sum does not depend on timing
+          uint32_t remote;
+          asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(part), "r"(rr));
+          float v[32];
+          // independent loads, all in flight together (rows past M hold stale data and are never stored)
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[e]) : "r"(remote + (uint32_t)(c0 + e) * (BNW * 4)));
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[e] += v[e];
+        }
+        if (n < p.n_out) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c0 + e < p.M) p.D[(size_t)(c0 + e) * p.ldd + n] = __float2half_rn(acc[e] + bv);
+        }
+      }
+    }
+    __syncwarp();
+    tcs_cluster_sync();                         // no rank leaves while its shared memory may still be read
+  }
+  if (timed_out && p.status_word) atomicOr(p.status_word, UNIQL_STATUS_WAIT_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -417,8 +786,87 @@ bool gemm_tc_supported(int64_t m, int64_t n, int64_t k) {
 
 size_t gemm_tc_scratch_bytes(int64_t, int64_t, int64_t) { return 0; }
 
+static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m,
+                               cudaStream_t stream) {
+  using namespace tcs;
+  EncodeTiledFn enc = tc_encode_fn();
+  if (!enc) return cuda_fail(cudaErrorNotSupported);
+  const int Mb = (int)((m + 15) / 16 * 16);
+  CUtensorMap xmap, wmap;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)Mb};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(A), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cuda_fail(cudaErrorInvalidValue);
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)(2 * a.n), (cuuint64_t)(a.k / 16)};
+    cuuint64_t strides[1] = {(cuuint64_t)(2 * a.n) * 4};
+    cuuint32_t box[2] = {256, 4};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.B), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cuda_fail(cudaErrorInvalidValue);
+  }
+  TcSwapParams p;
+  p.S = (const uint4*)a.s; p.bias = (const __half*)a.bias; p.D = D; p.ldd = a.ldd;
+  p.M = (int)m; p.Mb = Mb; p.N = (int)a.n; p.n_out = (int)a.n_out; p.K = (int)a.k;
+  p.ntiles = (int)((a.n + BNW - 1) / BNW);
+  p.status_word = a.status_word;
+  const int sms = device_info().sm_count;
+  // few column tiles: a cluster of `split` CTAs shares each tile, every CTA reducing a slice of k (at least four
+  // scale groups), and the partial accumulators are summed through distributed shared memory
+  int split = 1;
+  {
+    static const int forced = [] { const char* e = getenv("UNIQL_B200_TC_SPLIT"); return (e && *e) ? atoi(e) : 0; }();
+    const int groups = (int)(a.k / 128);
+    if (forced > 0) split = forced;
+    else if (p.ntiles * 2 <= sms) {
+      split = sms / p.ntiles;
+      if (split > 8) split = 8;
+      while (split > 1 && groups / split < 4) --split;
+    }
+    if (split > groups) split = groups;
+    if (split < 1) split = 1;
+    if (split > 8) split = 8;
+  }
+  p.split = split;
+  static thread_local bool attr_set = false;
+  if (!attr_set) {
+    UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        smem_bytes(128)));
+    attr_set = true;
+  }
+  if (split == 1) {
+    const int grid = p.ntiles < sms ? p.ntiles : sms;
+    w4a16_gemm_tc_swap_kernel<<<grid, THREADS, smem_bytes(Mb), stream>>>(p, xmap, wmap);
+    return launch_status();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.ntiles * split));
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes(Mb);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a16_gemm_tc_swap_kernel, p, xmap, wmap));
+  return launch_status();
+}
+
 int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m, cudaStream_t stream) {
   using namespace tc;
+  static const int swap_on = [] { const char* e = getenv("UNIQL_B200_TC_SWAP"); return (e && *e) ? atoi(e) : 1; }();
+  if (swap_on && m <= 128) return launch_gemm_tc_swap(a, A, lda, D, m, stream);
   EncodeTiledFn enc = tc_encode_fn();
   if (!enc) return cuda_fail(cudaErrorNotSupported);
   CUtensorMap amap, wmap;
