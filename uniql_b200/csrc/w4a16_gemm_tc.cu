@@ -395,28 +395,34 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
 
 // ------------------------------------------------------------------------------------------------------------
 // Small-batch variant (16 < m <= 128): operands swapped.  The dequantised weight tile [128 columns x 64 k] is the
-// 128-row MMA operand (TMEM lane = output column), the activation tile [Mb x 64 k] (Mb = m rounded up to 16) the
-// N operand, so the MMA is 128 x Mb x 16 and no tensor work is spent on padding rows; a CTA dequantises 128 columns
-// instead of 256, which doubles the number of tiles for these launches that are bound by the dequantise rate.
+// 128-row MMA operand (tensor-memory lane = output column), the activation tile [Mb x 64 k] (Mb = m rounded up to 16) the
+// N operand, so the MMA is 128 x Mb x 16 and no tensor work is spent on padding rows.  Shared-memory bandwidth
+// (128 bytes per clock per SM: generic stores, TMA writes and the tensor core's operand reads all draw on it) is what
+// bounds these kernels, so the weight operand never enters shared memory: the dequantise warps write it to tensor
+// memory and the MMA reads it from there.  Only the packed words (4 KB) and the activation tile cross shared memory.
 // The accumulator holds D^T: the epilogue stores, per batch row, 32 adjacent columns per warp (64-byte segments).
 namespace tcs {
 constexpr int BNW = 128, BK = 64;
-constexpr int W_BYTES = BNW * BK * 2;           // 16 KB dequantised weight tile
 constexpr int P_BYTES = (BK / 16) * (2 * BNW) * 4;   // 4 KB: 4 packed rows x 256 words
-constexpr int STAGES = 4, P_STAGES = 16;
-constexpr int NSETS = 2;                // dequantise warp sets; set t converts k-blocks t, t + NSETS, ...
-constexpr int DEQ_WARPS = 8;                    // warps per set: 2 column blocks x 4 packed rows
+constexpr int STAGES = 6, P_STAGES = 16;
+constexpr int NSETS = 4;                        // dequantise warp sets; set t converts k-blocks t, t + NSETS, ...
+constexpr int DEQ_WARPS = 4;                    // warps per set: one per 32-lane quarter of tensor memory
 constexpr int FIRST_DEQ_WARP = 7;
-constexpr int OFF_W = 0;
-constexpr int OFF_P = OFF_W + STAGES * W_BYTES;
+constexpr int OFF_P = 0;
 constexpr int OFF_BAR = OFF_P + P_STAGES * P_BYTES;
 constexpr int NUM_BARS = 2 * STAGES + 2 * P_STAGES + 4;
 constexpr int OFF_X = OFF_BAR + 1024;           // activation ring: STAGES stages of Mb x 128 bytes
 constexpr int THREADS = (FIRST_DEQ_WARP + NSETS * DEQ_WARPS) * 32;
-constexpr int TMEM_COLS = 256;                  // two accumulators of up to 128 columns
+constexpr int TMEM_COLS = 512;                  // two accumulators of up to 128 columns, then the weight-tile ring
+constexpr int TMEM_W0 = 256;                    // weight tile of stage s: columns TMEM_W0 + 32 s (64 k as 32 half2 columns)
+static_assert(TMEM_W0 + STAGES * 32 <= TMEM_COLS, "tensor memory budget");
 static_assert(NUM_BARS * 8 + 16 <= 1024, "barrier block");
 static_assert(THREADS <= 1024, "block size");
-inline int smem_bytes(int Mb) { return OFF_X + STAGES * Mb * 128 + 1024; }
+// at least 120 KB, so that two CTAs (each allocates all 512 tensor-memory columns) can never share an SM
+inline int smem_bytes(int Mb) {
+  const int need = OFF_X + STAGES * Mb * 128 + 1024;
+  return need < 120 * 1024 ? 120 * 1024 : need;
+}
 }  // namespace tcs
 
 struct TcSwapParams {
@@ -463,25 +469,25 @@ __device__ __forceinline__ bool tcs_wait2(uint32_t bar_a, uint32_t par_a, uint32
 // The four MMAs of one 64-k stage, the commit that releases the stage, and one poll of the NEXT stage's barrier, in one
 // block: the poll is issued first and its result read last, so its latency hides behind the issue of the MMAs instead
 // of adding to the single issuing thread's serial time per stage.  Returns whether the next stage was already full.
-__device__ __forceinline__ uint32_t tcs_issue_stage(uint32_t tmem_d, uint64_t wdesc, uint64_t xdesc, uint32_t idesc,
+__device__ __forceinline__ uint32_t tcs_issue_stage(uint32_t tmem_d, uint32_t tmem_w, uint64_t xdesc, uint32_t idesc,
                                                     uint32_t accumulate, uint32_t bar_release, uint32_t bar_next,
                                                     uint32_t par_next) {
   uint32_t ok;
   asm volatile(
-      "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "{\n\t.reg .pred p, q, t;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b64 b1, b2, b3;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 q, [%7], %8;\n\t"
       "setp.ne.b32 p, %5, 0;\n\t"
       "setp.eq.b32 t, 0, 0;\n\t"
-      "add.u64 a1, %2, 2;\n\tadd.u64 a2, %2, 4;\n\tadd.u64 a3, %2, 6;\n\t"
+      "add.u32 a1, %2, 8;\n\tadd.u32 a2, %2, 16;\n\tadd.u32 a3, %2, 24;\n\t"
       "add.u64 b1, %3, 2;\n\tadd.u64 b2, %3, 4;\n\tadd.u64 b3, %3, 6;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, p;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %4, t;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %4, t;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %4, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], b1, %4, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], b2, %4, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], b3, %4, t;\n\t"
       "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(ok)
-      : "r"(tmem_d), "l"(wdesc), "l"(xdesc), "r"(idesc), "r"(accumulate), "r"(bar_release), "r"(bar_next), "r"(par_next)
+      : "r"(tmem_d), "r"(tmem_w), "l"(xdesc), "r"(idesc), "r"(accumulate), "r"(bar_release), "r"(bar_next), "r"(par_next)
       : "memory");
   return ok;
 }
@@ -494,7 +500,8 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = tc_smem_addr(smem);
   const uint32_t bars = sbase + OFF_BAR;
-  // full[s]: the activation tile has landed (TMA bytes) AND the set's warps have written the weight tile;
+  // full[s]: the activation tile has landed in shared memory (TMA bytes) AND the set's warps have written the weight
+  // tile of the stage into tensor memory;
   // empty[s]: the MMAs that read stage s have completed
   const uint32_t bar_full = bars, bar_empty = bar_full + 8 * STAGES;
   const uint32_t bar_full_p = bar_empty + 8 * STAGES, bar_empty_p = bar_full_p + 8 * P_STAGES;
@@ -585,7 +592,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
           if (!ready && !timed_out && !tc_mbar_wait(bar_full + 8 * s, (it / STAGES) & 1)) timed_out = true;
           tc_fence_after();
           const int s1 = (s + 1 == STAGES) ? 0 : s + 1;
-          ready = tcs_issue_stage(tmem_d, tc_smem_desc(sbase + OFF_W + s * W_BYTES), tc_smem_desc(sbase + OFF_X + s * x_bytes),
+          ready = tcs_issue_stage(tmem_d, tmem_base + TMEM_W0 + s * 32, tc_smem_desc(sbase + OFF_X + s * x_bytes),
                                   idesc, kb != 0 ? 1u : 0u, bar_empty + 8 * s, bar_full + 8 * s1, ((it + 1) / STAGES) & 1);
           if (it + 1 >= total_it) ready = 0;      // that poll looked at a phase nobody will complete
         }
@@ -597,14 +604,14 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
     const int q = warp & 3;
     int it_tile = 0;
     if (p.split > 1) {
-      // one tile per cluster: ranks other than 0 park their partial accumulator in shared memory (the weight ring,
-      // idle once the last MMA has completed) as part[batch row][column]; rank 0 sums after the cluster barrier
+      // one tile per cluster: ranks other than 0 park their partial accumulator in shared memory (the activation
+      // ring, idle once the last MMA has completed) as part[batch row][column]; rank 0 sums after the cluster barrier
       if (tile0 < p.ntiles) {
         if (!timed_out && !tc_mbar_wait_relaxed(bar_tmem_full, 0)) timed_out = true;
         tc_fence_after();
         if (rank != 0) {
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-          const uint32_t part = sbase + OFF_W + (uint32_t)(q * 32 + lane) * 4;
+          const uint32_t part = sbase + OFF_X + (uint32_t)(q * 32 + lane) * 4;
 #pragma unroll 1
           for (int c0 = 0; c0 < p.Mb; c0 += 32) {
             uint32_t r[32];
@@ -638,12 +645,16 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
       if (lane == 0) tc_mbar_arrive(bar_tmem_empty + 8 * buf);
     }
   } else {
-    // ------------------------------------------------------------------ dequantise: per set, 2 blocks x 4 packed rows per stage
+    // ------------------------------------------------------------------ dequantise into tensor memory
+    // A lane of the Marlin layout holds, per packed word j, the half2 pairs (n = 16j+g | 16j+g+8) x (k = 2c.. | 2c+8..):
+    // exactly the register fragment of tcgen05.st.16x128b (register 2i -> lane g, column 4i+c; 2i+1 -> lane g+8), so
+    // the weight tile goes from registers to the MMA's A operand without touching shared memory.  Warp quarter q owns
+    // tensor-memory lanes 32q..32q+31 = columns 32q.. of the tile = Marlin block q/2, words j = 2(q%2), 2(q%2)+1.
     const int dw = warp - FIRST_DEQ_WARP;
     const int set = dw / DEQ_WARPS;
-    const int blk_local = dw & 1;
-    const int kt = (dw >> 1) & 3;
-    const int g = lane >> 2, c = lane & 3;
+    const int q = warp & 3;
+    const int blk_local = q >> 1;
+    const int g = lane >> 2;
     const int nblk = p.N >> 6;
     const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
     const uint4* sbase_g = p.S + g;
@@ -652,60 +663,74 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
     while (kb >= KB && ti < my_tiles) { kb -= KB; ++ti; }
     int ti2 = ti, kb2 = kb + NSETS;
     while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
-    uint4 snext = make_uint4(0, 0, 0, 0);
+    uint2 snext = make_uint2(0, 0);
     if (set < total_it) {
       const int blk = (tile0 + ti * tile_step) * 2 + blk_local;
-      if (blk < nblk) snext = ld_nc16(sbase_g + (size_t)blk * 8 + (size_t)((kb0 + kb) >> 1) * srow_u4);
+      if (blk < nblk)
+        snext = __ldg(reinterpret_cast<const uint2*>(sbase_g + (size_t)blk * 8 + (size_t)((kb0 + kb) >> 1) * srow_u4) + (q & 1));
     }
     for (int it = set; it < total_it; it += NSETS) {
       const int blk = (tile0 + ti * tile_step) * 2 + blk_local;
       const bool valid = blk < nblk;
-      uint32_t sdup[8];
-      {
-        const uint32_t s4[4] = {snext.x, snext.y, snext.z, snext.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          sdup[2 * j] = __byte_perm(s4[j], 0, 0x1010);       // low half  -> columns 16j+g
-          sdup[2 * j + 1] = __byte_perm(s4[j], 0, 0x3232);   // high half -> columns 16j+g+8
-        }
-        if (it + NSETS < total_it) {
-          const int blk2 = (tile0 + ti2 * tile_step) * 2 + blk_local;
-          if (blk2 < nblk) snext = ld_nc16(sbase_g + (size_t)blk2 * 8 + (size_t)((kb0 + kb2) >> 1) * srow_u4);
-        }
-        ti = ti2; kb = kb2;
-        kb2 += NSETS;
-        while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
+      uint32_t sdup[4];
+      sdup[0] = __byte_perm(snext.x, 0, 0x1010);   // word j0:   columns 16 j0 + g
+      sdup[1] = __byte_perm(snext.x, 0, 0x3232);   //            columns 16 j0 + g + 8
+      sdup[2] = __byte_perm(snext.y, 0, 0x1010);   // word j0+1
+      sdup[3] = __byte_perm(snext.y, 0, 0x3232);
+      if (it + NSETS < total_it) {
+        const int blk2 = (tile0 + ti2 * tile_step) * 2 + blk_local;
+        if (blk2 < nblk)
+          snext = __ldg(reinterpret_cast<const uint2*>(sbase_g + (size_t)blk2 * 8 + (size_t)((kb0 + kb2) >> 1) * srow_u4) + (q & 1));
       }
+      ti = ti2; kb = kb2;
+      kb2 += NSETS;
+      while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
+
       const int sp = it % P_STAGES, s = it % STAGES;
       if (!timed_out && !tcs_wait2(bar_full_p + 8 * sp, (it / P_STAGES) & 1, bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1))
         timed_out = true;
-      uint4 w4 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-      if (valid) w4 = tc_lds128(sbase + OFF_P + sp * P_BYTES + blk_local * 512 + lane * 16 + kt * 1024);
-      const uint32_t wtile = sbase + OFF_W + s * W_BYTES + (uint32_t)(blk_local * 64 + g) * 128 + 4 * c;
-      {
-        const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
-        const uint32_t a_lo = wtile + ((uint32_t)((2 * kt) ^ g) << 4), a_hi = wtile + ((uint32_t)((2 * kt + 1) ^ g) << 4);
+      tc_fence_after();
+      uint32_t wq[4][2];
+      const uint32_t pk = sbase + OFF_P + sp * P_BYTES + blk_local * 512 + lane * 16 + (q & 1) * 8;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t qw = wq[j], qs = wq[j] >> 8;
-          uint32_t v;
-          __half2 r;
-          v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 2c, 2c+1
-          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
-          tc_sts32(a_lo + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
-          v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 2c+8, 2c+9
-          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
-          tc_sts32(a_hi + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
-          v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 2c, 2c+1
-          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
-          tc_sts32(a_lo + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
-          v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 2c+8, 2c+9
-          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
-          tc_sts32(a_hi + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
-        }
+      for (int kt = 0; kt < 4; ++kt) {
+        wq[kt][0] = wq[kt][1] = 0x88888888u;
+        if (valid)
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wq[kt][0]), "=r"(wq[kt][1]) : "r"(pk + kt * 1024) : "memory");
       }
-      // make the generic-proxy stores visible to the tensor core's async-proxy reads, then signal
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        uint32_t r[16];
+        const __half2 s_lo = *reinterpret_cast<const __half2*>(&sdup[2 * jj]);
+        const __half2 s_hi = *reinterpret_cast<const __half2*>(&sdup[2 * jj + 1]);
+#pragma unroll
+        for (int kt = 0; kt < 4; ++kt) {
+          const uint32_t qw = wq[kt][jj], qs = qw >> 8;
+          uint32_t v;
+          __half2 h;
+          v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 16kt + 2c, 2c+1
+          h = __hmul2(*reinterpret_cast<__half2*>(&v), s_lo);
+          r[4 * kt + 0] = *reinterpret_cast<uint32_t*>(&h);
+          v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 16kt + 2c, 2c+1
+          h = __hmul2(*reinterpret_cast<__half2*>(&v), s_hi);
+          r[4 * kt + 1] = *reinterpret_cast<uint32_t*>(&h);
+          v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 16kt + 2c+8, 2c+9
+          h = __hmul2(*reinterpret_cast<__half2*>(&v), s_lo);
+          r[4 * kt + 2] = *reinterpret_cast<uint32_t*>(&h);
+          v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 16kt + 2c+8, 2c+9
+          h = __hmul2(*reinterpret_cast<__half2*>(&v), s_hi);
+          r[4 * kt + 3] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32 + jj * 16) << 16) + TMEM_W0 + s * 32;
+        asm volatile(
+            "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "
+            "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+            ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+              "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+            : "memory");
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) {
         tc_mbar_arrive(bar_full + 8 * s);
@@ -721,7 +746,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
       const int q = warp & 3;
       const int n = tile0 * BNW + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-      const uint32_t part = sbase + OFF_W + (uint32_t)(q * 32 + lane) * 4;
+      const uint32_t part = sbase + OFF_X + (uint32_t)(q * 32 + lane) * 4;
       const float bv = (p.bias && n < p.n_out) ? __half2float(p.bias[n]) : 0.f;
       tc_fence_after();
 #pragma unroll 1
