@@ -32,21 +32,22 @@ namespace tc {
 constexpr int BMH = 128, BN = 256, BK = 64;   // BMH: rows of one MMA (one "half")
 constexpr int A_BYTES = BMH * BK * 2;         // 16 KB per half
 constexpr int B_BYTES = BN * BK * 2;          // 32 KB
-constexpr int P_BYTES = (BK / 16) * (2 * BN) * 4;   // 8 KB: 4 packed rows x 512 words
-constexpr int P_STAGES = 3;
-constexpr int DEQ_WARPS = 16;
+constexpr int DEQ_SETS = 2;                   // dequantise warp sets; set t converts k-blocks t, t + 2, ...
+constexpr int DEQ_SET_WARPS = 8;              // per set: 4 column blocks x 2 pairs of packed rows
+constexpr int DEQ_WARPS = DEQ_SETS * DEQ_SET_WARPS;
 constexpr int TMEM_COLS = 512;
 template <int H> struct Cfg {
   static constexpr int AB_STAGES = H == 1 ? 4 : 3;
   static constexpr int STAGE_A = H * A_BYTES;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + AB_STAGES * STAGE_A;
-  static constexpr int OFF_P = OFF_B + AB_STAGES * B_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_STAGES * P_BYTES;
-  static constexpr int NUM_BARS = 3 * AB_STAGES + 2 * P_STAGES + 4;
+  static constexpr int OFF_BAR = OFF_B + AB_STAGES * B_BYTES;
+  static constexpr int NUM_BARS = 2 * AB_STAGES + 4;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;   // + slack to align the base to 1 KB
+  static constexpr int FIRST_EPI_WARP = 2;
   static constexpr int EPI_WARPS = 4 * H;
-  static constexpr int THREADS = (2 + EPI_WARPS + DEQ_WARPS) * 32;
+  static constexpr int FIRST_DEQ_WARP = FIRST_EPI_WARP + EPI_WARPS;
+  static constexpr int THREADS = (FIRST_DEQ_WARP + DEQ_WARPS) * 32;
 };
 // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128
 constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BMH >> 4) << 24);
@@ -57,6 +58,7 @@ constexpr int WAIT_POLLS = UNIQL_TC_WAIT_POLLS;
 }  // namespace tc
 
 struct TcParams {
+  const uint4* B;        // packed weights [K/16][2N] words
   const uint4* S;        // permuted scales, row g has n/8 uint4
   const __half* bias;
   __half* D;
@@ -154,39 +156,117 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// One poll of two barriers at once, so that the two shared-memory round trips overlap: bit 0 / bit 1 of the result
+// say which phase has completed.
+__device__ __forceinline__ uint32_t tc_try_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred pa, pb;\n\t.reg .u32 ra, rb;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 pa, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 pb, [%3], %4;\n\t"
+      "selp.u32 ra, 1, 0, pa;\n\t"
+      "selp.u32 rb, 2, 0, pb;\n\t"
+      "or.b32 %0, ra, rb;\n\t}"
+      : "=r"(ok)
+      : "r"(bar_a), "r"(par_a), "r"(bar_b), "r"(par_b)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool tc_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b) {
+  uint32_t done = 0;
+  for (int it = 0; it < tc::WAIT_POLLS; ++it) {
+    done |= tc_try_wait2(bar_a, par_a, bar_b, par_b);
+    if (done == 3) return true;
+  }
+  return false;
+}
+
+// All MMAs of one 64-k stage (four K=16 steps for each 128-row half), the commit that releases the stage, and one poll
+// of the NEXT stage's barrier, in one block: the poll is issued first and its result read last, so its latency hides
+// behind the issue of the MMAs instead of adding to the single issuing thread's serial time per stage.  Returns
+// whether the next stage was already full.
+template <int H>
+__device__ __forceinline__ uint32_t tc_issue_stage(uint32_t tmem_d, uint64_t adesc0, uint64_t adesc1, uint64_t bdesc,
+                                                   uint32_t accumulate, uint32_t bar_release, uint32_t bar_next,
+                                                   uint32_t par_next) {
+  uint32_t ok;
+  if (H == 1) {
+    asm volatile(
+        "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%7], %8;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "add.u64 a1, %2, 2;\n\tadd.u64 a2, %2, 4;\n\tadd.u64 a3, %2, 6;\n\t"
+        "add.u64 b1, %3, 2;\n\tadd.u64 b2, %3, 4;\n\tadd.u64 b3, %3, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %4, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %4, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %4, t;\n\t"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(ok)
+        : "r"(tmem_d), "l"(adesc0), "l"(bdesc), "r"(tc::IDESC), "r"(accumulate), "r"(bar_release), "r"(bar_next),
+          "r"(par_next)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a1, a2, a3, c1, c2, c3, b1, b2, b3;\n\t.reg .b32 d1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "add.u32 d1, %1, 256;\n\t"
+        "add.u64 a1, %2, 2;\n\tadd.u64 a2, %2, 4;\n\tadd.u64 a3, %2, 6;\n\t"
+        "add.u64 c1, %3, 2;\n\tadd.u64 c2, %3, 4;\n\tadd.u64 c3, %3, 6;\n\t"
+        "add.u64 b1, %4, 2;\n\tadd.u64 b2, %4, 4;\n\tadd.u64 b3, %4, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %4, %5, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a1, b1, %5, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a2, b2, %5, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a3, b3, %5, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [d1], %3, %4, %5, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [d1], c1, b1, %5, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [d1], c2, b2, %5, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [d1], c3, b3, %5, t;\n\t"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(ok)
+        : "r"(tmem_d), "l"(adesc0), "l"(adesc1), "l"(bdesc), "r"(tc::IDESC), "r"(accumulate), "r"(bar_release),
+          "r"(bar_next), "r"(par_next)
+        : "memory");
+  }
+  return ok;
+}
+
 template <int H>
 __global__ void __launch_bounds__(tc::Cfg<H>::THREADS, 1)
-w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
-                     const __grid_constant__ CUtensorMap wmap) {
+w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap) {
   using namespace tc;
   constexpr int AB_STAGES = Cfg<H>::AB_STAGES, STAGE_A = Cfg<H>::STAGE_A;
-  constexpr int OFF_A = Cfg<H>::OFF_A, OFF_B = Cfg<H>::OFF_B, OFF_P = Cfg<H>::OFF_P, OFF_BAR = Cfg<H>::OFF_BAR;
-  constexpr int NUM_BARS = Cfg<H>::NUM_BARS, EPI_WARPS = Cfg<H>::EPI_WARPS;
+  constexpr int OFF_A = Cfg<H>::OFF_A, OFF_B = Cfg<H>::OFF_B, OFF_BAR = Cfg<H>::OFF_BAR;
+  constexpr int NUM_BARS = Cfg<H>::NUM_BARS, FIRST_EPI_WARP = Cfg<H>::FIRST_EPI_WARP;
+  constexpr int FIRST_DEQ_WARP = Cfg<H>::FIRST_DEQ_WARP;
+  static_assert(BN == 256, "the second accumulator sits 256 tensor-memory columns after the first");
   extern __shared__ uint8_t smem_unaligned[];
   // 1 KB alignment: the 128B-swizzled tiles must start on a swizzle-atom boundary
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = tc_smem_addr(smem);
   const uint32_t bars = sbase + OFF_BAR;
-  const uint32_t bar_full_a = bars, bar_full_b = bars + 8 * AB_STAGES, bar_empty_ab = bars + 16 * AB_STAGES;
-  const uint32_t bar_full_p = bars + 24 * AB_STAGES, bar_empty_p = bar_full_p + 8 * P_STAGES;
-  const uint32_t bar_tmem_full = bar_empty_p + 8 * P_STAGES, bar_tmem_empty = bar_tmem_full + 16;
+  // full[s]: the activation tile has landed (TMA bytes) AND one set's warps have written the weight tile;
+  // empty[s]: the MMAs that read stage s have completed
+  const uint32_t bar_full = bars, bar_empty_ab = bars + 8 * AB_STAGES;
+  const uint32_t bar_tmem_full = bars + 16 * AB_STAGES, bar_tmem_empty = bar_tmem_full + 16;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + NUM_BARS * 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = p.K / BK;
   const int total_tiles = p.mtiles * p.ntiles;
+  const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int total_it = my_tiles * KB;
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&amap) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
     for (int s = 0; s < AB_STAGES; ++s) {
-      tc_mbar_init(bar_full_a + 8 * s, 1);
-      tc_mbar_init(bar_full_b + 8 * s, DEQ_WARPS);
+      tc_mbar_init(bar_full + 8 * s, 1 + DEQ_SET_WARPS);
       tc_mbar_init(bar_empty_ab + 8 * s, 1);
-    }
-    for (int s = 0; s < P_STAGES; ++s) {
-      tc_mbar_init(bar_full_p + 8 * s, 1);
-      tc_mbar_init(bar_empty_p + 8 * s, DEQ_WARPS);
     }
     for (int b = 0; b < 2; ++b) {
       tc_mbar_init(bar_tmem_full + 8 * b, 1);
@@ -208,25 +288,18 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
   bool timed_out = false;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ activation producer
     if (lane == 0) {
-      int it_ab = 0, it_p = 0;
+      int it_ab = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        const int mt = tile % p.mtiles, nt = tile / p.mtiles;
-        for (int kb = 0; kb < KB; ++kb, ++it_ab, ++it_p) {
-          const int sp = it_p % P_STAGES;
-          if (!timed_out && !tc_mbar_wait(bar_empty_p + 8 * sp, ((it_p / P_STAGES) & 1) ^ 1)) timed_out = true;
-          tc_mbar_expect_tx(bar_full_p + 8 * sp, P_BYTES);
-          tc_tma_2d(sbase + OFF_P + sp * P_BYTES, &wmap, nt * (2 * BN), kb * 4, bar_full_p + 8 * sp);
-          tc_tma_2d(sbase + OFF_P + sp * P_BYTES + P_BYTES / 2, &wmap, nt * (2 * BN) + 256, kb * 4,
-                    bar_full_p + 8 * sp);
+        const int mt = tile % p.mtiles;
+        for (int kb = 0; kb < KB; ++kb, ++it_ab) {
           const int s = it_ab % AB_STAGES;
           if (!timed_out && !tc_mbar_wait(bar_empty_ab + 8 * s, ((it_ab / AB_STAGES) & 1) ^ 1)) timed_out = true;
-          tc_mbar_expect_tx(bar_full_a + 8 * s, STAGE_A);
+          tc_mbar_expect_tx(bar_full + 8 * s, STAGE_A);
 #pragma unroll
           for (int h = 0; h < H; ++h)
-            tc_tma_2d(sbase + OFF_A + s * STAGE_A + h * A_BYTES, &amap, kb * BK, (mt * H + h) * BMH,
-                      bar_full_a + 8 * s);
+            tc_tma_2d(sbase + OFF_A + s * STAGE_A + h * A_BYTES, &amap, kb * BK, (mt * H + h) * BMH, bar_full + 8 * s);
         }
       }
     }
@@ -234,6 +307,7 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       int it_ab = 0, it_tile = 0;
+      uint32_t ready = 0;                        // the current stage's full barrier was seen complete by the last poll
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it_tile) {
         // H == 1: one accumulator per tile, alternating between the two TMEM halves (epilogue of tile t overlaps
         // the main loop of tile t+1).  H == 2: both halves belong to this tile.
@@ -245,29 +319,23 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
         tc_fence_after();
         for (int kb = 0; kb < KB; ++kb, ++it_ab) {
           const int s = it_ab % AB_STAGES;
-          const uint32_t ph = (it_ab / AB_STAGES) & 1;
-          if (!timed_out && !tc_mbar_wait(bar_full_a + 8 * s, ph)) timed_out = true;
-          if (!timed_out && !tc_mbar_wait(bar_full_b + 8 * s, ph)) timed_out = true;
+          if (!ready && !timed_out && !tc_mbar_wait(bar_full + 8 * s, (it_ab / AB_STAGES) & 1)) timed_out = true;
           tc_fence_after();
-          const uint64_t bdesc = tc_smem_desc(sbase + OFF_B + s * B_BYTES);
-#pragma unroll
-          for (int h = 0; h < H; ++h) {
-            const uint64_t adesc = tc_smem_desc(sbase + OFF_A + s * STAGE_A + h * A_BYTES);
-            const uint32_t tmem_d = tmem_base + (buf0 + h) * BN;
-#pragma unroll
-            for (int k4 = 0; k4 < BK / 16; ++k4)
-              tc_mma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
-          }
-          tc_commit(bar_empty_ab + 8 * s);      // stage reusable once these MMAs have read it
+          const int s1 = (s + 1 == AB_STAGES) ? 0 : s + 1;
+          const uint64_t adesc0 = tc_smem_desc(sbase + OFF_A + s * STAGE_A);
+          ready = tc_issue_stage<H>(tmem_base + buf0 * BN, adesc0, adesc0 + (A_BYTES >> 4),
+                                    tc_smem_desc(sbase + OFF_B + s * B_BYTES), kb != 0 ? 1u : 0u, bar_empty_ab + 8 * s,
+                                    bar_full + 8 * s1, ((it_ab + 1) / AB_STAGES) & 1);
+          if (it_ab + 1 >= total_it) ready = 0;   // that poll looked at a phase nobody will complete
         }
 #pragma unroll
         for (int h = 0; h < H; ++h) tc_commit(bar_tmem_full + 8 * (buf0 + h));   // accumulators complete
       }
     }
-  } else if (warp < 2 + EPI_WARPS) {
+  } else if (warp < FIRST_DEQ_WARP) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;                     // TMEM lane quadrant this warp may access
-    const int half = (warp - 2) >> 2;           // which 128-row half of the tile (always 0 when H == 1)
+    const int half = (warp - FIRST_EPI_WARP) >> 2;   // which 128-row half of the tile (always 0 when H == 1)
     int it_tile = 0;
     const bool vec_ok = ((p.ldd & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it_tile) {
@@ -318,69 +386,93 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap,
     }
   } else {
     // ------------------------------------------------------------------ dequantise
-    const int dw = warp - 2 - EPI_WARPS;
+    // Two sets of eight warps convert alternate k-blocks, so that two stages are in conversion at any time: what
+    // bounds this path is the latency of one warp's chain per stage (barrier polls, packed-word read, convert, store,
+    // proxy fence, arrive), not its instruction count.
+    const int dw = warp - FIRST_DEQ_WARP;
+    const int set = dw / DEQ_SET_WARPS;
     const int blk_local = dw & 3;               // 64-column block of the 256-column tile
-    const int kt = dw >> 2;                     // packed row of the stage this warp converts -> k = 16 kt .. 16 kt + 15
+    const int kt0 = ((dw >> 2) & 1) * 2;        // this warp's two packed rows of the stage: k = 16 kt0 .. 16 kt0 + 31
     const int g = lane >> 2, c = lane & 3;
     const int nblk = p.N >> 6;
     const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
-    int it_ab = 0, it_p = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int nt = tile / p.mtiles;
-      const int blk = nt * 4 + blk_local;
-      const bool valid = blk < nblk;
+    const uint4* sbase_g = p.S + g;
+    // position of the k-block this warp converts next, and of the one after it (whose scales are requested early)
+    int ti = 0, kb = set;
+    while (kb >= KB && ti < my_tiles) { kb -= KB; ++ti; }
+    int ti2 = ti, kb2 = kb + DEQ_SETS;
+    while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
+    // The packed words come straight from global memory into registers (512 contiguous bytes per warp and packed
+    // row), requested one iteration = two k-blocks ahead like the scales: a hop through shared memory would add a
+    // barrier wait and a read to the chain that bounds this path, and 16 KB per stage to the shared-memory traffic.
+    const uint32_t prow_u4 = (uint32_t)(p.N >> 1);            // one packed row: 2N words = N/2 uint4
+    const uint4* pbase = p.B + (size_t)kt0 * prow_u4 + lane;
+    const uint4 kZero = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);   // (8 - 8) * scale = 0
+    uint4 snext = make_uint4(0, 0, 0, 0), wnext[2] = {kZero, kZero};
+    if (set < total_it) {
+      const int blk = (((int)blockIdx.x + ti * (int)gridDim.x) / p.mtiles) * 4 + blk_local;
+      if (blk < nblk) {
+        snext = ld_nc16(sbase_g + (size_t)blk * 8 + (size_t)(kb >> 1) * srow_u4);
+        const uint4* src = pbase + (size_t)kb * 4 * prow_u4 + (size_t)blk * 32;
+        wnext[0] = ld_nc16(src);
+        wnext[1] = ld_nc16(src + prow_u4);
+      }
+    }
+    for (int it = set; it < total_it; it += DEQ_SETS) {
       uint32_t sdup[8];                         // the lane's 8 group scales, each duplicated into a half2
-      const uint4* srow = p.S + (size_t)blk * 8 + g;
-      uint4 snext = make_uint4(0, 0, 0, 0);     // scales of the next group, requested one group ahead
-      if (valid) snext = ld_nc16(srow);
-      for (int kb = 0; kb < KB; ++kb, ++it_ab, ++it_p) {
-        if ((kb & 1) == 0) {                    // 128 k-values per scale group, 64 per stage
-          const uint32_t s4[4] = {snext.x, snext.y, snext.z, snext.w};
+      const uint4 w4[2] = {wnext[0], wnext[1]};
+      {
+        const uint32_t s4[4] = {snext.x, snext.y, snext.z, snext.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            sdup[2 * j] = __byte_perm(s4[j], 0, 0x1010);       // low half  -> columns 16j+g
-            sdup[2 * j + 1] = __byte_perm(s4[j], 0, 0x3232);   // high half -> columns 16j+g+8
-          }
-          if (valid && kb + 2 < KB) snext = ld_nc16(srow + (size_t)((kb >> 1) + 1) * srow_u4);
+        for (int j = 0; j < 4; ++j) {
+          sdup[2 * j] = __byte_perm(s4[j], 0, 0x1010);       // low half  -> columns 16j+g
+          sdup[2 * j + 1] = __byte_perm(s4[j], 0, 0x3232);   // high half -> columns 16j+g+8
         }
-        const int sp = it_p % P_STAGES, s = it_ab % AB_STAGES;
-        if (!timed_out && !tc_mbar_wait(bar_full_p + 8 * sp, (it_p / P_STAGES) & 1)) timed_out = true;
-        if (!timed_out && !tc_mbar_wait(bar_empty_ab + 8 * s, ((it_ab / AB_STAGES) & 1) ^ 1)) timed_out = true;
-        const uint32_t pk = sbase + OFF_P + sp * P_BYTES + (blk_local >> 1) * (P_BYTES / 2) + (blk_local & 1) * 512 +
-                            lane * 16;
-        const uint32_t btile = sbase + OFF_B + s * B_BYTES + (uint32_t)(blk_local * 64 + g) * 128 + 4 * c;
-        {
-          uint4 w4 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-          if (valid) w4 = tc_lds128(pk + kt * 1024);
-          const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
-          const uint32_t a_lo = btile + ((uint32_t)((2 * kt) ^ g) << 4), a_hi = btile + ((uint32_t)((2 * kt + 1) ^ g) << 4);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t qw = wq[j], qs = wq[j] >> 8;
-            uint32_t v;
-            __half2 r;
-            v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 2c, 2c+1
-            r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
-            tc_sts32(a_lo + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
-            v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 2c+8, 2c+9
-            r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
-            tc_sts32(a_hi + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
-            v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 2c, 2c+1
-            r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
-            tc_sts32(a_lo + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
-            v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 2c+8, 2c+9
-            r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
-            tc_sts32(a_hi + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
+        if (it + DEQ_SETS < total_it) {
+          const int blk2 = (((int)blockIdx.x + ti2 * (int)gridDim.x) / p.mtiles) * 4 + blk_local;
+          wnext[0] = wnext[1] = kZero;
+          if (blk2 < nblk) {
+            snext = ld_nc16(sbase_g + (size_t)blk2 * 8 + (size_t)(kb2 >> 1) * srow_u4);
+            const uint4* src = pbase + (size_t)kb2 * 4 * prow_u4 + (size_t)blk2 * 32;
+            wnext[0] = ld_nc16(src);
+            wnext[1] = ld_nc16(src + prow_u4);
           }
         }
-        // make the generic-proxy stores visible to the tensor core's async-proxy reads, then signal
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          tc_mbar_arrive(bar_full_b + 8 * s);
-          tc_mbar_arrive(bar_empty_p + 8 * sp);
+        ti = ti2; kb = kb2;
+        kb2 += DEQ_SETS;
+        while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
+      }
+      const int s = it % AB_STAGES;
+      if (!timed_out && !tc_mbar_wait(bar_empty_ab + 8 * s, ((it / AB_STAGES) & 1) ^ 1)) timed_out = true;
+      const uint32_t btile = sbase + OFF_B + s * B_BYTES + (uint32_t)(blk_local * 64 + g) * 128 + 4 * c;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int kt = kt0 + u;
+        const uint32_t wq[4] = {w4[u].x, w4[u].y, w4[u].z, w4[u].w};
+        const uint32_t a_lo = btile + ((uint32_t)((2 * kt) ^ g) << 4), a_hi = btile + ((uint32_t)((2 * kt + 1) ^ g) << 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t qw = wq[j], qs = wq[j] >> 8;
+          uint32_t v;
+          __half2 r;
+          v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 2c, 2c+1
+          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
+          tc_sts32(a_lo + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
+          v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 2c+8, 2c+9
+          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j]));
+          tc_sts32(a_hi + (16 * j) * 128, *reinterpret_cast<uint32_t*>(&r));
+          v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 2c, 2c+1
+          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
+          tc_sts32(a_lo + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
+          v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 2c+8, 2c+9
+          r = __hmul2(*reinterpret_cast<__half2*>(&v), *reinterpret_cast<const __half2*>(&sdup[2 * j + 1]));
+          tc_sts32(a_hi + (16 * j + 8) * 128, *reinterpret_cast<uint32_t*>(&r));
         }
       }
+      // make the generic-proxy stores visible to the tensor core's async-proxy reads, then signal
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) tc_mbar_arrive(bar_full + 8 * s);
     }
   }
 
@@ -439,31 +531,6 @@ struct TcSwapParams {
 __device__ __forceinline__ void tcs_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// One poll of two barriers at once, so that the two shared-memory round trips overlap: bit 0 / bit 1 of the result
-// say which phase has completed.
-__device__ __forceinline__ uint32_t tcs_try_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred pa, pb;\n\t.reg .u32 ra, rb;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 pa, [%1], %2;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 pb, [%3], %4;\n\t"
-      "selp.u32 ra, 1, 0, pa;\n\t"
-      "selp.u32 rb, 2, 0, pb;\n\t"
-      "or.b32 %0, ra, rb;\n\t}"
-      : "=r"(ok)
-      : "r"(bar_a), "r"(par_a), "r"(bar_b), "r"(par_b)
-      : "memory");
-  return ok;
-}
-__device__ __forceinline__ bool tcs_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b) {
-  uint32_t done = 0;
-  for (int it = 0; it < tc::WAIT_POLLS; ++it) {
-    done |= tcs_try_wait2(bar_a, par_a, bar_b, par_b);
-    if (done == 3) return true;
-  }
-  return false;
 }
 
 // The four MMAs of one 64-k stage, the commit that releases the stage, and one poll of the NEXT stage's barrier, in one
@@ -687,7 +754,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
       while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
 
       const int sp = it % P_STAGES, s = it % STAGES;
-      if (!timed_out && !tcs_wait2(bar_full_p + 8 * sp, (it / P_STAGES) & 1, bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1))
+      if (!timed_out && !tc_wait2(bar_full_p + 8 * sp, (it / P_STAGES) & 1, bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1))
         timed_out = true;
       tc_fence_after();
       uint32_t wq[4][2];
@@ -894,7 +961,7 @@ int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D,
   if (swap_on && m <= 128) return launch_gemm_tc_swap(a, A, lda, D, m, stream);
   EncodeTiledFn enc = tc_encode_fn();
   if (!enc) return cuda_fail(cudaErrorNotSupported);
-  CUtensorMap amap, wmap;
+  CUtensorMap amap;
   {
     cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)m};
     cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
@@ -905,18 +972,8 @@ int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cuda_fail(cudaErrorInvalidValue);
   }
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)(2 * a.n), (cuuint64_t)(a.k / 16)};
-    cuuint64_t strides[1] = {(cuuint64_t)(2 * a.n) * 4};
-    cuuint32_t box[2] = {256, 4};
-    cuuint32_t estr[2] = {1, 1};
-    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.B), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return cuda_fail(cudaErrorInvalidValue);
-  }
   TcParams p;
-  p.S = (const uint4*)a.s; p.bias = (const __half*)a.bias; p.D = D; p.ldd = a.ldd;
+  p.B = (const uint4*)a.B; p.S = (const uint4*)a.s; p.bias = (const __half*)a.bias; p.D = D; p.ldd = a.ldd;
   p.M = (int)m; p.N = (int)a.n; p.n_out = (int)a.n_out; p.K = (int)a.k;
   // 256-row tiles share each dequantised weight tile between two MMAs; use them once they still fill the GPU
   p.ntiles = (int)((a.n + BN - 1) / BN);
@@ -936,9 +993,9 @@ int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D,
   const int sms = device_info().sm_count;
   const int grid = (int)(tiles < sms ? tiles : sms);
   if (H == 1)
-    w4a16_gemm_tc_kernel<1><<<grid, Cfg<1>::THREADS, Cfg<1>::SMEM_BYTES, stream>>>(p, amap, wmap);
+    w4a16_gemm_tc_kernel<1><<<grid, Cfg<1>::THREADS, Cfg<1>::SMEM_BYTES, stream>>>(p, amap);
   else
-    w4a16_gemm_tc_kernel<2><<<grid, Cfg<2>::THREADS, Cfg<2>::SMEM_BYTES, stream>>>(p, amap, wmap);
+    w4a16_gemm_tc_kernel<2><<<grid, Cfg<2>::THREADS, Cfg<2>::SMEM_BYTES, stream>>>(p, amap);
   return launch_status();
 }
 
