@@ -494,25 +494,26 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap)
 // memory and the MMA reads it from there.  Only the packed words (4 KB) and the activation tile cross shared memory.
 // The accumulator holds D^T: the epilogue stores, per batch row, 32 adjacent columns per warp (64-byte segments).
 namespace tcs {
-constexpr int BNW = 128, BK = 64;
-constexpr int P_BYTES = (BK / 16) * (2 * BNW) * 4;   // 4 KB: 4 packed rows x 256 words
-constexpr int STAGES = 6, P_STAGES = 16;
+constexpr int BNW = 128, BK = 128;              // one stage = one scale group: the hand-offs between the warp roles,
+                                                // which bound this kernel, are paid once per 128 k
+constexpr int P_BYTES = (BK / 16) * (2 * BNW) * 4;   // 8 KB: 8 packed rows x 256 words
+constexpr int STAGES = 4, P_STAGES = 8;
 constexpr int NSETS = 4;                        // dequantise warp sets; set t converts k-blocks t, t + NSETS, ...
 constexpr int DEQ_WARPS = 4;                    // warps per set: one per 32-lane quarter of tensor memory
 constexpr int FIRST_DEQ_WARP = 7;
 constexpr int OFF_P = 0;
 constexpr int OFF_BAR = OFF_P + P_STAGES * P_BYTES;
 constexpr int NUM_BARS = 2 * STAGES + 2 * P_STAGES + 4;
-constexpr int OFF_X = OFF_BAR + 1024;           // activation ring: STAGES stages of Mb x 128 bytes
+constexpr int OFF_X = OFF_BAR + 1024;           // activation ring: STAGES stages of two [Mb x 64 k] swizzled sub-tiles
 constexpr int THREADS = (FIRST_DEQ_WARP + NSETS * DEQ_WARPS) * 32;
 constexpr int TMEM_COLS = 512;                  // two accumulators of up to 128 columns, then the weight-tile ring
-constexpr int TMEM_W0 = 256;                    // weight tile of stage s: columns TMEM_W0 + 32 s (64 k as 32 half2 columns)
-static_assert(TMEM_W0 + STAGES * 32 <= TMEM_COLS, "tensor memory budget");
+constexpr int TMEM_W0 = 256;                    // weight tile of stage s: columns TMEM_W0 + 64 s (128 k as 64 half2 columns)
+static_assert(TMEM_W0 + STAGES * (BK / 2) <= TMEM_COLS, "tensor memory budget");
 static_assert(NUM_BARS * 8 + 16 <= 1024, "barrier block");
 static_assert(THREADS <= 1024, "block size");
 // at least 120 KB, so that two CTAs (each allocates all 512 tensor-memory columns) can never share an SM
 inline int smem_bytes(int Mb) {
-  const int need = OFF_X + STAGES * Mb * 128 + 1024;
+  const int need = OFF_X + STAGES * Mb * (BK * 2) + 1024;
   return need < 120 * 1024 ? 120 * 1024 : need;
 }
 }  // namespace tcs
@@ -533,28 +534,37 @@ __device__ __forceinline__ void tcs_cluster_sync() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// The four MMAs of one 64-k stage, the commit that releases the stage, and one poll of the NEXT stage's barrier, in one
-// block: the poll is issued first and its result read last, so its latency hides behind the issue of the MMAs instead
-// of adding to the single issuing thread's serial time per stage.  Returns whether the next stage was already full.
-__device__ __forceinline__ uint32_t tcs_issue_stage(uint32_t tmem_d, uint32_t tmem_w, uint64_t xdesc, uint32_t idesc,
-                                                    uint32_t accumulate, uint32_t bar_release, uint32_t bar_next,
-                                                    uint32_t par_next) {
+// The eight MMAs of one 128-k stage, the commit that releases the stage, and one poll of the NEXT stage's barrier, in
+// one block: the poll is issued first and its result read last, so its latency hides behind the issue of the MMAs
+// instead of adding to the single issuing thread's serial time per stage.  The weight operand comes from tensor memory
+// (8 columns per K=16 step), the activation operand from two swizzled [Mb x 64 k] sub-tiles in shared memory.
+// Returns whether the next stage was already full.
+__device__ __forceinline__ uint32_t tcs_issue_stage(uint32_t tmem_d, uint32_t tmem_w, uint64_t xdesc0, uint64_t xdesc1,
+                                                    uint32_t idesc, uint32_t accumulate, uint32_t bar_release,
+                                                    uint32_t bar_next, uint32_t par_next) {
   uint32_t ok;
   asm volatile(
-      "{\n\t.reg .pred p, q, t;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b64 b1, b2, b3;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 q, [%7], %8;\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
+      "{\n\t.reg .pred p, q, t;\n\t.reg .b32 a1, a2, a3, a4, a5, a6, a7;\n\t.reg .b64 b1, b2, b3, c1, c2, c3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
       "setp.eq.b32 t, 0, 0;\n\t"
-      "add.u32 a1, %2, 8;\n\tadd.u32 a2, %2, 16;\n\tadd.u32 a3, %2, 24;\n\t"
+      "add.u32 a1, %2, 8;\n\tadd.u32 a2, %2, 16;\n\tadd.u32 a3, %2, 24;\n\tadd.u32 a4, %2, 32;\n\t"
+      "add.u32 a5, %2, 40;\n\tadd.u32 a6, %2, 48;\n\tadd.u32 a7, %2, 56;\n\t"
       "add.u64 b1, %3, 2;\n\tadd.u64 b2, %3, 4;\n\tadd.u64 b3, %3, 6;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, p;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], b1, %4, t;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], b2, %4, t;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], b3, %4, t;\n\t"
-      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t"
+      "add.u64 c1, %4, 2;\n\tadd.u64 c2, %4, 4;\n\tadd.u64 c3, %4, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %5, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], b1, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], b2, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], b3, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a4], %4, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a5], c1, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a6], c2, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a7], c3, %5, t;\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(ok)
-      : "r"(tmem_d), "r"(tmem_w), "l"(xdesc), "r"(idesc), "r"(accumulate), "r"(bar_release), "r"(bar_next), "r"(par_next)
+      : "r"(tmem_d), "r"(tmem_w), "l"(xdesc0), "l"(xdesc1), "r"(idesc), "r"(accumulate), "r"(bar_release),
+        "r"(bar_next), "r"(par_next)
       : "memory");
   return ok;
 }
@@ -574,16 +584,17 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
   const uint32_t bar_full_p = bar_empty + 8 * STAGES, bar_empty_p = bar_full_p + 8 * P_STAGES;
   const uint32_t bar_tmem_full = bar_empty_p + 8 * P_STAGES, bar_tmem_empty = bar_tmem_full + 16;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + NUM_BARS * 8);
-  const uint32_t x_bytes = (uint32_t)p.Mb * (BK * 2);
+  const uint32_t x_half = (uint32_t)p.Mb * 128;   // one [Mb x 64 k] sub-tile
+  const uint32_t x_bytes = 2 * x_half;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // a cluster of p.split CTAs owns one column tile at a time; CTA `rank` of it reduces k-blocks [kb0, kb0 + KB),
-  // cut on scale-group boundaries (two k-blocks per group)
+  // a cluster of p.split CTAs owns one column tile at a time; CTA `rank` of it reduces k-blocks (= scale groups)
+  // [kb0, kb0 + KB)
   const int rank = (int)blockIdx.x % p.split;
   const int tile0 = (int)blockIdx.x / p.split, tile_step = (int)gridDim.x / p.split;
   const int groups = p.K / 128;
-  const int kb0 = 2 * (int)((long long)groups * rank / p.split);
-  const int KB = 2 * (int)((long long)groups * (rank + 1) / p.split) - kb0;
+  const int kb0 = (int)((long long)groups * rank / p.split);
+  const int KB = (int)((long long)groups * (rank + 1) / p.split) - kb0;
   const int my_tiles = (tile0 < p.ntiles) ? (p.ntiles - 1 - tile0) / tile_step + 1 : 0;
   const int total_it = my_tiles * KB;
   // instruction descriptor: D fp32, A/B fp16, both K-major, M = 128 (weight columns), N = Mb (batch rows)
@@ -628,7 +639,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
           const int sp = it % P_STAGES;
           if (!timed_out && !tc_mbar_wait(bar_empty_p + 8 * sp, ((it / P_STAGES) & 1) ^ 1)) timed_out = true;
           tc_mbar_expect_tx(bar_full_p + 8 * sp, P_BYTES);
-          tc_tma_2d(sbase + OFF_P + sp * P_BYTES, &wmap, nt * (2 * BNW), (kb0 + kb) * 4, bar_full_p + 8 * sp);
+          tc_tma_2d(sbase + OFF_P + sp * P_BYTES, &wmap, nt * (2 * BNW), (kb0 + kb) * (BK / 16), bar_full_p + 8 * sp);
         }
       }
     }
@@ -641,6 +652,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
         if (!timed_out && !tc_mbar_wait(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1)) timed_out = true;
         tc_mbar_expect_tx(bar_full + 8 * s, x_bytes);
         tc_tma_2d(sbase + OFF_X + s * x_bytes, &xmap, (kb0 + kb) * BK, 0, bar_full + 8 * s);
+        tc_tma_2d(sbase + OFF_X + s * x_bytes + x_half, &xmap, (kb0 + kb) * BK + 64, 0, bar_full + 8 * s);
         if (++kb == KB) kb = 0;
       }
     }
@@ -659,8 +671,9 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
           if (!ready && !timed_out && !tc_mbar_wait(bar_full + 8 * s, (it / STAGES) & 1)) timed_out = true;
           tc_fence_after();
           const int s1 = (s + 1 == STAGES) ? 0 : s + 1;
-          ready = tcs_issue_stage(tmem_d, tmem_base + TMEM_W0 + s * 32, tc_smem_desc(sbase + OFF_X + s * x_bytes),
-                                  idesc, kb != 0 ? 1u : 0u, bar_empty + 8 * s, bar_full + 8 * s1, ((it + 1) / STAGES) & 1);
+          ready = tcs_issue_stage(tmem_d, tmem_base + TMEM_W0 + s * (BK / 2), tc_smem_desc(sbase + OFF_X + s * x_bytes),
+                                  tc_smem_desc(sbase + OFF_X + s * x_bytes + x_half), idesc, kb != 0 ? 1u : 0u,
+                                  bar_empty + 8 * s, bar_full + 8 * s1, ((it + 1) / STAGES) & 1);
           if (it + 1 >= total_it) ready = 0;      // that poll looked at a phase nobody will complete
         }
         tc_commit(bar_tmem_full + 8 * buf);
@@ -734,7 +747,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
     if (set < total_it) {
       const int blk = (tile0 + ti * tile_step) * 2 + blk_local;
       if (blk < nblk)
-        snext = __ldg(reinterpret_cast<const uint2*>(sbase_g + (size_t)blk * 8 + (size_t)((kb0 + kb) >> 1) * srow_u4) + (q & 1));
+        snext = __ldg(reinterpret_cast<const uint2*>(sbase_g + (size_t)blk * 8 + (size_t)(kb0 + kb) * srow_u4) + (q & 1));
     }
     for (int it = set; it < total_it; it += NSETS) {
       const int blk = (tile0 + ti * tile_step) * 2 + blk_local;
@@ -747,7 +760,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
       if (it + NSETS < total_it) {
         const int blk2 = (tile0 + ti2 * tile_step) * 2 + blk_local;
         if (blk2 < nblk)
-          snext = __ldg(reinterpret_cast<const uint2*>(sbase_g + (size_t)blk2 * 8 + (size_t)((kb0 + kb2) >> 1) * srow_u4) + (q & 1));
+          snext = __ldg(reinterpret_cast<const uint2*>(sbase_g + (size_t)blk2 * 8 + (size_t)(kb0 + kb2) * srow_u4) + (q & 1));
       }
       ti = ti2; kb = kb2;
       kb2 += NSETS;
@@ -757,44 +770,48 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
       if (!timed_out && !tc_wait2(bar_full_p + 8 * sp, (it / P_STAGES) & 1, bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1))
         timed_out = true;
       tc_fence_after();
-      uint32_t wq[4][2];
       const uint32_t pk = sbase + OFF_P + sp * P_BYTES + blk_local * 512 + lane * 16 + (q & 1) * 8;
 #pragma unroll
-      for (int kt = 0; kt < 4; ++kt) {
-        wq[kt][0] = wq[kt][1] = 0x88888888u;
-        if (valid)
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(wq[kt][0]), "=r"(wq[kt][1]) : "r"(pk + kt * 1024) : "memory");
-      }
-#pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        uint32_t r[16];
-        const __half2 s_lo = *reinterpret_cast<const __half2*>(&sdup[2 * jj]);
-        const __half2 s_hi = *reinterpret_cast<const __half2*>(&sdup[2 * jj + 1]);
+      for (int hk = 0; hk < 2; ++hk) {            // the two 64-k halves of the stage: packed rows 4 hk .. 4 hk + 3
+        uint32_t wq[4][2];
 #pragma unroll
         for (int kt = 0; kt < 4; ++kt) {
-          const uint32_t qw = wq[kt][jj], qs = qw >> 8;
-          uint32_t v;
-          __half2 h;
-          v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 16kt + 2c, 2c+1
-          h = __hmul2(*reinterpret_cast<__half2*>(&v), s_lo);
-          r[4 * kt + 0] = *reinterpret_cast<uint32_t*>(&h);
-          v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 16kt + 2c, 2c+1
-          h = __hmul2(*reinterpret_cast<__half2*>(&v), s_hi);
-          r[4 * kt + 1] = *reinterpret_cast<uint32_t*>(&h);
-          v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 16kt + 2c+8, 2c+9
-          h = __hmul2(*reinterpret_cast<__half2*>(&v), s_lo);
-          r[4 * kt + 2] = *reinterpret_cast<uint32_t*>(&h);
-          v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 16kt + 2c+8, 2c+9
-          h = __hmul2(*reinterpret_cast<__half2*>(&v), s_hi);
-          r[4 * kt + 3] = *reinterpret_cast<uint32_t*>(&h);
+          wq[kt][0] = wq[kt][1] = 0x88888888u;
+          if (valid)
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];"
+                         : "=r"(wq[kt][0]), "=r"(wq[kt][1]) : "r"(pk + (4 * hk + kt) * 1024) : "memory");
         }
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32 + jj * 16) << 16) + TMEM_W0 + s * 32;
-        asm volatile(
-            "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "
-            "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-            ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-              "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-            : "memory");
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          uint32_t r[16];
+          const __half2 s_lo = *reinterpret_cast<const __half2*>(&sdup[2 * jj]);
+          const __half2 s_hi = *reinterpret_cast<const __half2*>(&sdup[2 * jj + 1]);
+#pragma unroll
+          for (int kt = 0; kt < 4; ++kt) {
+            const uint32_t qw = wq[kt][jj], qs = qw >> 8;
+            uint32_t v;
+            __half2 h;
+            v = nib_pair_to_half2_m8(qw);                               // n = 16j+g,   k = 16kt + 2c, 2c+1
+            h = __hmul2(*reinterpret_cast<__half2*>(&v), s_lo);
+            r[4 * kt + 0] = *reinterpret_cast<uint32_t*>(&h);
+            v = nib_pair_to_half2_m8(qs);                               // n = 16j+g+8, k = 16kt + 2c, 2c+1
+            h = __hmul2(*reinterpret_cast<__half2*>(&v), s_hi);
+            r[4 * kt + 1] = *reinterpret_cast<uint32_t*>(&h);
+            v = nib_pair_hi_to_half2_m8(qw);                            // n = 16j+g,   k = 16kt + 2c+8, 2c+9
+            h = __hmul2(*reinterpret_cast<__half2*>(&v), s_lo);
+            r[4 * kt + 2] = *reinterpret_cast<uint32_t*>(&h);
+            v = nib_pair_hi_to_half2_m8(qs);                            // n = 16j+g+8, k = 16kt + 2c+8, 2c+9
+            h = __hmul2(*reinterpret_cast<__half2*>(&v), s_hi);
+            r[4 * kt + 3] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32 + jj * 16) << 16) + TMEM_W0 + s * (BK / 2) + hk * 32;
+          asm volatile(
+              "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "
+              "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+              ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+              : "memory");
+        }
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
@@ -878,6 +895,34 @@ bool gemm_tc_supported(int64_t m, int64_t n, int64_t k) {
 
 size_t gemm_tc_scratch_bytes(int64_t, int64_t, int64_t) { return 0; }
 
+// Clusters of `split` CTAs of the small-batch kernel that can be resident together (0 if the query fails).
+static int max_active_clusters(int split, int smem) {
+  static int cache[64][9][2];                   // [device][split] -> {smem the answer is for, answer}
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || split < 1 || split > 8) return 0;
+  if (cache[dev][split][0] == smem) return cache[dev][split][1];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(split * 64));
+  cfg.blockDim = dim3(tcs::THREADS);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, w4a16_gemm_tc_swap_kernel, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  cache[dev][split][0] = smem;
+  cache[dev][split][1] = n;
+  return n;
+}
+
 static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m,
                                cudaStream_t stream) {
   using namespace tcs;
@@ -888,7 +933,7 @@ static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda
   {
     cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)m};
     cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)Mb};
+    cuuint32_t box[2] = {64, (cuuint32_t)Mb};
     cuuint32_t estr[2] = {1, 1};
     if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(A), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -898,7 +943,7 @@ static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda
   {
     cuuint64_t dims[2] = {(cuuint64_t)(2 * a.n), (cuuint64_t)(a.k / 16)};
     cuuint64_t strides[1] = {(cuuint64_t)(2 * a.n) * 4};
-    cuuint32_t box[2] = {256, 4};
+    cuuint32_t box[2] = {256, (cuuint32_t)(BK / 16)};
     cuuint32_t estr[2] = {1, 1};
     if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.B), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -910,6 +955,18 @@ static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda
   p.M = (int)m; p.Mb = Mb; p.N = (int)a.n; p.n_out = (int)a.n_out; p.K = (int)a.k;
   p.ntiles = (int)((a.n + BNW - 1) / BNW);
   p.status_word = a.status_word;
+  {
+    // function attributes are per device
+    static thread_local bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_set[dev]) {
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          smem_bytes(128)));
+      attr_set[dev] = true;
+    }
+  }
   const int sms = device_info().sm_count;
   // few column tiles: a cluster of `split` CTAs shares each tile, every CTA reducing a slice of k (at least four
   // scale groups), and the partial accumulators are summed through distributed shared memory
@@ -926,14 +983,11 @@ static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda
     if (split > groups) split = groups;
     if (split < 1) split = 1;
     if (split > 8) split = 8;
+    // every cluster must be resident at once (a second wave would cost more than the split gains): clusters are
+    // placed inside one GPC, so fewer fit than SMs / split suggests
+    while (split > 1 && forced <= 0 && max_active_clusters(split, smem_bytes(Mb)) < p.ntiles) --split;
   }
   p.split = split;
-  static thread_local bool attr_set = false;
-  if (!attr_set) {
-    UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        smem_bytes(128)));
-    attr_set = true;
-  }
   if (split == 1) {
     const int grid = p.ntiles < sms ? p.ntiles : sms;
     w4a16_gemm_tc_swap_kernel<<<grid, THREADS, smem_bytes(Mb), stream>>>(p, xmap, wmap);
@@ -981,13 +1035,18 @@ int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D,
   const int H = (m > BMH && ((m + 2 * BMH - 1) / (2 * BMH)) * (int64_t)p.ntiles >= sms_) ? 2 : 1;
   p.mtiles = (int)((m + H * BMH - 1) / (H * BMH));
   p.status_word = a.status_word;
-  static thread_local bool attr_set = false;
-  if (!attr_set) {
-    UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        Cfg<1>::SMEM_BYTES));
-    UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        Cfg<2>::SMEM_BYTES));
-    attr_set = true;
+  {
+    static thread_local bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_set[dev]) {
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg<1>::SMEM_BYTES));
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg<2>::SMEM_BYTES));
+      attr_set[dev] = true;
+    }
   }
   const int64_t tiles = (int64_t)p.mtiles * p.ntiles;
   const int sms = device_info().sm_count;
