@@ -1,23 +1,31 @@
-// Prefill-regime W4A16 linear (m > 16) for sm_100a: tcgen05 tensor cores with the accumulator in TMEM and
-// the int4 -> fp16 dequantisation done in shared memory in front of the MMA.
+// Prefill-regime W4A16 linear (m > 16) for sm_100a: tcgen05 tensor cores with the accumulator in TMEM and the
+// int4 -> fp16 dequantisation done on the SM in front of the MMA.  Two kernels:
+//   w4a16_gemm_tc_kernel<H>      m > 128: activations are the 128-row operand, dequantised weights the N operand
+//                                (shared memory);
+//   w4a16_gemm_tc_swap_kernel    16 < m <= 128: operands swapped, dequantised weights written to tensor memory.
 //
 // Replaces the large-batch instantiations of UniQL's Marlin kernel (csrc/linear/marlin_gemm_kernel.cuh:176-740,
 // tile table :802-810), which run mma.sync with dequantisation on the same warps, while consuming the same
 // packed buffers (quantize/quantize_helpers.py:145-165 weight order, :54-62 scale order).
 //
-// Tile: (128 * H) batch rows x 256 output columns x 64 k per pipeline stage, one persistent CTA per SM.  H = 2 for
-// m > 128: the two 128-row halves are separate M=128 MMAs that read the same dequantised weight tile, which halves
-// the dequantisation work and the shared-memory writes per tensor-core cycle; their accumulators are the two 256-column
-// halves of TMEM.  H = 1 (m <= 128) double-buffers one accumulator across tiles instead.
-//   warp 0      TMA producer: activation tile [128 x 64] fp16 (128B-swizzled, K-major) and the packed weight
-//               tile [4 packed rows x 512 words] (two boxes of 256 words); no multicast.
-//   warp 1      allocates TMEM (2 x 256 fp32 columns), issues tcgen05.mma kind::f16 (M=128, N=256, K=16) from one
-//               elected lane, commits stage-release and accumulator-ready barriers.
-//   warps 2-5   epilogue: tcgen05.ld (32 lanes x 32 columns), + bias, fp32 -> fp16, row-major stores; overlaps the
-//               next tile's main loop through the second TMEM accumulator.
-//   warps 6-21  dequantise: 16-byte reads of packed words, exact (q - 8) in fp16 via LOP3 + HSUB2/HFMA2, one
-//               HMUL2 by the group scale (bit-identical to the reference's dequantised weight), 32-bit stores
-//               into the K-major 128B-swizzled B tile (bank-conflict free), fence.proxy.async, arrive.
+// w4a16_gemm_tc_kernel<H>.  Tile: (128 * H) batch rows x 256 output columns x 64 k per pipeline stage, one persistent
+// CTA per SM.  H = 2 when the 256-row tiles still fill the GPU: the two 128-row halves are separate M=128 MMAs that
+// read the same dequantised weight tile, which halves the dequantisation work and the shared-memory writes per
+// tensor-core cycle; their accumulators are the two 256-column halves of TMEM.  H = 1 double-buffers one accumulator
+// across tiles instead.
+//   warp 0      TMA producer: activation tile(s) [128 x 64] fp16 (128B-swizzled, K-major); no multicast.
+//   warp 1      allocates TMEM (2 x 256 fp32 columns); one elected lane issues, per stage, one block of
+//               tcgen05.mma kind::f16 (M=128, N=256, K=16) + the commit that releases the stage + a poll of the next
+//               stage's barrier whose latency hides behind the MMA issue.
+//   warps 2..   epilogue (4 per 128-row half): tcgen05.ld (32 lanes x 32 columns), + bias, fp32 -> fp16, row-major
+//               stores; with H = 1 it overlaps the next tile's main loop through the second TMEM accumulator.
+//   16 warps    dequantise, as two sets of eight that convert alternate stages so two stages are always in
+//               conversion: packed words straight from global memory into registers (requested two stages ahead,
+//               no hop through shared memory), exact (q - 8) in fp16 via LOP3 + HSUB2/HFMA2, one HMUL2 by the group
+//               scale (bit-identical to the reference's dequantised weight), 32-bit stores into the K-major
+//               128B-swizzled B tile (bank-conflict free), fence.proxy.async, arrive.
+// One barrier per stage collects both the TMA bytes of the activation tile and the arrivals of the dequantise warps, so
+// the issuing thread pays one wait per stage.
 // Roofline: tensor pipe (2*m*n*k flops); algorithmic bytes k*n/2 + (k/128)*n*2 + m*k*2 + m*n*2.
 // Every mbarrier wait is bounded; a wait that gives up sets UNIQL_STATUS_WAIT_TIMEOUT and the kernel drains.
 #include "common.cuh"
@@ -486,13 +494,18 @@ w4a16_gemm_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap amap)
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Small-batch variant (16 < m <= 128): operands swapped.  The dequantised weight tile [128 columns x 64 k] is the
-// 128-row MMA operand (tensor-memory lane = output column), the activation tile [Mb x 64 k] (Mb = m rounded up to 16) the
-// N operand, so the MMA is 128 x Mb x 16 and no tensor work is spent on padding rows.  Shared-memory bandwidth
-// (128 bytes per clock per SM: generic stores, TMA writes and the tensor core's operand reads all draw on it) is what
-// bounds these kernels, so the weight operand never enters shared memory: the dequantise warps write it to tensor
-// memory and the MMA reads it from there.  Only the packed words (4 KB) and the activation tile cross shared memory.
+// Small-batch variant (16 < m <= 128): operands swapped.  The dequantised weight tile [128 columns x 128 k] is the
+// 128-row MMA operand (tensor-memory lane = output column), the activation tile [Mb x 128 k] (Mb = m rounded up to 16)
+// the N operand, so the MMA is 128 x Mb x 16 and no tensor work is spent on padding rows.  The weight operand never
+// enters shared memory: the dequantise warps (four sets of four, one warp per 32-lane quarter of tensor memory, each
+// set converting every fourth stage) write it to tensor memory with tcgen05.st and the MMA reads it from there, which
+// removes the shared stores, the proxy fence and the tensor core's operand reads of it.  Only the packed words (8 KB
+// per stage, TMA) and the activation tile (two swizzled [Mb x 64 k] sub-tiles, TMA) cross shared memory.
+// What bounds this kernel is the latency of the hand-offs between the warp roles, paid once per stage: hence one scale
+// group (128 k, eight MMAs) per stage, one merged barrier per stage, and the next-stage poll fused with the MMA issue.
 // The accumulator holds D^T: the epilogue stores, per batch row, 32 adjacent columns per warp (64-byte segments).
+// With few column tiles a cluster of up to 8 CTAs shares each tile, every CTA reducing a slice of k; the partial
+// accumulators are summed in rank order through distributed shared memory (deterministic, no global scratch).
 namespace tcs {
 constexpr int BNW = 128, BK = 128;              // one stage = one scale group: the hand-offs between the warp roles,
                                                 // which bound this kernel, are paid once per 128 k
