@@ -456,6 +456,23 @@ def run_ours(args):
         p1.record(stream)
         torch.cuda.synchronize()
         prefill_us = p0.elapsed_time(p1) * 1e3 / len(gate_mods)
+        # the same projection at batch 64 (small-batch tcgen05 kernel), one launch per distinct weight set
+        x64 = torch.randn(64, HIDDEN, generator=gen, device=device).to(torch.float16)
+        o64 = torch.empty((64, gate_mods[0].out_features), dtype=torch.float16, device=device)
+        for g in gate_mods[:3]:
+            ops.w4a16_linear(x64, g.weight, g.scale, None, g.out_features, out=o64)
+        torch.cuda.synchronize()
+        g64 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g64, stream=stream):
+            for g in gate_mods:
+                ops.w4a16_linear(x64, g.weight, g.scale, None, g.out_features, out=o64)
+        g64.replay()
+        torch.cuda.synchronize()
+        p0.record(stream)
+        g64.replay()
+        p1.record(stream)
+        torch.cuda.synchronize()
+        m64_us = p0.elapsed_time(p1) * 1e3 / len(gate_mods)
         del xp, op
 
     def rank_max(v):
@@ -471,6 +488,7 @@ def run_ours(args):
         ms_e2e_graph = rank_max(ms_e2e_graph)
     gate_us = rank_max(gate_us)
     prefill_us = rank_max(prefill_us)
+    m64_us = rank_max(m64_us)
     status = ops.read_and_clear_status(device)
 
     if rank == 0:
@@ -509,6 +527,8 @@ def run_ours(args):
                              "frac_of_measured_bf16_burst": (2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12)
                              / float(measured_peaks()[2].get("bf16_tflops", 1590.0)),
                              "frac_of_nominal_2250": (2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12) / 2250.0},
+            "m64_us": {"value": m64_us, "kernel": f"w4a16_gemm_tc_swap_kernel {n_gate}x{HIDDEN} m=64 per GPU",
+                       "weight_gbs": (n_gate * HIDDEN / 2 + n_gate * HIDDEN / 64) / (m64_us * 1e-6) / 1e9},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "kernel_status_word": status,
