@@ -59,10 +59,17 @@ template <int H> struct Cfg {
 };
 // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128
 constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BMH >> 4) << 24);
+// A blocking wait is a loop of mbarrier.try_wait with a suspend-time hint: the hardware parks the thread until the
+// phase completes or the hint runs out, so a waiting warp issues almost nothing (polling used to be half of all issued
+// instructions of the prefill kernel).  The loop gives up after WAIT_POLLS tries: about two seconds.
 #ifndef UNIQL_TC_WAIT_POLLS
-#define UNIQL_TC_WAIT_POLLS (1 << 22)
+#define UNIQL_TC_WAIT_POLLS (1 << 17)
+#endif
+#ifndef UNIQL_TC_WAIT_HINT_NS
+#define UNIQL_TC_WAIT_HINT_NS 16384
 #endif
 constexpr int WAIT_POLLS = UNIQL_TC_WAIT_POLLS;
+constexpr uint32_t WAIT_HINT_NS = UNIQL_TC_WAIT_HINT_NS;
 }  // namespace tc
 
 struct TcParams {
@@ -92,10 +99,10 @@ __device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(tc::WAIT_HINT_NS)
         : "memory");
     if (ok) return true;
   }
@@ -134,19 +141,18 @@ __device__ __forceinline__ uint4 tc_lds128(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
 }
-// Wait used by warps that sit idle for most of a tile: back off between polls to leave issue slots to the others.
+// Wait used by warps that sit idle for most of a tile (same parked wait; kept as a separate name for the call sites).
 __device__ __forceinline__ bool tc_mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
   for (int it = 0; it < tc::WAIT_POLLS; ++it) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(tc::WAIT_HINT_NS)
         : "memory");
     if (ok) return true;
-    __nanosleep(64);
   }
   return false;
 }
@@ -170,13 +176,13 @@ __device__ __forceinline__ uint32_t tc_try_wait2(uint32_t bar_a, uint32_t par_a,
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred pa, pb;\n\t.reg .u32 ra, rb;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 pa, [%1], %2;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 pb, [%3], %4;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 pa, [%1], %2, %5;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 pb, [%3], %4, %5;\n\t"
       "selp.u32 ra, 1, 0, pa;\n\t"
       "selp.u32 rb, 2, 0, pb;\n\t"
       "or.b32 %0, ra, rb;\n\t}"
       : "=r"(ok)
-      : "r"(bar_a), "r"(par_a), "r"(bar_b), "r"(par_b)
+      : "r"(bar_a), "r"(par_a), "r"(bar_b), "r"(par_b), "r"(tc::WAIT_HINT_NS)
       : "memory");
   return ok;
 }
@@ -201,7 +207,7 @@ __device__ __forceinline__ uint32_t tc_issue_stage(uint32_t tmem_d, uint64_t ade
   if (H == 1) {
     asm volatile(
         "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 q, [%7], %8;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%7], %8;\n\t"
         "setp.ne.b32 p, %5, 0;\n\t"
         "setp.eq.b32 t, 0, 0;\n\t"
         "add.u64 a1, %2, 2;\n\tadd.u64 a2, %2, 4;\n\tadd.u64 a3, %2, 6;\n\t"
@@ -219,7 +225,7 @@ __device__ __forceinline__ uint32_t tc_issue_stage(uint32_t tmem_d, uint64_t ade
   } else {
     asm volatile(
         "{\n\t.reg .pred p, q, t;\n\t.reg .b64 a1, a2, a3, c1, c2, c3, b1, b2, b3;\n\t.reg .b32 d1;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
         "setp.ne.b32 p, %6, 0;\n\t"
         "setp.eq.b32 t, 0, 0;\n\t"
         "add.u32 d1, %1, 256;\n\t"
@@ -558,7 +564,7 @@ __device__ __forceinline__ uint32_t tcs_issue_stage(uint32_t tmem_d, uint32_t tm
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p, q, t;\n\t.reg .b32 a1, a2, a3, a4, a5, a6, a7;\n\t.reg .b64 b1, b2, b3, c1, c2, c3;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 q, [%8], %9;\n\t"
       "setp.ne.b32 p, %6, 0;\n\t"
       "setp.eq.b32 t, 0, 0;\n\t"
       "add.u32 a1, %2, 8;\n\tadd.u32 a2, %2, 16;\n\tadd.u32 a3, %2, 24;\n\tadd.u32 a4, %2, 32;\n\t"
