@@ -181,8 +181,7 @@ def build_stack(m, rank, world, device, layers):
     """Synthetic RTN-quantised layers (seeded), sharded for this rank."""
     import torch
 
-    from uniql_b200 import tp
-    from uniql_b200.quantize import quantize_helpers as qh
+    from uniql_b200 import ops, tp
     from uniql_b200.quantize.quant_linear_layers import W4A16B16O16HadLinear, W4A16B16O16Linear
 
     def quantised(seed, n, k, cls, col=None, row=None):
@@ -192,7 +191,8 @@ def build_stack(m, rank, world, device, layers):
             w = w[col[0]:col[1]]
         if row is not None:
             w = w[:, row[0]:row[1]]
-        _, packed, scale = qh.w4a16_quantize(w.t().contiguous(), 4, 128, None, 0)
+        # RTN group-128 quantise + pack on the GPU (same bits as qh.w4a16_quantize(w.t(), 4, 128, None, 0))
+        _, packed, scale = ops.w4a16_quantize(w, n_pad=w.shape[0], want_ref=False)
         lin = cls(w.shape[1], w.shape[0], device="meta")
         lin._buffers["weight"], lin._buffers["scale"] = packed, scale
         lin._buffers["workspace"] = torch.zeros(lin.size_n // 64 * 16, dtype=torch.int32, device=device)

@@ -129,6 +129,23 @@ int uniql_w4_embedding(const int64_t* ids, int64_t n_ids, const void* W, const v
  */
 int uniql_hadamard(const void* x, void* y, int64_t rows, int64_t dim, float scale, int dtype, void* stream);
 
+/*
+ * Round-to-nearest group-128 int4 quantiser + packer on the GPU: fp16 nn.Linear weight -> the `weight` / `scale`
+ * buffers of W4A16B16O16Linear, bit-identical to the reference's CPU path.
+ * Replaces W4A16B16O16Linear.from_fp16's call of w4a16_quantize(W^T, 4, 128, scale, pad_out)
+ * (quantize/quant_linear_layers.py:50-89, quantize/quantize_helpers.py:184-241 with :88-141, :145-180).
+ *   W            fp16 [n_out, k_in] row-major with row stride ldw (elements): the nn.Linear layout, no transpose needed
+ *   group_scale  NULL for RTN (s = max|w| * 2/15 per group and column); or fp16 [ceil(k_in/128), n_out] in natural
+ *                column order when the weight is already fake-quantised on those scales (the GPTQ hand-over, :205-218)
+ *   packed       out, int32 [Kp/16, 2*n_pad], Kp = k_in rounded up to 128 (k rows past k_in quantise zeros)
+ *   scales       out, fp16 [Kp/128, n_pad], permuted inside 64-column blocks
+ *   w_ref        out or NULL, fp16 [Kp, n_pad]: the dequantised weights the reference returns alongside
+ *   n_pad        stored column count: a multiple of 64, >= n_out (the reference uses the next multiple of 256);
+ *                columns past n_out get code 0, scale 0
+ */
+int uniql_w4a16_quantize(const void* W, int64_t ldw, int64_t n_out, int64_t k_in, const void* group_scale,
+                         void* packed, void* scales, void* w_ref, int64_t n_pad, void* stream);
+
 /* Host helper: writes the base x base ±1 matrix (row-major int8) this library uses for
  * base in {12, 20, 28, 40}; `out` is a HOST pointer.  Returns UNIQL_ESHAPE for other orders. */
 int uniql_hadamard_base_matrix(int base, int8_t* out);

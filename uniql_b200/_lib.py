@@ -34,6 +34,9 @@ SYMBOLS = {
     "uniql_hadamard": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_float, _c.c_int, _c.c_void_p]),
     "uniql_hadamard_base_matrix": (_c.c_int, [_c.c_int, _c.c_void_p]),
+    "uniql_w4a16_quantize": (_c.c_int, [
+        _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+        _c.c_int64, _c.c_void_p]),
     "uniql_comm_handle_bytes": (_c.c_size_t, []),
     "uniql_comm_create": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int64, _c.POINTER(_c.c_void_p), _c.c_void_p]),
     "uniql_comm_connect": (_c.c_int, [_c.c_void_p, _c.c_void_p]),

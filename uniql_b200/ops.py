@@ -169,3 +169,42 @@ def hadamard(x: torch.Tensor, scale: float) -> torch.Tensor:
                                     _stream_handle(x.device))
     check(code, "uniql_hadamard")
     return y
+
+
+def w4a16_quantize(weight: torch.Tensor, group_scale: torch.Tensor | None = None, n_pad: int | None = None,
+                   want_ref: bool = True):
+    """Quantise and pack an nn.Linear weight [out, in] (fp16, CUDA) on the GPU.
+
+    Returns (w_ref fp16 [Kp, n_pad] or None, packed int32 [Kp/16, 2*n_pad], scales fp16 [Kp/128, n_pad]) with the
+    values of the reference's w4a16_quantize(weight.T, 4, 128, group_scale, pad_out) (quantize_helpers.py:184-241);
+    n_pad defaults to `out` rounded up to 256 as in W4A16B16O16Linear.from_fp16 (quant_linear_layers.py:65-66)."""
+    _require_cuda(weight, "weight")
+    if weight.dim() != 2:
+        raise RuntimeError("weight must be [out_features, in_features]")
+    w = weight.detach()
+    if w.dtype != torch.float16:
+        w = w.to(torch.float16)
+    if w.stride(1) != 1:
+        w = w.contiguous()
+    n_out, k_in = w.shape
+    if n_pad is None:
+        n_pad = (n_out + 255) // 256 * 256
+    kp = (k_in + 127) // 128 * 128
+    gs = None
+    if group_scale is not None:
+        _require_cuda(group_scale, "group_scale")
+        gs = group_scale.detach().to(torch.float16).contiguous()
+        if tuple(gs.shape) != (kp // 128, n_out):
+            raise RuntimeError(f"group_scale must be [{kp // 128}, {n_out}], got {tuple(gs.shape)}")
+    dev = w.device
+    packed = torch.empty((kp // 16, 2 * n_pad), dtype=torch.int32, device=dev)
+    scales = torch.empty((kp // 128, n_pad), dtype=torch.float16, device=dev)
+    w_ref = torch.empty((kp, n_pad), dtype=torch.float16, device=dev) if want_ref else None
+    with torch.cuda.device(dev):
+        code = lib().uniql_w4a16_quantize(w.data_ptr(), w.stride(0), n_out, k_in,
+                                          gs.data_ptr() if gs is not None else None,
+                                          packed.data_ptr(), scales.data_ptr(),
+                                          w_ref.data_ptr() if w_ref is not None else None, n_pad,
+                                          _stream_handle(dev))
+    check(code, "uniql_w4a16_quantize")
+    return w_ref, packed, scales

@@ -63,11 +63,18 @@ class W4A16B16O16Linear(torch.nn.Module):
         qlinear = cls(originalLayer.in_features, originalLayer.out_features, device=device)
         w = originalLayer.weight
         pad_out = (256 - w.shape[0] % 256) % 256
-        w_t = w.detach().to(torch.float16).t().contiguous()               # [Din, Dout]
-        w_ref, q_w, scale = w4a16_quantize(w_t, bits, group_size, group_scale, pad_out=pad_out)
+        if w.is_cuda:
+            # on the GPU in one pass over the [Dout, Din] weight, same bits as the host path below
+            gs = group_scale.to(device) if group_scale is not None else None
+            _, q_w, scale = ops.w4a16_quantize(w, gs, n_pad=w.shape[0] + pad_out, want_ref=False)
+            size_k, size_n = q_w.shape[0] * 16, q_w.shape[1] // 2
+        else:
+            w_t = w.detach().to(torch.float16).t().contiguous()           # [Din, Dout]
+            w_ref, q_w, scale = w4a16_quantize(w_t, bits, group_size, group_scale, pad_out=pad_out)
+            size_k, size_n = w_ref.shape
         qlinear.pad_out = pad_out
-        qlinear.size_k, qlinear.size_n = w_ref.shape
-        qlinear.pad_in = w_ref.shape[0] - w_t.shape[0]
+        qlinear.size_k, qlinear.size_n = size_k, size_n
+        qlinear.pad_in = size_k - w.shape[1]
         qlinear.max_par = 16
         qlinear.weight = q_w.to(device)
         qlinear.scale = scale.to(device)
