@@ -177,6 +177,63 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------- GPU arm
+def aux_kernels(device, stream, peak):
+    """The other kernels of the path on DRAM-sized inputs (N=1 only): embedding gather, Hadamard, quantise + pack.
+    Each entry: CUDA-event time per launch, algorithmic GB/s and its fraction of the HBM peak used for `roofline`."""
+    import torch
+
+    from uniql_b200 import ops
+
+    def timed(fn, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    def entry(us, nbytes, what):
+        gbs = nbytes / (us * 1e-6) / 1e9
+        return {"us_per_launch": us, "bytes": nbytes, "gbs": gbs, "frac_of_hbm_peak": gbs / peak, "workload": what}
+
+    out = {}
+    g = torch.Generator(device=device).manual_seed(7)
+    # embedding: Qwen2.5-7B table (152064 x 3584, 4-bit, one fp16 scale per row), 32768 random token ids
+    vocab, dim, tokens = 152064, 3584, 32768
+    table = torch.randint(-2 ** 31, 2 ** 31 - 1, (vocab, dim // 8), generator=g, device=device, dtype=torch.int64).to(torch.int32)
+    scales = (torch.rand(vocab, generator=g, device=device) * 0.01 + 0.001).to(torch.float16)
+    ids = torch.randint(0, vocab, (tokens,), generator=g, device=device, dtype=torch.int64)
+    us = timed(lambda: ops.w4_embedding(ids, table, scales))
+    out["w4_embedding"] = entry(us, tokens * (dim // 2 + 2 + 8 + 2 * dim), f"{tokens} ids into a {vocab}x{dim} table")
+    del table, scales, ids
+    # Hadamard 14336 = 28 x 512 (down_proj input): 16384 rows (prefill) and 1 row (decode latency)
+    rows, hd = 16384, 14336
+    x = torch.randn(rows, hd, generator=g, device=device).to(torch.float16)
+    us = timed(lambda: ops.hadamard(x, hd ** -0.5))
+    out["hadamard_14336_rows16384"] = entry(us, 2 * rows * hd * 2, f"{rows} x {hd} fp16 in and out")
+    x1 = x[:1].contiguous()
+    us = timed(lambda: ops.hadamard(x1, hd ** -0.5), reps=20)
+    out["hadamard_14336_rows1"] = entry(us, 2 * hd * 2, "1 row: launch and latency bound, not a bandwidth figure")
+    del x, x1
+    # RTN quantise + pack of one gate projection (no w_ref output); two weights in turn
+    n, k = SHAPES["gate"]
+    ws = [(torch.randn(n, k, generator=g, device=device) * 0.02).to(torch.float16) for _ in range(2)]
+    state = {"i": 0}
+
+    def quant():
+        state["i"] ^= 1
+        ops.w4a16_quantize(ws[state["i"]], n_pad=n, want_ref=False)
+
+    us = timed(quant, reps=6)
+    out["w4a16_quantize"] = entry(us, n * k * 2 + n * k // 2 + (k // 128) * n * 2,
+                                  f"{n}x{k} fp16 weight -> packed int4 + scales (includes the output allocation)")
+    return out
+
+
 def build_stack(m, rank, world, device, layers):
     """Synthetic RTN-quantised layers (seeded), sharded for this rank."""
     import torch
@@ -474,6 +531,8 @@ def run_ours(args):
         torch.cuda.synchronize()
         m64_us = p0.elapsed_time(p1) * 1e3 / len(gate_mods)
         del xp, op
+        aux = (aux_kernels(device, stream, measured_peaks()[0])
+               if (world == 1 and not os.environ.get("UNIQL_BENCH_NO_AUX")) else None)
 
     def rank_max(v):
         if world == 1:
@@ -529,6 +588,7 @@ def run_ours(args):
                              "frac_of_nominal_2250": (2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12) / 2250.0},
             "m64_us": {"value": m64_us, "kernel": f"w4a16_gemm_tc_swap_kernel {n_gate}x{HIDDEN} m=64 per GPU",
                        "weight_gbs": (n_gate * HIDDEN / 2 + n_gate * HIDDEN / 64) / (m64_us * 1e-6) / 1e9},
+            "aux_kernels": aux,
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "kernel_status_word": status,

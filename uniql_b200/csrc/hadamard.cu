@@ -14,14 +14,21 @@
 #include "common.cuh"
 #include "linear_internal.cuh"
 
+#include <type_traits>
+#include <utility>
+
 namespace uniql {
 
 struct HadSigns {
   uint64_t row[64];   // bit a' of row[a] set  <=>  H[a][a'] = -1
 };
 
-// ------------------------------------------------------------- base matrices (host, deterministic)
-static int legendre(int a, int q) {
+// ------------------------------------------------------------- base matrices (deterministic, one definition)
+// Paley I for 12 and 20, Paley II for 28, H_2 (x) H_20 for 40, element by element as constexpr functions: the host
+// uses them to fill sign masks and the exported matrix, the row kernel instantiates them at compile time so that its
+// base pass is plain FADD / FSUB with the signs folded into the instructions (a sign mask read at run time costs an
+// extra XOR per term and made that pass three quarters of the kernel's instructions).
+__host__ __device__ constexpr int c_legendre(int a, int q) {
   a %= q;
   if (a < 0) a += q;
   if (a == 0) return 0;
@@ -34,53 +41,39 @@ static int legendre(int a, int q) {
   }
   return r == 1 ? 1 : -1;
 }
-
-static void paley1(int q, int8_t* h) {   // order q + 1, q = 3 mod 4
-  const int n = q + 1;
-  for (int i = 0; i < n; ++i)
-    for (int j = 0; j < n; ++j) {
-      int v;
-      if (i == 0 && j == 0) v = 0;
-      else if (i == 0) v = 1;
-      else if (j == 0) v = -1;
-      else v = legendre(j - i, q);
-      if (i == j) v += 1;
-      h[i * n + j] = (int8_t)v;
-    }
+__host__ __device__ constexpr int c_paley1(int q, int i, int j) {
+  int v = 0;
+  if (i == 0 && j == 0) v = 0;
+  else if (i == 0) v = 1;
+  else if (j == 0) v = -1;
+  else v = c_legendre(j - i, q);
+  if (i == j) v += 1;
+  return v;
 }
-
-static void paley2(int q, int8_t* h) {   // order 2(q + 1), q = 1 mod 4
-  const int n = q + 1, n2 = 2 * n;
-  for (int i = 0; i < n; ++i)
-    for (int j = 0; j < n; ++j) {
-      int cij;
-      if (i == 0 && j == 0) cij = 0;
-      else if (i == 0 || j == 0) cij = 1;
-      else cij = legendre(j - i, q);
-      int blk[4];
-      if (cij == 0) { blk[0] = 1; blk[1] = 1; blk[2] = 1; blk[3] = -1; }
-      else { blk[0] = cij; blk[1] = -cij; blk[2] = -cij; blk[3] = -cij; }
-      h[(2 * i) * n2 + 2 * j] = (int8_t)blk[0];
-      h[(2 * i) * n2 + 2 * j + 1] = (int8_t)blk[1];
-      h[(2 * i + 1) * n2 + 2 * j] = (int8_t)blk[2];
-      h[(2 * i + 1) * n2 + 2 * j + 1] = (int8_t)blk[3];
-    }
+__host__ __device__ constexpr int c_paley2(int q, int r, int c) {
+  const int i = r >> 1, j = c >> 1, n = q + 1;
+  (void)n;
+  int cij = 0;
+  if (i == 0 && j == 0) cij = 0;
+  else if (i == 0 || j == 0) cij = 1;
+  else cij = c_legendre(j - i, q);
+  const int pos = (r & 1) * 2 + (c & 1);
+  if (cij == 0) return pos == 3 ? -1 : 1;
+  return pos == 0 ? cij : -cij;
+}
+__host__ __device__ constexpr int c_base_entry(int base, int i, int j) {
+  if (base == 12) return c_paley1(11, i, j);
+  if (base == 20) return c_paley1(19, i, j);
+  if (base == 28) return c_paley2(13, i, j);
+  // 40: H_2 (x) H_20
+  const int v = c_paley1(19, i % 20, j % 20);
+  return (i >= 20 && j >= 20) ? -v : v;
 }
 
 static int base_matrix(int base, int8_t* h) {
-  if (base == 12) paley1(11, h);
-  else if (base == 20) paley1(19, h);
-  else if (base == 28) paley2(13, h);
-  else if (base == 40) {
-    int8_t h20[400];
-    paley1(19, h20);
-    for (int i = 0; i < 40; ++i)
-      for (int j = 0; j < 40; ++j) {
-        int v = h20[(i % 20) * 20 + (j % 20)];
-        if (i >= 20 && j >= 20) v = -v;
-        h[i * 40 + j] = (int8_t)v;
-      }
-  } else return UNIQL_ESHAPE;
+  if (base != 12 && base != 20 && base != 28 && base != 40) return UNIQL_ESHAPE;
+  for (int i = 0; i < base; ++i)
+    for (int j = 0; j < base; ++j) h[i * base + j] = (int8_t)c_base_entry(base, i, j);
   return UNIQL_OK;
 }
 
@@ -173,6 +166,35 @@ __device__ __forceinline__ void strided_pass(float* buf, int dim, int h, int tid
   }
 }
 
+template <int BASE, int A, size_t... I>
+__device__ __forceinline__ float base_row(const float (&z)[BASE], std::index_sequence<I...>) {
+  return ((std::integral_constant<int, c_base_entry(BASE, A, (int)I)>::value > 0 ? z[I] : -z[I]) + ...);
+}
+template <typename T, int BASE, size_t... A>
+__device__ __forceinline__ void base_rows(const float (&z)[BASE], T* dst, int P, int a_lo, int a_hi, float scale,
+                                          std::index_sequence<A...>) {
+  (((int)A >= a_lo && (int)A < a_hi
+        ? Elem<T>::store1(dst + (size_t)A * P, base_row<BASE, (int)A>(z, std::make_index_sequence<BASE>{}) * scale)
+        : (void)0),
+   ...);
+}
+// Pass C of the row kernel: y[a * P + b] = scale * sum_a' H[a][a'] z[a' * P + b] for every column b.
+template <typename T, int BASE>
+__device__ __forceinline__ void base_pass(const float* buf, T* yr, int P, float scale, int tid, int nthreads) {
+  int asplit = nthreads / P;            // spread the output rows of a column over idle threads
+  if (asplit < 1) asplit = 1;
+  if (asplit > 8) asplit = 8;
+  const int tasks = P * asplit;
+  for (int task = tid; task < tasks; task += nthreads) {
+    const int b = task % P, part = task / P;
+    const int a_lo = BASE * part / asplit, a_hi = BASE * (part + 1) / asplit;
+    float z[BASE];
+#pragma unroll
+    for (int a = 0; a < BASE; ++a) z[a] = buf[(size_t)a * P + b];
+    base_rows<T, BASE>(z, yr + b, P, a_lo, a_hi, scale, std::make_index_sequence<BASE>{});
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) hadamard_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y,
                                                        int64_t ldy, int dim, int P, int base, float scale,
@@ -242,34 +264,12 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const T* __restrict__ x, 
     }
     return;
   }
-  int asplit = nthreads / P;            // spread the output rows of a column over idle threads
-  if (asplit < 1) asplit = 1;
-  if (asplit > 8) asplit = 8;
-  const int tasks = P * asplit;
-  for (int task = tid; task < tasks; task += nthreads) {
-    const int b = task % P, part = task / P;
-    const int a_lo = base * part / asplit, a_hi = base * (part + 1) / asplit;
-    float z[40];
-#pragma unroll
-    for (int a = 0; a < 40; ++a) z[a] = (a < base) ? buf[(size_t)a * P + b] : 0.f;
-    for (int a = a_lo; a < a_hi; ++a) {
-      const uint64_t mask = signs.row[a];
-      float sum = 0.f;
-#pragma unroll
-      for (int ap = 0; ap < 40; ++ap) {
-        const uint32_t flip = (uint32_t)((mask >> ap) & 1ull) << 31;
-        sum += __uint_as_float(__float_as_uint(z[ap]) ^ flip);
-      }
-      Elem<T>::store1(yr + (size_t)a * P + b, sum * scale);
-    }
-  }
+  if (base == 12) base_pass<T, 12>(buf, yr, P, scale, tid, nthreads);
+  else if (base == 20) base_pass<T, 20>(buf, yr, P, scale, tid, nthreads);
+  else if (base == 28) base_pass<T, 28>(buf, yr, P, scale, tid, nthreads);
+  else base_pass<T, 40>(buf, yr, P, scale, tid, nthreads);
 }
 
-// Few-row variant (decode): the transform factorises as (M (x) H_P) with M = H_base (x) H_Q acting across the
-// B = base*Q segments of length P, and the two factors commute.  CTA (s, row) forms segment s of M x with
-// signed sums of the B input segments (each CTA re-reads the row from L2: B * dim * sizeof(T) bytes per row
-// in total, which is why this path is only used for a handful of rows) and then runs the P-point
-// Walsh-Hadamard transform on it locally.  B CTAs per row instead of one.
 template <typename T>
 __global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict__ x, int64_t ldx,
                                                              T* __restrict__ y, int64_t ldy, int P, int B,
