@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "linear_internal.cuh"
 
+#include <stdlib.h>
 #include <type_traits>
 #include <utility>
 
@@ -197,77 +198,99 @@ __device__ __forceinline__ void base_pass(const float* buf, T* yr, int P, float 
 
 template <typename T>
 __global__ void __launch_bounds__(512) hadamard_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y,
-                                                       int64_t ldy, int dim, int P, int base, float scale,
-                                                       const HadSigns signs, int pdl_trigger) {
+                                                       int64_t ldy, int64_t rows, int rows_per_cta, int dim, int P,
+                                                       int base, float scale, int pdl_trigger) {
   extern __shared__ __align__(16) float buf[];
   if (pdl_trigger) pdl_launch_dependents();   // the dependent kernel only prefetches until it waits on us
   const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31;
-  const T* xr = x + (int64_t)blockIdx.x * ldx;
-  T* yr = y + (int64_t)blockIdx.x * ldy;
+  // a CTA takes rows_per_cta consecutive rows (more than one for short rows, so that every thread has several
+  // independent 16-byte loads in flight before the butterfly chain starts)
+  const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
+  const int nr = (int)(rows - row0 < rows_per_cta ? rows - row0 : rows_per_cta);
+  const T* xr = x + row0 * ldx;
+  T* yr = y + row0 * ldy;
 
   // ---- pass A: 8 contiguous elements per thread, stages h = 1..128 (limited by P) ----
   const int nchunks = dim >> 3;
-  const int nchunks_pad = (nchunks + 31) & ~31;
+  const int nchunks_pad = (nchunks + 31) & ~31;   // whole warps per row: the shuffle stages stay inside one row
+  const int total = nr * nchunks_pad;
   const bool only_a = (base == 1 && P <= 256);   // whole transform fits pass A: store straight from registers
-  for (int ch = tid; ch < nchunks_pad; ch += nthreads) {
-    float v[8];
-    if (ch < nchunks) Elem<T>::load8(xr + (size_t)ch * 8, v);
-    else {
+  constexpr int LB = 4;                          // chunks loaded together per thread
+  for (int i0 = tid; i0 < total; i0 += nthreads * LB) {
+    float v[LB][8];
+    int row_of[LB], ch_of[LB];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0.f;
-    }
-    butterflies<8>(v);
+    for (int u = 0; u < LB; ++u) {
+      const int idx = i0 + u * nthreads;
+      row_of[u] = idx / nchunks_pad;
+      ch_of[u] = idx - row_of[u] * nchunks_pad;
+      if (idx < total && ch_of[u] < nchunks) Elem<T>::load8(xr + (int64_t)row_of[u] * ldx + (size_t)ch_of[u] * 8, v[u]);
+      else {
 #pragma unroll
-    for (int s = 0; s < 5; ++s) {
-      if ((8 << s) < P) {
-        const bool upper = (lane >> s) & 1;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float o = __shfl_xor_sync(0xffffffffu, v[i], 1 << s);
-          v[i] = upper ? (o - v[i]) : (v[i] + o);
-        }
+        for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
       }
     }
-    if (ch < nchunks) {
-      if (only_a) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= scale;
-        Elem<T>::store8(yr + (size_t)ch * 8, v);
-      } else {
-        float4* d = reinterpret_cast<float4*>(buf + (size_t)ch * 8);
-        d[0] = make_float4(v[0], v[1], v[2], v[3]);
-        d[1] = make_float4(v[4], v[5], v[6], v[7]);
+    for (int u = 0; u < LB; ++u) {
+      if (i0 + u * nthreads >= total) break;     // uniform per warp: total and nthreads are multiples of 32
+      butterflies<8>(v[u]);
+#pragma unroll
+      for (int s = 0; s < 5; ++s) {
+        if ((8 << s) < P) {
+          const bool upper = (lane >> s) & 1;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[u][i], 1 << s);
+            v[u][i] = upper ? (o - v[u][i]) : (v[u][i] + o);
+          }
+        }
+      }
+      if (ch_of[u] < nchunks) {
+        if (only_a) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[u][i] *= scale;
+          Elem<T>::store8(yr + (int64_t)row_of[u] * ldy + (size_t)ch_of[u] * 8, v[u]);
+        } else {
+          float4* d = reinterpret_cast<float4*>(buf + (size_t)row_of[u] * dim + (size_t)ch_of[u] * 8);
+          d[0] = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+          d[1] = make_float4(v[u][4], v[u][5], v[u][6], v[u][7]);
+        }
       }
     }
   }
   if (only_a) return;
   __syncthreads();
 
-  // ---- pass B: stages h = 256 .. P/2 out of shared memory ----
+  // ---- pass B: stages h = 256 .. P/2 out of shared memory (all rows of the CTA as one array: P divides dim) ----
   for (int h = 256; h < P;) {
     const int rem = P / h;
-    if (rem >= 8) { strided_pass<8>(buf, dim, h, tid, nthreads); h *= 8; }
-    else if (rem == 4) { strided_pass<4>(buf, dim, h, tid, nthreads); h *= 4; }
-    else { strided_pass<2>(buf, dim, h, tid, nthreads); h *= 2; }
+    if (rem >= 8) { strided_pass<8>(buf, nr * dim, h, tid, nthreads); h *= 8; }
+    else if (rem == 4) { strided_pass<4>(buf, nr * dim, h, tid, nthreads); h *= 4; }
+    else { strided_pass<2>(buf, nr * dim, h, tid, nthreads); h *= 2; }
     __syncthreads();
   }
 
   // ---- pass C: base matrix across the `base` segments, scale, store ----
   if (base == 1) {
-    for (int ch = tid; ch < nchunks; ch += nthreads) {
+    for (int idx = tid; idx < nr * nchunks; idx += nthreads) {
+      const int r = idx / nchunks, ch = idx - r * nchunks;
       float v[8];
-      const float4* s4 = reinterpret_cast<const float4*>(buf + (size_t)ch * 8);
+      const float4* s4 = reinterpret_cast<const float4*>(buf + (size_t)r * dim + (size_t)ch * 8);
       const float4 a = s4[0], b = s4[1];
       v[0] = a.x * scale; v[1] = a.y * scale; v[2] = a.z * scale; v[3] = a.w * scale;
       v[4] = b.x * scale; v[5] = b.y * scale; v[6] = b.z * scale; v[7] = b.w * scale;
-      Elem<T>::store8(yr + (size_t)ch * 8, v);
+      Elem<T>::store8(yr + (int64_t)r * ldy + (size_t)ch * 8, v);
     }
     return;
   }
-  if (base == 12) base_pass<T, 12>(buf, yr, P, scale, tid, nthreads);
-  else if (base == 20) base_pass<T, 20>(buf, yr, P, scale, tid, nthreads);
-  else if (base == 28) base_pass<T, 28>(buf, yr, P, scale, tid, nthreads);
-  else base_pass<T, 40>(buf, yr, P, scale, tid, nthreads);
+  for (int r = 0; r < nr; ++r) {
+    const float* rb = buf + (size_t)r * dim;
+    T* ry = yr + (int64_t)r * ldy;
+    if (base == 12) base_pass<T, 12>(rb, ry, P, scale, tid, nthreads);
+    else if (base == 20) base_pass<T, 20>(rb, ry, P, scale, tid, nthreads);
+    else if (base == 28) base_pass<T, 28>(rb, ry, P, scale, tid, nthreads);
+    else base_pass<T, 40>(rb, ry, P, scale, tid, nthreads);
+  }
 }
 
 template <typename T>
@@ -382,15 +405,20 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
     }
   }
 
-  if (base > 1) {
-    for (int i = 0; i < base; ++i)
-      for (int j = 0; j < base; ++j)
-        if (h[i * base + j] < 0) signs.row[i] |= (1ull << j);
-  }
-  int threads = (int)((dim / 8 + 31) / 32 * 32);
+  // Small CTAs: many independent CTAs per SM in different phases (load, butterflies, store) overlap better than a few
+  // large ones.  128 threads up to 8192 elements per row, 256 beyond (measured on B200: 14336 -> 689 us for 16384 rows
+  // with 256 threads, 773 with 512, 870 with 128; 4096 -> 163 / 202 / 220 us with 128 / 256 / 512).  Very short rows
+  // share a CTA so that every thread still has a chunk.
+  int rpc = (int)((1024 + dim - 1) / dim);
+  if (rpc < 1) rpc = 1;
+  if (rpc > 8) rpc = 8;
+  const int64_t want_ctas = 4 * (int64_t)device_info().sm_count;
+  while (rpc > 1 && (rows + rpc - 1) / rpc < want_ctas) --rpc;
+  int threads = (int)(((int64_t)rpc * dim / 8 + 31) / 32 * 32);
   if (threads < 64) threads = 64;
-  if (threads > 512) threads = 512;
-  const size_t smem = (size_t)dim * sizeof(float);
+  const int max_threads = dim > 8192 ? 256 : 128;
+  if (threads > max_threads) threads = max_threads;
+  const size_t smem = (size_t)rpc * dim * sizeof(float);
 
 #define UNIQL_HAD_LAUNCH(T)                                                                                   \
   do {                                                                                                        \
@@ -400,11 +428,12 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
                                           40960 * (int)sizeof(float)));                                       \
       attr_done = true;                                                                                       \
     }                                                                                                         \
-    for (int64_t r0 = 0; r0 < rows; r0 += 1 << 30) {                                                          \
-      const int64_t nr = rows - r0 < (1 << 30) ? rows - r0 : (1 << 30);                                       \
-      hadamard_kernel<T><<<(unsigned)nr, threads, smem, stream>>>((const T*)x + r0 * ldx, ldx, (T*)y + r0 * ldy, \
-                                                                  ldy, (int)dim, (int)P, base, scale, signs,  \
-                                                                  pdl_trigger ? 1 : 0);                       \
+    const int64_t step = ((int64_t)1 << 30) * rpc;                                                            \
+    for (int64_t r0 = 0; r0 < rows; r0 += step) {                                                             \
+      const int64_t nr = rows - r0 < step ? rows - r0 : step;                                                 \
+      hadamard_kernel<T><<<(unsigned)((nr + rpc - 1) / rpc), threads, smem, stream>>>(                        \
+          (const T*)x + r0 * ldx, ldx, (T*)y + r0 * ldy, ldy, nr, rpc, (int)dim, (int)P, base, scale,         \
+          pdl_trigger ? 1 : 0);                                                                               \
     }                                                                                                         \
   } while (0)
 
