@@ -179,6 +179,35 @@ __device__ __forceinline__ void base_rows(const float (&z)[BASE], T* dst, int P,
         : (void)0),
    ...);
 }
+// Order-28 matrix (Paley II over GF(13)) through its 2 x 2 block structure: with u_j = z_2j - z_2j+1 and
+// v_j = -(z_2j + z_2j+1), rows 2i and 2i+1 are  sum_{j != i} c_ij u_j - v_i  and  sum_{j != i} c_ij v_j + u_i
+// where c is the 14 x 14 symmetric core (c_ij = 1 on the border, else the Legendre symbol of j - i): 392 adds per
+// column instead of 756.
+__host__ __device__ constexpr int c_core14(int i, int j) {
+  return (i == 0 || j == 0) ? 1 : c_legendre(j - i, 13);
+}
+template <int I, int J>
+__device__ __forceinline__ float core14_acc(const float (&w)[14], float acc) {
+  if constexpr (J == 14) return acc;
+  else if constexpr (J == I) return core14_acc<I, J + 1>(w, acc);
+  else return core14_acc<I, J + 1>(w, std::integral_constant<int, c_core14(I, J)>::value > 0 ? acc + w[J] : acc - w[J]);
+}
+template <typename T, size_t... I>
+__device__ __forceinline__ void base_rows28(const float (&u)[14], const float (&v)[14], T* dst, int P, int a_lo, int a_hi,
+                                            float scale, std::index_sequence<I...>) {
+  (((int)(2 * I) >= a_lo && (int)(2 * I) < a_hi
+        ? Elem<T>::store1(dst + (size_t)(2 * I) * P, core14_acc<(int)I, 0>(u, -v[I]) * scale) : (void)0), ...);
+  (((int)(2 * I + 1) >= a_lo && (int)(2 * I + 1) < a_hi
+        ? Elem<T>::store1(dst + (size_t)(2 * I + 1) * P, core14_acc<(int)I, 0>(v, u[I]) * scale) : (void)0), ...);
+}
+template <typename T, size_t... A>
+__device__ __forceinline__ void base_rows40(const float (&sm)[20], const float (&df)[20], T* dst, int P, int a_lo, int a_hi,
+                                            float scale, std::index_sequence<A...>) {
+  (((int)A >= a_lo && (int)A < a_hi
+        ? Elem<T>::store1(dst + (size_t)A * P, base_row<20, (int)A>(sm, std::make_index_sequence<20>{}) * scale) : (void)0), ...);
+  (((int)(20 + A) >= a_lo && (int)(20 + A) < a_hi
+        ? Elem<T>::store1(dst + (size_t)(20 + A) * P, base_row<20, (int)A>(df, std::make_index_sequence<20>{}) * scale) : (void)0), ...);
+}
 // Pass C of the row kernel: y[a * P + b] = scale * sum_a' H[a][a'] z[a' * P + b] for every column b.
 template <typename T, int BASE>
 __device__ __forceinline__ void base_pass(const float* buf, T* yr, int P, float scale, int tid, int nthreads) {
@@ -192,7 +221,20 @@ __device__ __forceinline__ void base_pass(const float* buf, T* yr, int P, float 
     float z[BASE];
 #pragma unroll
     for (int a = 0; a < BASE; ++a) z[a] = buf[(size_t)a * P + b];
-    base_rows<T, BASE>(z, yr + b, P, a_lo, a_hi, scale, std::make_index_sequence<BASE>{});
+    if constexpr (BASE == 28) {
+      float u[14], v[14];
+#pragma unroll
+      for (int j = 0; j < 14; ++j) { u[j] = z[2 * j] - z[2 * j + 1]; v[j] = -z[2 * j] - z[2 * j + 1]; }
+      base_rows28<T>(u, v, yr + b, P, a_lo, a_hi, scale, std::make_index_sequence<14>{});
+    } else if constexpr (BASE == 40) {
+      // H_40 = [[H_20, H_20], [H_20, -H_20]]: two order-20 products of the sum and the difference of the halves
+      float sm[20], df[20];
+#pragma unroll
+      for (int j = 0; j < 20; ++j) { sm[j] = z[j] + z[20 + j]; df[j] = z[j] - z[20 + j]; }
+      base_rows40<T>(sm, df, yr + b, P, a_lo, a_hi, scale, std::make_index_sequence<20>{});
+    } else {
+      base_rows<T, BASE>(z, yr + b, P, a_lo, a_hi, scale, std::make_index_sequence<BASE>{});
+    }
   }
 }
 
