@@ -35,83 +35,84 @@ struct QuantParams {
 template <bool HAS_SCALE>
 __global__ void __launch_bounds__(kQThreads)
 w4a16_quantize_kernel(const QuantParams p) {
-  __shared__ __align__(16) __half tile[kTileN][kTileK + kTilePad];   // [column][k]
-  __shared__ __align__(16) __half wref[kTileK][kTileN + kTilePad];   // [k][column]
+  __shared__ __align__(16) __half wref[kTileK][kTileN + kTilePad];   // [k][column], only filled when w_ref is wanted
   __shared__ uint8_t codes[kTileK][kTileN + 4];
   __shared__ __half col_scale[kTileN];
 
   const int t = threadIdx.x;
   const int n0 = blockIdx.x * kTileN, k0 = blockIdx.y * kTileK;
 
-  // ---- load the tile: 16 threads per weight row, 16 rows per pass; rows / k past the matrix read as zero ----
+  // ---- load: 16 lanes per weight row (= output column), 8 consecutive k each, 16 columns per pass; the four passes'
+  //      loads are issued together and the values stay in registers.  Rows / k past the matrix read as zero. ----
   const bool vec_ok = ((p.ldw & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.W) & 15u) == 0);
-  {
-    const int r = t >> 4, seg = t & 15;
+  const int r = t >> 4, seg = t & 15;
+  constexpr int kPasses = kTileN / 16;
+  uint4 raw[kPasses];
 #pragma unroll
-    for (int pass = 0; pass < kTileN / 16; ++pass) {
-      const int n = pass * 16 + r;
-      const int gn = n0 + n, gk = k0 + seg * 8;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (gn < p.n_out) {
-        const __half* src = p.W + (size_t)gn * p.ldw + gk;
-        if (vec_ok && gk + 8 <= p.k_in) {
-          v = *reinterpret_cast<const uint4*>(src);
-        } else {
-          __half h[8];
+  for (int pass = 0; pass < kPasses; ++pass) {
+    const int gn = n0 + pass * 16 + r, gk = k0 + seg * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (gn < p.n_out) {
+      const __half* src = p.W + (size_t)gn * p.ldw + gk;
+      if (vec_ok && gk + 8 <= p.k_in) {
+        v = *reinterpret_cast<const uint4*>(src);
+      } else {
+        __half h[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) h[e] = (gk + e < p.k_in) ? src[e] : __float2half(0.f);
-          v = *reinterpret_cast<uint4*>(h);
-        }
+        for (int e = 0; e < 8; ++e) h[e] = (gk + e < p.k_in) ? src[e] : __float2half(0.f);
+        v = *reinterpret_cast<uint4*>(h);
       }
-      *reinterpret_cast<uint4*>(&tile[n][seg * 8]) = v;
     }
+    raw[pass] = v;
   }
-  __syncthreads();
 
-  // ---- four threads per column, 32 k-values each ----
-  const int n = t >> 2, part = t & 3;
-  const bool real_col = n0 + n < p.n_out;
-  __half s16;
-  if (HAS_SCALE) {
-    s16 = real_col ? p.gscale[(size_t)blockIdx.y * p.n_out + n0 + n] : __float2half(0.f);
-  } else {
-    float amax = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__half2float(tile[n][part * 32 + i])));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    // fp16 tensor times the Python scalar 2/15: one fp32 multiply, one rounding to fp16
-    s16 = __float2half_rn(__fmul_rn(amax, (float)(2.0 / 15.0)));
-  }
-  if (part == 0) col_scale[n] = s16;
-  const float s = __half2float(s16);
-
-#pragma unroll 4
-  for (int i = 0; i < 32; ++i) {
-    const int k = part * 32 + i;
-    const __half w16 = tile[n][k];
-    const float w = __half2float(w16);
-    int q;
-    __half ref;
-    if (!real_col) {                              // padded output column: zero code, zero scale, +0 reference
-      q = 0;
-      ref = __float2half(0.f);
-    } else if (HAS_SCALE) {
-      // the weight is already on the grid of the given scales: q = round(fp16(fp16(w / s) + 8)), NaN and inf -> 0
-      const __half ratio = __float2half_rn(__fdiv_rn(w, s));
-      const float shifted = __half2float(__float2half_rn(__fadd_rn(__half2float(ratio), 8.f)));
-      q = (isnan(shifted) || isinf(shifted)) ? 0 : (int)rintf(shifted);
-      q = min(max(q, 0), 15);
-      ref = w16;
+#pragma unroll
+  for (int pass = 0; pass < kPasses; ++pass) {
+    const int n = pass * 16 + r;
+    const bool real_col = n0 + n < p.n_out;
+    const __half* h8 = reinterpret_cast<const __half*>(&raw[pass]);
+    __half s16;
+    if (HAS_SCALE) {
+      s16 = real_col ? p.gscale[(size_t)blockIdx.y * p.n_out + n0 + n] : __float2half(0.f);
     } else {
-      // q = clamp(round(fp16(w / s)) + 8, 0, 15); an all-zero group (s = 0, w / s = NaN) gets code 0
-      const __half ratio = __float2half_rn(__fdiv_rn(w, s));
-      const float rf = __half2float(ratio);
-      q = (s == 0.f || isnan(rf)) ? 0 : min(max((int)rintf(rf) + 8, 0), 15);
-      ref = __float2half_rn(__fmul_rn((float)(q - 8), s));
+      float amax = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(__half2float(h8[e])));
+      // the 16 lanes of a column are one half of the warp: xor steps 1..8 stay inside it
+#pragma unroll
+      for (int d = 1; d < 16; d <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+      // fp16 tensor times the Python scalar 2/15: one fp32 multiply, one rounding to fp16
+      s16 = __float2half_rn(__fmul_rn(amax, (float)(2.0 / 15.0)));
     }
-    codes[k][n] = (uint8_t)q;
-    wref[k][n] = ref;
+    if (seg == 0) col_scale[n] = s16;
+    const float s = __half2float(s16);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int k = seg * 8 + e;
+      const __half w16 = h8[e];
+      const float w = __half2float(w16);
+      int q;
+      __half ref;
+      if (!real_col) {                              // padded output column: zero code, zero scale, +0 reference
+        q = 0;
+        ref = __float2half(0.f);
+      } else if (HAS_SCALE) {
+        // the weight is already on the grid of the given scales: q = round(fp16(fp16(w / s) + 8)), NaN and inf -> 0
+        const __half ratio = __float2half_rn(__fdiv_rn(w, s));
+        const float shifted = __half2float(__float2half_rn(__fadd_rn(__half2float(ratio), 8.f)));
+        q = (isnan(shifted) || isinf(shifted)) ? 0 : (int)rintf(shifted);
+        q = min(max(q, 0), 15);
+        ref = w16;
+      } else {
+        // q = clamp(round(fp16(w / s)) + 8, 0, 15); an all-zero group (s = 0, w / s = NaN) gets code 0
+        const __half ratio = __float2half_rn(__fdiv_rn(w, s));
+        const float rf = __half2float(ratio);
+        q = (s == 0.f || isnan(rf)) ? 0 : min(max((int)rintf(rf) + 8, 0), 15);
+        ref = __float2half_rn(__fmul_rn((float)(q - 8), s));
+      }
+      codes[k][n] = (uint8_t)q;
+      if (p.w_ref) wref[k][n] = ref;
+    }
   }
   __syncthreads();
 
