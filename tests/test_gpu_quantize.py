@@ -97,3 +97,30 @@ def test_bad_arguments_are_refused():
         ops.w4a16_quantize(w, n_pad=64)                    # smaller than out_features
     with pytest.raises(RuntimeError):
         ops.w4a16_quantize(w, torch.zeros(3, 128, device="cuda", dtype=torch.float16))   # wrong scale shape
+
+
+def test_full_size_gate_projection_properties():
+    """14336 x 4096 (the bench's gate projection): properties that need no CPU-sized oracle run.  Every weight lies
+    within half a quantisation step of its dequantised value, scales follow max|w| * 2/15, and a decode-size product
+    through the linear kernel agrees with the fp16 weights within the quantisation noise."""
+    from uniql_b200 import ops
+    from uniql_b200.quantize import quantize_helpers as qh
+    n, k = 14336, 4096
+    g = torch.Generator(device="cuda").manual_seed(5)
+    w = (torch.randn(n, k, generator=g, device="cuda") * 0.02).to(torch.float16)
+    w_ref, packed, scales = ops.w4a16_quantize(w, n_pad=n)
+    assert packed.shape == (k // 16, 2 * n) and scales.shape == (k // 128, n) and w_ref.shape == (k, n)
+    nat = qh.unpermute_group_scales(scales)                                       # [groups, n]
+    want = (w.t().reshape(k // 128, 128, n).abs().amax(dim=1).float() * (2.0 / 15.0)).to(torch.float16)
+    assert torch.equal(nat, want)
+    step = nat.float().repeat_interleave(128, dim=0)                              # [k, n]
+    err = (w_ref.float() - w.t().float()).abs()
+    # half a step, plus the fp16 roundings of w / s (|w / s| <= 7.5) and of w_ref itself
+    assert bool((err <= 0.52 * step + 1e-8).all())
+    codes = torch.round(w_ref.float() / step.clamp_min(1e-30)) + 8
+    assert float(codes.min()) >= 0 and float(codes.max()) <= 15
+    # the packed buffers drive the linear kernel to the same result as the reference weights
+    x = (torch.randn(4, k, generator=g, device="cuda")).to(torch.float16)
+    y = ops.w4a16_linear(x, packed, scales, None, n)
+    y_ref = x.float() @ w_ref.float()
+    assert float((y.float() - y_ref).abs().max() / y_ref.abs().max()) <= 1e-2    # the linear path's tolerance

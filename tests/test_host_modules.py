@@ -161,6 +161,12 @@ def test_c_abi_argument_validation_without_gpu(built_lib):
     assert L.uniql_hadamard(None, None, 1, 12160, 1.0, 0, None) == -3
     assert L.uniql_hadamard(None, None, 1, 64, 1.0, 7, None) == -6
     assert L.uniql_hadamard(None, None, 0, 64, 1.0, 0, None) == 0
+    # uniql_w4a16_quantize(W, ldw, n_out, k_in, group_scale, packed, scales, w_ref, n_pad, stream)
+    assert L.uniql_w4a16_quantize(None, 256, 128, 256, None, None, None, None, 100, None) == -3    # n_pad % 64
+    assert L.uniql_w4a16_quantize(None, 256, 128, 256, None, None, None, None, 64, None) == -3     # n_pad < n_out
+    assert L.uniql_w4a16_quantize(None, 100, 128, 256, None, None, None, None, 128, None) == -1    # ldw < k_in
+    assert L.uniql_w4a16_quantize(None, 256, 0, 256, None, None, None, None, 128, None) == -1      # empty
+    assert L.uniql_w4a16_quantize(None, 256, 128, 256, None, None, None, None, 128, None) == -1    # null pointers
 
 
 @pytest.mark.parametrize("base", [12, 20, 28, 40])
