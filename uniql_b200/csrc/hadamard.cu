@@ -5,11 +5,12 @@
 // i = a * 2^j + b: b runs through a Sylvester-ordered Walsh-Hadamard transform, a through a fixed
 // base x base Hadamard matrix (Paley I for 12 and 20, Paley II for 28, H_2 (x) H_20 for 40).
 //
-// One CTA per row.  Pass A: each thread takes 8 contiguous elements (one 16-byte load for 16-bit
-// types), does 3 butterfly stages in registers and up to 5 more with warp shuffles, and parks the
-// result in shared memory as fp32.  Pass B: the remaining stages run radix-8/4/2 out of shared
-// memory with a stride >= 256 (bank-conflict free).  Pass C: the base matrix is applied per column b
-// with signs taken from a bit mask in the kernel parameters, scaled, converted and stored coalesced.
+// Many rows: one CTA per row.  hadamard_rows32_kernel (P >= 32): each thread takes 32 contiguous elements (four
+// 16-byte loads for 16-bit types), does 5 butterfly stages in registers and parks the result in a padded fp32 copy in
+// shared memory; the remaining stages run radix-8/4/2 out of shared memory (stride >= 32, bank-conflict free); the base
+// matrix is applied per column b with compile-time signs, scaled, converted and stored coalesced.  hadamard_kernel
+// (tiny transforms): 8 contiguous elements per thread, 3 register stages and up to 5 shuffle stages.
+// Few rows (decode): hadamard_split_kernel, one CTA per (segment, row).
 // HBM-bound for many rows (2 * dim * sizeof(T) bytes per row); latency-bound for a single row.
 #include "common.cuh"
 #include "linear_internal.cuh"
@@ -167,6 +168,26 @@ __device__ __forceinline__ void strided_pass(float* buf, int dim, int h, int tid
   }
 }
 
+// Padded shared-memory layout of the 32-element kernel: 4 floats of padding after every 32, so that lanes storing
+// their 32 contiguous elements as 16-byte vectors (lane stride 144 bytes) hit distinct banks.
+__device__ __forceinline__ int pad32(int e) { return e + ((e >> 5) << 2); }
+
+template <int R>
+__device__ __forceinline__ void strided_pass_padded(float* buf, int total, int h, int tid, int nthreads) {
+  const int groups = total / R;
+  const int hp = h + (h >> 3);                  // pad32 is linear in steps of h when h is a multiple of 32
+  for (int idx = tid; idx < groups; idx += nthreads) {
+    const int low = idx % h, high = idx / h;
+    float* p = buf + pad32(high * h * R + low);
+    float v[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) v[i] = p[(size_t)i * hp];
+    butterflies<R>(v);
+#pragma unroll
+    for (int i = 0; i < R; ++i) p[(size_t)i * hp] = v[i];
+  }
+}
+
 template <int BASE, int A, size_t... I>
 __device__ __forceinline__ float base_row(const float (&z)[BASE], std::index_sequence<I...>) {
   return ((std::integral_constant<int, c_base_entry(BASE, A, (int)I)>::value > 0 ? z[I] : -z[I]) + ...);
@@ -209,7 +230,7 @@ __device__ __forceinline__ void base_rows40(const float (&sm)[20], const float (
         ? Elem<T>::store1(dst + (size_t)(20 + A) * P, base_row<20, (int)A>(df, std::make_index_sequence<20>{}) * scale) : (void)0), ...);
 }
 // Pass C of the row kernel: y[a * P + b] = scale * sum_a' H[a][a'] z[a' * P + b] for every column b.
-template <typename T, int BASE>
+template <typename T, int BASE, bool PAD = false>
 __device__ __forceinline__ void base_pass(const float* buf, T* yr, int P, float scale, int tid, int nthreads) {
   int asplit = nthreads / P;            // spread the output rows of a column over idle threads
   if (asplit < 1) asplit = 1;
@@ -220,7 +241,7 @@ __device__ __forceinline__ void base_pass(const float* buf, T* yr, int P, float 
     const int a_lo = BASE * part / asplit, a_hi = BASE * (part + 1) / asplit;
     float z[BASE];
 #pragma unroll
-    for (int a = 0; a < BASE; ++a) z[a] = buf[(size_t)a * P + b];
+    for (int a = 0; a < BASE; ++a) z[a] = PAD ? buf[pad32(a * P + b)] : buf[(size_t)a * P + b];
     if constexpr (BASE == 28) {
       float u[14], v[14];
 #pragma unroll
@@ -335,6 +356,61 @@ __global__ void __launch_bounds__(512) hadamard_kernel(const T* __restrict__ x, 
   }
 }
 
+// Many rows, P >= 32: one CTA per row, 32 contiguous elements per thread.  Stages h = 1..16 run in registers (no
+// shuffles: the five shuffle stages of the 8-element kernel were most of its instructions), the rest as radix-8/4/2
+// passes over the padded shared-memory copy, then the base matrix.
+template <typename T>
+__global__ void __launch_bounds__(256) hadamard_rows32_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y,
+                                                              int64_t ldy, int dim, int P, int base, float scale,
+                                                              int pdl_trigger) {
+  extern __shared__ __align__(16) float buf[];
+  if (pdl_trigger) pdl_launch_dependents();
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const T* xr = x + (int64_t)blockIdx.x * ldx;
+  T* yr = y + (int64_t)blockIdx.x * ldy;
+  const int nch = dim >> 5;
+
+  for (int c = tid; c < nch; c += nthreads) {
+    float v[32];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float t8[8];
+      Elem<T>::load8(xr + (size_t)c * 32 + q * 8, t8);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[q * 8 + i] = t8[i];
+    }
+    butterflies<32>(v);
+    float4* d = reinterpret_cast<float4*>(buf + c * 36);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) d[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  }
+  __syncthreads();
+
+  for (int h = 32; h < P;) {
+    const int rem = P / h;
+    if (rem >= 8) { strided_pass_padded<8>(buf, dim, h, tid, nthreads); h *= 8; }
+    else if (rem == 4) { strided_pass_padded<4>(buf, dim, h, tid, nthreads); h *= 4; }
+    else { strided_pass_padded<2>(buf, dim, h, tid, nthreads); h *= 2; }
+    __syncthreads();
+  }
+
+  if (base == 1) {
+    for (int c = tid; c < nch * 4; c += nthreads) {     // 8 elements per step: never across a padding gap
+      float v[8];
+      const float4* s4 = reinterpret_cast<const float4*>(buf + pad32(c * 8));
+      const float4 a = s4[0], b = s4[1];
+      v[0] = a.x * scale; v[1] = a.y * scale; v[2] = a.z * scale; v[3] = a.w * scale;
+      v[4] = b.x * scale; v[5] = b.y * scale; v[6] = b.z * scale; v[7] = b.w * scale;
+      Elem<T>::store8(yr + (size_t)c * 8, v);
+    }
+    return;
+  }
+  if (base == 12) base_pass<T, 12, true>(buf, yr, P, scale, tid, nthreads);
+  else if (base == 20) base_pass<T, 20, true>(buf, yr, P, scale, tid, nthreads);
+  else if (base == 28) base_pass<T, 28, true>(buf, yr, P, scale, tid, nthreads);
+  else base_pass<T, 40, true>(buf, yr, P, scale, tid, nthreads);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict__ x, int64_t ldx,
                                                              T* __restrict__ y, int64_t ldy, int P, int B,
@@ -445,6 +521,35 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
       else return UNIQL_EDTYPE;
       return launch_status();
     }
+  }
+
+  // ---- many rows, P >= 32 and more stages than fit the register + shuffle pass: 32 elements per thread ----
+  if (P >= 32 && !(base == 1 && P <= 256)) {
+    int threads = (int)((dim / 32 + 31) / 32 * 32);
+    if (threads < 64) threads = 64;
+    const int max_threads = dim > 8192 ? 256 : 128;
+    if (threads > max_threads) threads = max_threads;
+    const size_t smem = (size_t)(dim + dim / 8) * sizeof(float);
+#define UNIQL_HAD32_LAUNCH(T)                                                                                 \
+  do {                                                                                                        \
+    static thread_local bool attr_done = false;                                                               \
+    if (smem > 48 * 1024 && !attr_done) {                                                                     \
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(hadamard_rows32_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                          (40960 + 40960 / 8) * (int)sizeof(float)));                         \
+      attr_done = true;                                                                                       \
+    }                                                                                                         \
+    for (int64_t r0 = 0; r0 < rows; r0 += (int64_t)1 << 30) {                                                 \
+      const int64_t nr = rows - r0 < ((int64_t)1 << 30) ? rows - r0 : ((int64_t)1 << 30);                     \
+      hadamard_rows32_kernel<T><<<(unsigned)nr, threads, smem, stream>>>(                                     \
+          (const T*)x + r0 * ldx, ldx, (T*)y + r0 * ldy, ldy, (int)dim, (int)P, base, scale, pdl_trigger ? 1 : 0); \
+    }                                                                                                         \
+  } while (0)
+    if (dtype == UNIQL_F16) UNIQL_HAD32_LAUNCH(__half);
+    else if (dtype == UNIQL_BF16) UNIQL_HAD32_LAUNCH(__nv_bfloat16);
+    else if (dtype == UNIQL_F32) UNIQL_HAD32_LAUNCH(float);
+    else return UNIQL_EDTYPE;
+#undef UNIQL_HAD32_LAUNCH
+    return launch_status();
   }
 
   // Small CTAs: many independent CTAs per SM in different phases (load, butterflies, store) overlap better than a few
