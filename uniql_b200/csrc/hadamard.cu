@@ -156,8 +156,9 @@ __device__ __forceinline__ void butterflies(float (&v)[R]) {
 template <int R>
 __device__ __forceinline__ void strided_pass(float* buf, int dim, int h, int tid, int nthreads) {
   const int groups = dim / R;
+  const int lh = __ffs(h) - 1;                  // h is a power of two: shifts and masks instead of divisions
   for (int idx = tid; idx < groups; idx += nthreads) {
-    const int low = idx % h, high = idx / h;
+    const int low = idx & (h - 1), high = idx >> lh;
     float* p = buf + (size_t)high * h * R + low;
     float v[R];
 #pragma unroll
@@ -176,8 +177,9 @@ template <int R>
 __device__ __forceinline__ void strided_pass_padded(float* buf, int total, int h, int tid, int nthreads) {
   const int groups = total / R;
   const int hp = h + (h >> 3);                  // pad32 is linear in steps of h when h is a multiple of 32
+  const int lh = __ffs(h) - 1;                  // h is a power of two: shifts and masks instead of divisions
   for (int idx = tid; idx < groups; idx += nthreads) {
-    const int low = idx % h, high = idx / h;
+    const int low = idx & (h - 1), high = idx >> lh;
     float* p = buf + pad32(high * h * R + low);
     float v[R];
 #pragma unroll
@@ -192,13 +194,15 @@ template <int BASE, int A, size_t... I>
 __device__ __forceinline__ float base_row(const float (&z)[BASE], std::index_sequence<I...>) {
   return ((std::integral_constant<int, c_base_entry(BASE, A, (int)I)>::value > 0 ? z[I] : -z[I]) + ...);
 }
-template <typename T, int BASE, size_t... A>
+// ALL: the thread writes every output row of its column (no range test, no branches around the stores).
+template <typename T, bool ALL>
+__device__ __forceinline__ void put_row(T* dst, int a, int P, int a_lo, int a_hi, float v) {
+  if (ALL || (a >= a_lo && a < a_hi)) Elem<T>::store1(dst + (size_t)a * P, v);
+}
+template <typename T, int BASE, bool ALL, size_t... A>
 __device__ __forceinline__ void base_rows(const float (&z)[BASE], T* dst, int P, int a_lo, int a_hi, float scale,
                                           std::index_sequence<A...>) {
-  (((int)A >= a_lo && (int)A < a_hi
-        ? Elem<T>::store1(dst + (size_t)A * P, base_row<BASE, (int)A>(z, std::make_index_sequence<BASE>{}) * scale)
-        : (void)0),
-   ...);
+  (put_row<T, ALL>(dst, (int)A, P, a_lo, a_hi, base_row<BASE, (int)A>(z, std::make_index_sequence<BASE>{}) * scale), ...);
 }
 // Order-28 matrix (Paley II over GF(13)) through its 2 x 2 block structure: with u_j = z_2j - z_2j+1 and
 // v_j = -(z_2j + z_2j+1), rows 2i and 2i+1 are  sum_{j != i} c_ij u_j - v_i  and  sum_{j != i} c_ij v_j + u_i
@@ -213,49 +217,63 @@ __device__ __forceinline__ float core14_acc(const float (&w)[14], float acc) {
   else if constexpr (J == I) return core14_acc<I, J + 1>(w, acc);
   else return core14_acc<I, J + 1>(w, std::integral_constant<int, c_core14(I, J)>::value > 0 ? acc + w[J] : acc - w[J]);
 }
-template <typename T, size_t... I>
+template <typename T, bool ALL, size_t... I>
 __device__ __forceinline__ void base_rows28(const float (&u)[14], const float (&v)[14], T* dst, int P, int a_lo, int a_hi,
                                             float scale, std::index_sequence<I...>) {
-  (((int)(2 * I) >= a_lo && (int)(2 * I) < a_hi
-        ? Elem<T>::store1(dst + (size_t)(2 * I) * P, core14_acc<(int)I, 0>(u, -v[I]) * scale) : (void)0), ...);
-  (((int)(2 * I + 1) >= a_lo && (int)(2 * I + 1) < a_hi
-        ? Elem<T>::store1(dst + (size_t)(2 * I + 1) * P, core14_acc<(int)I, 0>(v, u[I]) * scale) : (void)0), ...);
+  (put_row<T, ALL>(dst, (int)(2 * I), P, a_lo, a_hi, core14_acc<(int)I, 0>(u, -v[I]) * scale), ...);
+  (put_row<T, ALL>(dst, (int)(2 * I + 1), P, a_lo, a_hi, core14_acc<(int)I, 0>(v, u[I]) * scale), ...);
 }
-template <typename T, size_t... A>
+template <typename T, bool ALL, size_t... A>
 __device__ __forceinline__ void base_rows40(const float (&sm)[20], const float (&df)[20], T* dst, int P, int a_lo, int a_hi,
                                             float scale, std::index_sequence<A...>) {
-  (((int)A >= a_lo && (int)A < a_hi
-        ? Elem<T>::store1(dst + (size_t)A * P, base_row<20, (int)A>(sm, std::make_index_sequence<20>{}) * scale) : (void)0), ...);
-  (((int)(20 + A) >= a_lo && (int)(20 + A) < a_hi
-        ? Elem<T>::store1(dst + (size_t)(20 + A) * P, base_row<20, (int)A>(df, std::make_index_sequence<20>{}) * scale) : (void)0), ...);
+  (put_row<T, ALL>(dst, (int)A, P, a_lo, a_hi, base_row<20, (int)A>(sm, std::make_index_sequence<20>{}) * scale), ...);
+  (put_row<T, ALL>(dst, (int)(20 + A), P, a_lo, a_hi, base_row<20, (int)A>(df, std::make_index_sequence<20>{}) * scale), ...);
 }
-// Pass C of the row kernel: y[a * P + b] = scale * sum_a' H[a][a'] z[a' * P + b] for every column b.
+template <typename T, int BASE, bool ALL>
+__device__ __forceinline__ void base_column(const float (&z)[BASE], T* dst, int P, int a_lo, int a_hi, float scale) {
+  if constexpr (BASE == 28) {
+    float u[14], v[14];
+#pragma unroll
+    for (int j = 0; j < 14; ++j) { u[j] = z[2 * j] - z[2 * j + 1]; v[j] = -z[2 * j] - z[2 * j + 1]; }
+    base_rows28<T, ALL>(u, v, dst, P, a_lo, a_hi, scale, std::make_index_sequence<14>{});
+  } else if constexpr (BASE == 40) {
+    // H_40 = [[H_20, H_20], [H_20, -H_20]]: two order-20 products of the sum and the difference of the halves
+    float sm[20], df[20];
+#pragma unroll
+    for (int j = 0; j < 20; ++j) { sm[j] = z[j] + z[20 + j]; df[j] = z[j] - z[20 + j]; }
+    base_rows40<T, ALL>(sm, df, dst, P, a_lo, a_hi, scale, std::make_index_sequence<20>{});
+  } else {
+    base_rows<T, BASE, ALL>(z, dst, P, a_lo, a_hi, scale, std::make_index_sequence<BASE>{});
+  }
+}
+// Pass C of the row kernels: y[a * P + b] = scale * sum_a' H[a][a'] z[a' * P + b] for every column b.
 template <typename T, int BASE, bool PAD = false>
 __device__ __forceinline__ void base_pass(const float* buf, T* yr, int P, float scale, int tid, int nthreads) {
   int asplit = nthreads / P;            // spread the output rows of a column over idle threads
   if (asplit < 1) asplit = 1;
   if (asplit > 8) asplit = 8;
+  // distance between the segments of a column in the (padded) copy: pad32 is linear in steps of P (P % 32 == 0)
+  const int seg_stride = PAD ? P + (P >> 3) : P;
+  if (asplit == 1) {
+    for (int b = tid; b < P; b += nthreads) {
+      const float* col = buf + (PAD ? pad32(b) : b);
+      float z[BASE];
+#pragma unroll
+      for (int a = 0; a < BASE; ++a) z[a] = col[(size_t)a * seg_stride];
+      base_column<T, BASE, true>(z, yr + b, P, 0, BASE, scale);
+    }
+    return;
+  }
   const int tasks = P * asplit;
+  const int lp = __ffs(P) - 1;                  // P is a power of two
   for (int task = tid; task < tasks; task += nthreads) {
-    const int b = task % P, part = task / P;
+    const int b = task & (P - 1), part = task >> lp;
     const int a_lo = BASE * part / asplit, a_hi = BASE * (part + 1) / asplit;
+    const float* col = buf + (PAD ? pad32(b) : b);
     float z[BASE];
 #pragma unroll
-    for (int a = 0; a < BASE; ++a) z[a] = PAD ? buf[pad32(a * P + b)] : buf[(size_t)a * P + b];
-    if constexpr (BASE == 28) {
-      float u[14], v[14];
-#pragma unroll
-      for (int j = 0; j < 14; ++j) { u[j] = z[2 * j] - z[2 * j + 1]; v[j] = -z[2 * j] - z[2 * j + 1]; }
-      base_rows28<T>(u, v, yr + b, P, a_lo, a_hi, scale, std::make_index_sequence<14>{});
-    } else if constexpr (BASE == 40) {
-      // H_40 = [[H_20, H_20], [H_20, -H_20]]: two order-20 products of the sum and the difference of the halves
-      float sm[20], df[20];
-#pragma unroll
-      for (int j = 0; j < 20; ++j) { sm[j] = z[j] + z[20 + j]; df[j] = z[j] - z[20 + j]; }
-      base_rows40<T>(sm, df, yr + b, P, a_lo, a_hi, scale, std::make_index_sequence<20>{});
-    } else {
-      base_rows<T, BASE>(z, yr + b, P, a_lo, a_hi, scale, std::make_index_sequence<BASE>{});
-    }
+    for (int a = 0; a < BASE; ++a) z[a] = col[(size_t)a * seg_stride];
+    base_column<T, BASE, false>(z, yr + b, P, a_lo, a_hi, scale);
   }
 }
 
