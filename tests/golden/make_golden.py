@@ -41,7 +41,9 @@ def _weights(seed, out_f, in_f, std=0.02):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to a checkout of enyac-group/UniQL>")
+    root = sys.argv[1]
     qh, qll, qel, hh = _import_reference(root)
 
     # ---- 1. w4a16_quantize on a few shapes (incl. N padding and K padding) ----
