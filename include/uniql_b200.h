@@ -146,6 +146,29 @@ int uniql_hadamard(const void* x, void* y, int64_t rows, int64_t dim, float scal
 int uniql_w4a16_quantize(const void* W, int64_t ldw, int64_t n_out, int64_t k_in, const void* group_scale,
                          void* packed, void* scales, void* w_ref, int64_t n_pad, void* stream);
 
+/*
+ * Load-time slicing of packed layers on the GPU (the reference re-slices on the CPU through unpack -> slice -> repack:
+ * modeling/modeling_helpers.py:361-867 with quantize/quantize_helpers.py:279-328 and :67-84).
+ *
+ * uniql_w4a16_gather_columns: new packed layer whose output column c is source column col_index[c] (c < n_new; the
+ * columns from n_new to n_out_pad, and entries < 0, get code 0 and scale 0).  Rows k >= zero_rows_from get code 0 (the
+ * reference drops the k padding before slicing and pads with zeros afterwards); pass size_k to keep every row.
+ *   packed_in  int32 [size_k/16, 2*n_src_pad]   scales_in  fp16 [size_k/128, n_src_pad] (permuted)
+ *   packed_out int32 [size_k/16, 2*n_out_pad]   scales_out fp16 [size_k/128, n_out_pad] (permuted)
+ *   col_index  DEVICE int32 [n_new], values in [0, n_src_pad) or negative
+ *
+ * uniql_w4a16_dequantize_rows: out[n][j] = fp16((q - 8) * s) of source row row_index[j], column n, for n < n_real and
+ * j < k_new, row stride ld (elements): the [out_features, in_features] layout uniql_w4a16_quantize reads, so that
+ * "keep these input rows and quantise again" (slice_w4a16_o_proj :632-650, slice_w4a16_out_proj :845-862) is two calls.
+ *   row_index  DEVICE int32 [k_new], values in [0, size_k)
+ */
+int uniql_w4a16_gather_columns(const void* packed_in, const void* scales_in, int64_t size_k, int64_t n_src_pad,
+                               const int32_t* col_index, int64_t n_new, int64_t zero_rows_from,
+                               void* packed_out, void* scales_out, int64_t n_out_pad, void* stream);
+int uniql_w4a16_dequantize_rows(const void* packed, const void* scales, int64_t size_k, int64_t n_src_pad,
+                                const int32_t* row_index, int64_t k_new, int64_t n_real, void* out, int64_t ld,
+                                void* stream);
+
 /* Host helper: writes the base x base ±1 matrix (row-major int8) this library uses for
  * base in {12, 20, 28, 40}; `out` is a HOST pointer.  Returns UNIQL_ESHAPE for other orders. */
 int uniql_hadamard_base_matrix(int base, int8_t* out);

@@ -8,7 +8,7 @@ The reference's CUDA extension modules (quant_linear_cuda, quant_embedding_cuda,
 fast_hadamard_transform_cuda) are replaced by empty stand-ins so that the pure
 Python/CPU parts of the reference — the RTN quantiser, the weight/scale
 permutation and packing helpers, their inverses, the module constructors and
-their from_fp16 class methods — can be imported and executed as they are.
+their from_fp16 class methods, the load-time slicing functions — can be imported and executed as they are.
 Outputs are small .npz files holding the seeded inputs and the reference's outputs.
 """
 import os
@@ -107,7 +107,69 @@ def main():
     np.savez_compressed(os.path.join(HERE, "hadamard_dispatch.npz"),
                         dims=np.array([p[0] for p in picks]), base=np.array([p[1] for p in picks]),
                         scale=np.array([p[2] for p in picks]))
+    make_slicing(root, qh)
     print("wrote fixtures to", HERE)
+
+
+def make_slicing(root, qh):
+    """The load-time slicing functions of modeling/modeling_helpers.py:361-867, run unmodified on small seeded
+    layers (shapes with and without k / n padding).  Inputs are regenerated by the test from the stored fp16 weights;
+    stored per case: the reference's packed weight, scale (and bias / workspace length)."""
+    import modeling.modeling_helpers as mh
+
+    seeds = {}
+
+    def quantised(seed, out_f, in_f):
+        seeds[len(seeds)] = (seed, out_f, in_f)
+        w = _weights(seed, out_f, in_f)
+        pad_out = (256 - out_f % 256) % 256
+        _, packed, scale = qh.w4a16_quantize(w.t().contiguous(), 4, 128, None, pad_out)
+        ws = torch.zeros((out_f + pad_out) // 64 * 16, dtype=torch.int32)
+        return w, packed, scale, ws
+
+    blob = {}
+
+    def put(tag, w, outs, names):
+        # the fp16 input is regenerated by the test from (seed, shape) with the same generator call as _weights();
+        # a checksum of its bits guards against a change of the generator
+        blob[tag + "_w_sum"] = np.int64(w.numpy().view(np.uint16).astype(np.int64).sum())
+        for n, o in zip(names, outs):
+            if o is not None:
+                blob[f"{tag}_{n}"] = o.numpy()
+
+    # Llama-style MLP: hidden 256 (the reference's column slicers assume an unpadded hidden size), intermediate
+    # 384 -> 320 (320 needs 192 columns / 64 rows of padding)
+    hidden, inter, red = 256, 384, 320
+    w, packed, scale, ws = quantised(21, inter, hidden)
+    put("up", w, mh.slice_w4a16_up_gate_proj(packed, scale, ws, hidden, inter, red, packed.shape), ("packed", "scale", "ws"))
+    w, packed, scale, ws = quantised(22, hidden, inter)
+    put("down", w, mh.slice_w4a16_down_proj(packed, scale, ws, hidden, inter, red, packed.shape), ("packed", "scale", "ws"))
+    # attention: 3 heads x 64 -> 48 (q/k keep the first halves of both rotary halves, v/o the leading dims)
+    nheads, hd, rhd = 3, 64, 48
+    w, packed, scale, ws = quantised(23, nheads * hd, hidden)
+    bias = torch.linspace(-1, 1, nheads * hd).to(torch.float16)
+    blob["qk_bias_in"] = bias.numpy()
+    put("qk", w, mh.slice_w4a16_qk_proj(packed, bias, scale, ws, hidden, nheads, hd, rhd, packed.shape),
+        ("packed", "bias", "scale", "ws"))
+    w, packed, scale, ws = quantised(24, nheads * hd, hidden)
+    put("v", w, mh.slice_w4a16_v_proj(packed, scale, ws, hidden, nheads, hd, rhd, packed.shape), ("packed", "scale", "ws"))
+    w, packed, scale, ws = quantised(25, hidden, nheads * hd)
+    put("o", w, mh.slice_w4a16_o_proj(packed, scale, ws, hidden, nheads, hd, rhd, packed.shape), ("packed", "scale", "ws"))
+    # Mamba2-style mixer: 2 groups, 4 heads, intermediate 256 -> 192, state 32 -> 24
+    ng, nh, inter2, state, linter, lstate = 2, 4, 256, 32, 192, 24
+    proj = 2 * inter2 + 2 * ng * state + nh
+    w, packed, scale, ws = quantised(26, proj, hidden)
+    put("in", w, mh.slice_w4a16_in_proj(packed, scale, ws, hidden, ng, nh, inter2, state, linter, lstate, packed.shape),
+        ("packed", "scale", "ws"))
+    w, packed, scale, ws = quantised(27, hidden, inter2)
+    put("out", w, mh.slice_w4a16_out_proj(packed, scale, ws, hidden, ng, nh, inter2, linter, packed.shape),
+        ("packed", "scale", "ws"))
+    idx = torch.arange(nheads * hd).reshape(nheads, hd)
+    blob["slice_indices"] = mh.slice_indices(idx, hd, rhd).numpy()
+    blob["topk_head"] = mh.get_topk_head_indices(ng, nh, inter2 // nh, linter // nh).numpy()
+    blob["topk_state"] = mh.get_topk_ssm_state_indices(ng, state, lstate).numpy()
+    blob["inputs_seed_out_in"] = np.array([seeds[i] for i in range(len(seeds))], dtype=np.int64)   # order: up, down, qk, v, o, in, out
+    np.savez_compressed(os.path.join(HERE, "slicing.npz"), **blob)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,126 @@
+"""Load-time slicing of packed layers (uniql_b200.modeling_helpers) against fixtures made by running the reference's
+own functions (tests/golden/make_golden.py, make_slicing) on the same seeded layers.  CPU; bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from uniql_b200 import modeling_helpers as mh
+from uniql_b200.quantize import quantize_helpers as qh
+
+
+@pytest.fixture(scope="module")
+def gold(golden_dir):
+    return np.load(os.path.join(golden_dir, "slicing.npz"))
+
+
+ORDER = ["up", "down", "qk", "v", "o", "in", "out"]
+HIDDEN, INTER, RED = 256, 384, 320
+NHEADS, HD, RHD = 3, 64, 48
+NG, NH, INTER2, STATE, LINTER, LSTATE = 2, 4, 256, 32, 192, 24
+
+
+def _layer(gold, tag):
+    seed, out_f, in_f = (int(v) for v in gold["inputs_seed_out_in"][ORDER.index(tag)])
+    g = torch.Generator().manual_seed(seed)
+    w = (torch.randn(out_f, in_f, generator=g) * 0.02).to(torch.float16)
+    assert int(w.numpy().view(np.uint16).astype(np.int64).sum()) == int(gold[tag + "_w_sum"]), \
+        "the seeded generator no longer reproduces the fixture's input"
+    pad_out = (256 - out_f % 256) % 256
+    _, packed, scale = qh.w4a16_quantize(w.t().contiguous(), 4, 128, None, pad_out)
+    ws = torch.zeros((out_f + pad_out) // 64 * 16, dtype=torch.int32)
+    return packed, scale, ws
+
+
+def _same(got, want):
+    got = got.cpu().numpy()
+    assert got.shape == want.shape and got.dtype == want.dtype
+    if got.dtype == np.float16:
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    else:
+        assert np.array_equal(got, want)
+
+
+def _run(tag, packed, scale, ws, gold=None):
+    if tag == "up":
+        return mh.slice_w4a16_up_gate_proj(packed, scale, ws, HIDDEN, INTER, RED, packed.shape)
+    if tag == "down":
+        return mh.slice_w4a16_down_proj(packed, scale, ws, HIDDEN, INTER, RED, packed.shape)
+    if tag == "qk":
+        bias = torch.from_numpy(gold["qk_bias_in"]).to(packed.device)
+        p, b, s, w = mh.slice_w4a16_qk_proj(packed, bias, scale, ws, HIDDEN, NHEADS, HD, RHD, packed.shape)
+        return p, s, w, b
+    if tag == "v":
+        return mh.slice_w4a16_v_proj(packed, scale, ws, HIDDEN, NHEADS, HD, RHD, packed.shape)
+    if tag == "o":
+        return mh.slice_w4a16_o_proj(packed, scale, ws, HIDDEN, NHEADS, HD, RHD, packed.shape)
+    if tag == "in":
+        return mh.slice_w4a16_in_proj(packed, scale, ws, HIDDEN, NG, NH, INTER2, STATE, LINTER, LSTATE, packed.shape)
+    return mh.slice_w4a16_out_proj(packed, scale, ws, HIDDEN, NG, NH, INTER2, LINTER, packed.shape)
+
+
+@pytest.mark.parametrize("tag", ORDER)
+def test_slicers_match_reference(gold, tag):
+    packed, scale, ws = _layer(gold, tag)
+    out = _run(tag, packed, scale, ws, gold)
+    _same(out[0], gold[tag + "_packed"])
+    _same(out[1], gold[tag + "_scale"])
+    _same(out[2], gold[tag + "_ws"])
+    if tag == "qk":
+        _same(out[3], gold["qk_bias"])
+
+
+def test_index_helpers_match_reference(gold):
+    idx = torch.arange(NHEADS * HD).reshape(NHEADS, HD)
+    _same(mh.slice_indices(idx, HD, RHD), gold["slice_indices"])
+    _same(mh.get_topk_head_indices(NG, NH, INTER2 // NH, LINTER // NH), gold["topk_head"])
+    _same(mh.get_topk_ssm_state_indices(NG, STATE, LSTATE), gold["topk_state"])
+
+
+def test_sliced_layer_computes_the_sliced_product(gold):
+    """A sliced v_proj gives, per head, the first RHD channels of the full layer's output (dequantised weights)."""
+    packed, scale, ws = _layer(gold, "v")
+    p2, s2, _ = mh.slice_w4a16_v_proj(packed, scale, ws, HIDDEN, NHEADS, HD, RHD, packed.shape)
+    full = qh.w4a16_dequantize(packed, scale)[:HIDDEN, :NHEADS * HD].float()
+    part = qh.w4a16_dequantize(p2, s2)[:HIDDEN, :NHEADS * RHD].float()
+    want = full.reshape(HIDDEN, NHEADS, HD)[:, :, :RHD].reshape(HIDDEN, -1)
+    assert torch.equal(part, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag", ORDER)
+def test_slicers_on_the_gpu_match_reference(gold, tag):
+    """Same functions with the tensors on the GPU (o / out re-quantise through uniql_w4a16_quantize)."""
+    packed, scale, ws = _layer(gold, tag)
+    out = _run(tag, packed.cuda(), scale.cuda(), ws.cuda(), gold)
+    assert out[0].is_cuda and out[1].is_cuda
+    _same(out[0], gold[tag + "_packed"])
+    _same(out[1], gold[tag + "_scale"])
+    _same(out[2], gold[tag + "_ws"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,k,keep", [(320, 256, 200), (1000, 384, 777), (4096, 1024, 2500)])
+def test_gather_and_dequantize_kernels_against_the_host_path(n, k, keep):
+    """The two CUDA primitives on random index lists, against the unpack -> index -> repack path on the CPU."""
+    from uniql_b200 import ops
+    g = torch.Generator().manual_seed(n + k)
+    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.float16)
+    _, packed, scale = qh.w4a16_quantize(w.t().contiguous(), 4, 128, None, (256 - n % 256) % 256)
+    idx = torch.randperm(n, generator=g)[:keep]
+    zero_from = k - 37
+    want_p, want_s, n_pad = mh._select_columns(packed, scale, k, zero_from, idx, True)
+    got_p, got_s = ops.w4a16_gather_columns(packed.cuda(), scale.cuda(), idx, n_pad, zero_from)
+    assert torch.equal(got_p.cpu(), want_p) and torch.equal(got_s.cpu().view(torch.int16), want_s.view(torch.int16))
+    holes = idx.clone()
+    holes[::7] = -1                                            # negative entries give zero columns
+    got_p2, got_s2 = ops.w4a16_gather_columns(packed.cuda(), scale.cuda(), holes, n_pad)
+    codes = qh.unpack_w4a16_permute_weights(got_p2.cpu(), k, n_pad, 4, qh.get_w4a16_weight_perms(), 128)
+    assert int(codes[:, :keep][:, ::7].abs().max()) == 0
+    assert float(qh.unpermute_group_scales(got_s2.cpu())[:, :keep][:, ::7].abs().max()) == 0.0
+    rows = torch.randperm(k, generator=g)[:k // 2 + 3]
+    deq = qh.w4a16_dequantize(packed, scale)[:, :n]            # [Kp, n]
+    want = deq[rows].t().contiguous()
+    got = ops.w4a16_dequantize_rows(packed.cuda(), scale.cuda(), rows, n)
+    assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))

@@ -208,3 +208,41 @@ def w4a16_quantize(weight: torch.Tensor, group_scale: torch.Tensor | None = None
                                           _stream_handle(dev))
     check(code, "uniql_w4a16_quantize")
     return w_ref, packed, scales
+
+
+def w4a16_gather_columns(weight: torch.Tensor, scale: torch.Tensor, col_index: torch.Tensor, n_out_pad: int,
+                         zero_rows_from: int | None = None):
+    """New packed layer with output column c = source column col_index[c], zero-padded to n_out_pad columns; rows from
+    `zero_rows_from` on get code 0.  Returns (packed int32 [K/16, 2*n_out_pad], scales fp16 [K/128, n_out_pad])."""
+    _require_cuda(weight, "weight")
+    _require_cuda(scale, "scale")
+    dev = weight.device
+    size_k, n_src_pad = weight.shape[0] * 16, weight.shape[1] // 2
+    idx = col_index.to(device=dev, dtype=torch.int32).contiguous()
+    weight, scale = weight.contiguous(), scale.contiguous()
+    packed = torch.empty((size_k // 16, 2 * n_out_pad), dtype=torch.int32, device=dev)
+    scales = torch.empty((size_k // 128, n_out_pad), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        code = lib().uniql_w4a16_gather_columns(weight.data_ptr(), scale.data_ptr(), size_k, n_src_pad, idx.data_ptr(),
+                                                idx.numel(), size_k if zero_rows_from is None else zero_rows_from,
+                                                packed.data_ptr(), scales.data_ptr(), n_out_pad, _stream_handle(dev))
+    check(code, "uniql_w4a16_gather_columns")
+    return packed, scales
+
+
+def w4a16_dequantize_rows(weight: torch.Tensor, scale: torch.Tensor, row_index: torch.Tensor, n_real: int) -> torch.Tensor:
+    """fp16 [n_real, len(row_index)]: dequantised weights of the chosen input rows in nn.Linear layout."""
+    _require_cuda(weight, "weight")
+    _require_cuda(scale, "scale")
+    dev = weight.device
+    size_k, n_src_pad = weight.shape[0] * 16, weight.shape[1] // 2
+    idx = row_index.to(device=dev, dtype=torch.int32).contiguous()
+    if idx.numel() and (int(idx.min()) < 0 or int(idx.max()) >= size_k):
+        raise RuntimeError("row_index out of range")
+    weight, scale = weight.contiguous(), scale.contiguous()
+    out = torch.empty((n_real, idx.numel()), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        code = lib().uniql_w4a16_dequantize_rows(weight.data_ptr(), scale.data_ptr(), size_k, n_src_pad, idx.data_ptr(),
+                                                 idx.numel(), n_real, out.data_ptr(), idx.numel(), _stream_handle(dev))
+    check(code, "uniql_w4a16_dequantize_rows")
+    return out
