@@ -168,6 +168,12 @@ def make_slicing(root, qh):
     blob["slice_indices"] = mh.slice_indices(idx, hd, rhd).numpy()
     blob["topk_head"] = mh.get_topk_head_indices(ng, nh, inter2 // nh, linter // nh).numpy()
     blob["topk_state"] = mh.get_topk_ssm_state_indices(ng, state, lstate).numpy()
+    conv_ch = inter2 + 2 * ng * state
+    conv_w = _weights(28, conv_ch, 4).reshape(conv_ch, 1, 4)
+    conv_b = torch.linspace(-1, 1, conv_ch).to(torch.float16)
+    cw, cb = mh.slice_conv1d(conv_w, conv_b, ng, nh, inter2, state, linter, lstate)
+    blob["conv_w_out"], blob["conv_b_out"] = cw.numpy(), cb.numpy()
+    blob["norm_out"] = mh.slice_norm(torch.linspace(0, 1, inter2).to(torch.float16), ng, nh, inter2, linter).numpy()
     blob["inputs_seed_out_in"] = np.array([seeds[i] for i in range(len(seeds))], dtype=np.int64)   # order: up, down, qk, v, o, in, out
     np.savez_compressed(os.path.join(HERE, "slicing.npz"), **blob)
 

@@ -78,6 +78,17 @@ def test_index_helpers_match_reference(gold):
     _same(mh.get_topk_ssm_state_indices(NG, STATE, LSTATE), gold["topk_state"])
 
 
+def test_conv1d_and_norm_slicers_match_reference(gold):
+    conv_ch = INTER2 + 2 * NG * STATE
+    g = torch.Generator().manual_seed(28)
+    conv_w = (torch.randn(conv_ch, 4, generator=g) * 0.02).to(torch.float16).reshape(conv_ch, 1, 4)
+    conv_b = torch.linspace(-1, 1, conv_ch).to(torch.float16)
+    cw, cb = mh.slice_conv1d(conv_w, conv_b, NG, NH, INTER2, STATE, LINTER, LSTATE)
+    _same(cw, gold["conv_w_out"])
+    _same(cb, gold["conv_b_out"])
+    _same(mh.slice_norm(torch.linspace(0, 1, INTER2).to(torch.float16), NG, NH, INTER2, LINTER), gold["norm_out"])
+
+
 def test_sliced_layer_computes_the_sliced_product(gold):
     """A sliced v_proj gives, per head, the first RHD channels of the full layer's output (dequantised weights)."""
     packed, scale, ws = _layer(gold, "v")

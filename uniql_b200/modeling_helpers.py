@@ -213,3 +213,22 @@ def slice_w4a16_out_proj(weight, scale, workspace, hidden_size, n_groups, num_he
     idx = get_topk_head_indices(n_groups, num_heads, head_dim, load_intermediate_size // num_heads)
     packed, new_scale = _requantize_rows(weight, scale, size_k, hidden_size, idx, pad_n)
     return packed, new_scale, workspace
+
+
+def slice_conv1d(weight, bias, n_groups, num_heads, intermediate_size, ssm_state_size, load_intermediate_size,
+                 load_ssm_state_size):
+    """modeling_helpers.py:770-797 (Mamba2 conv1d over x | B | C): the channels that in_proj keeps."""
+    head_dim = intermediate_size // num_heads
+    heads = get_topk_head_indices(n_groups, num_heads, head_dim, load_intermediate_size // num_heads)
+    states = get_topk_ssm_state_indices(n_groups, ssm_state_size, load_ssm_state_size)
+    b0 = intermediate_size
+    c0 = b0 + n_groups * ssm_state_size
+    idx = torch.cat([heads, b0 + states, c0 + states]).to(weight.device)
+    return weight[idx].contiguous(), bias[idx].contiguous()
+
+
+def slice_norm(weight, n_groups, num_heads, intermediate_size, load_intermediate_size):
+    """modeling_helpers.py:800-806 (gated RMSNorm weight): the channels that in_proj keeps."""
+    head_dim = intermediate_size // num_heads
+    idx = get_topk_head_indices(n_groups, num_heads, head_dim, load_intermediate_size // num_heads)
+    return weight[idx.to(weight.device)].contiguous()
