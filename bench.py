@@ -24,15 +24,20 @@ sys.path.insert(0, ROOT)
 HIDDEN, INTER, QKV, LAYERS = 4096, 14336, 6144, 32
 SHAPES = {"qkv": (QKV, HIDDEN), "o": (HIDDEN, HIDDEN), "gate": (INTER, HIDDEN), "up": (INTER, HIDDEN),
           "down": (HIDDEN, INTER)}
-FALLBACK_HBM_GBS = 6650.0        # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
-# dram__bytes_read+write of one 14336x4096 m=1 launch, from the ncu capture summarised in
-# profiles/w4a16_gemv_14336x4096_m1.md
-NCU_TRAFFIC_GATE_M1 = 30_331_136
+FALLBACK_HBM_GBS = 6650.0        # HBM copy bandwidth of a B200 (GB/s), used only if MEASURED_PEAKS.json is absent
+# DRAM bytes read + written by one fused gate+up launch (two 14336x4096 projections, m = 1) as counted by the
+# profiler (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture of this kernel exists
+NCU_TRAFFIC_GATE_UP_M1 = None
 
 
 def linear_bytes(n, k, m):
     """Algorithmic bytes of one W4A16 linear: packed weights + group scales + activations in + out."""
     return k * n // 2 + (k // 128) * n * 2 + m * k * 2 + m * n * 2
+
+
+def gate_up_bytes(n, k, m):
+    """Algorithmic bytes of the fused gate+up launch: two packed weights + scales, activations in, one result out."""
+    return 2 * (k * n // 2 + (k // 128) * n * 2) + m * k * 2 + m * n * 2
 
 
 def step_bytes(m):
@@ -271,51 +276,108 @@ def build_stack(m, rank, world, device, layers):
     return stack
 
 
-def make_step(stack, world, rank, group, push=None, fused=None):
-    """Returns step(x) -> y running every projection of every layer once (no attention / activation maths:
-    q-shard stands in for the attention output and the gate shard for the MLP activation)."""
-    import torch
+def _triple(mod):
+    return (mod.weight, mod.scale, mod.bias, mod.out_features)
+
+
+def make_step(stack, world, rank, group, mode="none", comm=None, taps=None):
+    """Returns step(x) -> y running the projections of every layer: qkv -> o -> [gate, up, SwiGLU] -> Hadamard -> down
+    (no attention maths: the q shard stands in for the attention output).  Four launches per layer at decode sizes.
+    mode (world > 1): "fused" = cross-GPU sums and the feature gather inside the decode kernels, "push" = separate
+    push all-reduce kernels, "nccl" = torch.distributed collectives.  taps: list that receives the two row-parallel
+    outputs (o_proj, down_proj) of every layer."""
     import torch.distributed as dist
 
+    from uniql_b200 import fused as fz
     from uniql_b200 import ops, tp
     o_rows = tp.row_bounds(HIDDEN, world)[rank]
     d_rows = tp.row_bounds(INTER, world)[rank]
     sizes = [b - a for a, b in tp.column_bounds(INTER, world)]
     had_scale = 1.0 / (INTER ** 0.5)
 
+    def reduce_(t):
+        if mode == "push" and comm is not None:
+            comm.all_reduce(t)
+        else:
+            dist.all_reduce(t, group=group)
+
     def step(x):
+        m = x.shape[0]
         for mods in stack:
             qkv = mods["qkv"](x)
             att = qkv[:, :o_rows[1] - o_rows[0]]
-            if fused is not None:
-                o = mods["o"]
-                y = fused[0].linear_all_reduce(att, o.weight, o.scale, None, o.out_features)
+            if world == 1:
+                y = mods["o"](att)
+                h = fz.gate_up_swiglu(mods["gate"], mods["up"], y)
+                x = mods["down"](h)                        # Hadamard in the kernel prologue
+            elif mode == "fused" and m <= 16:
+                o, d = mods["o"], mods["down"]
+                y = comm.linear_all_reduce(att, o.weight, o.scale, None, o.out_features)
+                comm.gate_up_gather(y, _triple(mods["gate"]), _triple(mods["up"]), d_rows[0])
+                x = comm.down_gather_reduce(m, _triple(d), INTER, d_rows[0])
             else:
                 y = mods["o"](att)
-            if world > 1 and fused is None:
-                if push is not None:
-                    push.all_reduce(y)
+                reduce_(y)
+                hl = fz.gate_up_swiglu(mods["gate"], mods["up"], y)
+                if mode == "push" and comm is not None and m * INTER <= comm.max_elems:
+                    h = comm.all_gather_features(hl, sizes)
                 else:
-                    dist.all_reduce(y, group=group)
-            gate = mods["gate"](y)
-            up = mods["up"](y)
-            if world == 1:
-                x = mods["down"](gate)                     # Hadamard fused into the call
-            else:
-                h = push.all_gather_features(gate, sizes) if push is not None else tp.all_gather_features(gate, sizes, group)
+                    h = tp.all_gather_features(hl, sizes, group)
                 h = ops.hadamard(h, had_scale)
-                if fused is not None:
-                    d = mods["down"]
-                    x = fused[1].linear_all_reduce(h[:, d_rows[0]:d_rows[1]], d.weight, d.scale, None, d.out_features)
-                else:
-                    x = mods["down"](h[:, d_rows[0]:d_rows[1]])
-                    if push is not None:
-                        push.all_reduce(x)
-                    else:
-                        dist.all_reduce(x, group=group)
-            del up
+                x = mods["down"](h[:, d_rows[0]:d_rows[1]])
+                reduce_(x)
+            if taps is not None:
+                taps.append((y, x))
         return x
     return step
+
+
+def parity_numbers(y, y_ref):
+    """The linear parity rule: max-normalised error, and the worst ratio of |y - y_ref| to
+    1e-2 |y_ref| + 1e-2 rms(y_ref).  Passing means max_rel <= 1e-2 and worst <= 1."""
+    import torch
+    y, y_ref = y.float(), y_ref.float()
+    denom = max(float(y_ref.abs().max()), 1e-6)
+    max_rel = float((y - y_ref).abs().max()) / denom
+    rms = float(y_ref.double().pow(2).mean().sqrt())
+    worst = float(((y - y_ref).abs() / (1e-2 * y_ref.abs() + 1e-2 * rms + 1e-6)).max())
+    finite = bool(torch.isfinite(y).all())
+    return max_rel, worst, finite
+
+
+def tp_parity(stack, world, rank, group, comm, x_dev, device):
+    """Layer 0 through the fused exchanges and through NCCL on the same input, both compared on rank 0 with the
+    unsharded layer built from the same seeds.  Returns the dict printed as "tp_parity" (rank 0) or None."""
+    import torch
+
+    from uniql_b200 import fused as fz
+    m = x_dev.shape[0]
+    got = {}
+    for mode in ("fused", "nccl"):
+        taps = []
+        make_step(stack[:1], world, rank, group, mode=mode, comm=comm, taps=taps)(x_dev)
+        torch.cuda.synchronize()
+        got[mode] = [t.clone() for t in taps[0]]
+    if rank != 0:
+        return None
+    full = build_stack(m, 0, 1, device, 1)[0]
+    qkv = full["qkv"](x_dev)
+    qw, aw = QKV // world, HIDDEN // world
+    att = torch.cat([qkv[:, r * qw:r * qw + aw] for r in range(world)], dim=1)
+    y_ref = full["o"](att)
+    out = {"vs": "unsharded layer 0 (same seeds) on rank 0, rule of the linear parity tests", "ok": True}
+    for mode in ("fused", "nccl"):
+        # each row-parallel output is compared with the unsharded linear applied to the same (gathered) input
+        y = got[mode][0]
+        h = fz.gate_up_swiglu(full["gate"], full["up"], y)
+        x_ref = full["down"](h)
+        r0 = parity_numbers(y, y_ref)
+        r1 = parity_numbers(got[mode][1], x_ref)
+        out[mode] = {"o_proj_max_rel": r0[0], "o_proj_worst": r0[1], "down_proj_max_rel": r1[0], "down_proj_worst": r1[1]}
+        if not (r0[2] and r1[2] and r0[0] <= 1e-2 and r0[1] <= 1.0 and r1[0] <= 1e-2 and r1[1] <= 1.0):
+            out["ok"] = False
+    out["max_rel"] = max(out["fused"]["o_proj_max_rel"], out["fused"]["down_proj_max_rel"])
+    return out
 
 
 def _log(msg):
@@ -336,6 +398,129 @@ def _arm_deadline(seconds):
     t.daemon = True
     t.start()
     return t
+
+
+def _graph_of(fn, stream):
+    """Capture fn() into a CUDA graph on `stream` (after one eager call) and return the graph."""
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        fn()
+    return g
+
+
+def _time_replays(graph, stream, reps, warm=3):
+    """CUDA-event time of `reps` back-to-back replays, in microseconds per replay."""
+    import torch
+    for _ in range(warm):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        graph.replay()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def _random_layer(gen, n, k, device, bias=False):
+    """A packed layer with random codes and plausible scales (timing only: no quantiser run, no checkpoint)."""
+    import torch
+
+    from uniql_b200.quantize.quant_linear_layers import W4A16B16O16Linear
+    lin = W4A16B16O16Linear(k, n, bias=bias, device="meta")
+    lin._buffers["weight"] = torch.randint(-2 ** 31, 2 ** 31 - 1, (lin.size_k // 16, 2 * lin.size_n), generator=gen,
+                                           device=device, dtype=torch.int64).to(torch.int32)
+    lin._buffers["scale"] = (torch.rand(lin.size_k // 128, lin.size_n, generator=gen, device=device) * 0.004 + 0.001).half()
+    lin._buffers["workspace"] = torch.zeros(lin.size_n // 64 * 16, dtype=torch.int32, device=device)
+    if bias:
+        lin.bias = torch.nn.Parameter((torch.randn(n, generator=gen, device=device) * 0.1).half(), requires_grad=False)
+    return lin
+
+
+def qwen_decode_leg(device, stream, peak, batches=(1, 8, 64)):
+    """BASELINE configuration 4 on one GPU: 4-bit embedding gather -> 28 Qwen2.5-7B layers (q/k/v with bias, o, gate, up,
+    down; no attention maths) -> lm_head 152064 x 3584, one CUDA graph per decode batch, random packed weights."""
+    import torch
+
+    from uniql_b200 import fused as fz
+    from uniql_b200 import ops
+    hidden, inter, kv, vocab, nlayers = 3584, 18944, 512, 152064, 28
+    gen = torch.Generator(device=device).manual_seed(11)
+    table = torch.randint(-2 ** 31, 2 ** 31 - 1, (vocab, hidden // 8), generator=gen, device=device, dtype=torch.int64).to(torch.int32)
+    tscale = (torch.rand(vocab, generator=gen, device=device) * 0.01 + 0.001).half()
+    layers = []
+    for _ in range(nlayers):
+        layers.append({"q": _random_layer(gen, hidden, hidden, device, True), "k": _random_layer(gen, kv, hidden, device, True),
+                       "v": _random_layer(gen, kv, hidden, device, True), "o": _random_layer(gen, hidden, hidden, device),
+                       "gate": _random_layer(gen, inter, hidden, device), "up": _random_layer(gen, inter, hidden, device),
+                       "down": _random_layer(gen, hidden, inter, device)})
+    head = _random_layer(gen, vocab, hidden, device)
+
+    def lin_bytes(mod, m):
+        return mod.size_k * mod.size_n // 2 + (mod.size_k // 128) * mod.size_n * 2 + m * mod.size_k * 2 + m * mod.out_features * 2
+
+    out = {}
+    for b in batches:
+        ids = torch.randint(0, vocab, (b,), generator=gen, device=device, dtype=torch.int64)
+
+        def step():
+            x = ops.w4_embedding(ids, table, tscale)
+            for L in layers:
+                q, _, _ = fz.qkv_proj(L["q"], L["k"], L["v"], x)
+                x = fz.linear_residual(L["o"], q, x)
+                h = fz.gate_up_swiglu(L["gate"], L["up"], x)
+                x = fz.linear_residual(L["down"], h, x)
+            return head(x)
+
+        g = _graph_of(step, stream)
+        us = _time_replays(g, stream, 10)
+        nbytes = b * (hidden // 2 + 2 + 8 + 2 * hidden) + lin_bytes(head, b) + sum(lin_bytes(mod, b) for L in layers for mod in L.values())
+        out[f"batch{b}"] = {"ms_per_step": us / 1e3, "decode_tok_s": b / (us * 1e-6), "gbs": nbytes / (us * 1e-6) / 1e9,
+                            "frac_of_hbm_peak": nbytes / (us * 1e-6) / 1e9 / peak,
+                            "launches_per_step": 2 + 4 * nlayers if b <= 16 else None}
+        del g
+    out["workload"] = ("Qwen2.5-7B W4A16 linear stack: embedding gather, 28 x (q/k/v+bias, o+residual, gate/up SwiGLU, "
+                       "down+residual), lm_head 152064x3584; random packed weights, seeded uniform token ids, 1 GPU")
+    return out
+
+
+def mamba_decode_leg(device, stream, peak, batches=(1, 16)):
+    """BASELINE configuration 5 on one GPU: 56 x (in_proj 18560 x 4096, out_proj 4096 x 8192 with its 8192-point online
+    Hadamard); the first 8192 columns of in_proj's output stand in for the SSM output."""
+    import torch
+
+    from uniql_b200.quantize.quant_linear_layers import W4A16B16O16HadLinear
+    d_model, d_inner, d_in, nlayers = 4096, 8192, 18560, 56
+    gen = torch.Generator(device=device).manual_seed(13)
+    layers = []
+    for _ in range(nlayers):
+        out_proj = _random_layer(gen, d_model, d_inner, device)
+        out_proj.__class__ = W4A16B16O16HadLinear
+        layers.append((_random_layer(gen, d_in, d_model, device), out_proj))
+    out = {}
+    for b in batches:
+        x0 = torch.randn(b, d_model, generator=gen, device=device).half()
+
+        def step():
+            x = x0
+            for in_proj, out_proj in layers:
+                z = in_proj(x)
+                x = out_proj(z[:, :d_inner])
+            return x
+
+        g = _graph_of(step, stream)
+        us = _time_replays(g, stream, 10)
+        nbytes = sum(mod.size_k * mod.size_n // 2 + (mod.size_k // 128) * mod.size_n * 2 + b * mod.size_k * 2 +
+                     b * mod.out_features * 2 for pair in layers for mod in pair)
+        out[f"batch{b}"] = {"ms_per_step": us / 1e3, "decode_tok_s": b / (us * 1e-6), "gbs": nbytes / (us * 1e-6) / 1e9,
+                            "frac_of_hbm_peak": nbytes / (us * 1e-6) / 1e9 / peak}
+        del g
+    out["workload"] = "Mamba2-8b block linears x56 (in_proj 18560x4096, out_proj 4096x8192 + 8192-pt Hadamard), random packed weights, 1 GPU"
+    return out
 
 
 def run_ours(args):
@@ -361,26 +546,26 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
         group = dist.group.WORLD
     import uniql_b200  # noqa: F401  (fails loudly if the library is missing)
+    from uniql_b200 import fused as fz
     from uniql_b200 import ops
 
     m = args.batch
     layers = args.layers
+    peak, peak_kind, peaks = measured_peaks()
     _log("process group up, building the synthetic stack")
     stack = build_stack(m, rank, world, device, layers)
     _log("stack built")
-    push, fused, collective = None, None, "none"
+    comm, collective = None, "none"
     if world > 1:
-        collective = os.environ.get("UNIQL_TP_COLLECTIVE", "fused" if m <= 16 else "push")
+        collective = os.environ.get("UNIQL_TP_COLLECTIVE", "fused")
         if collective in ("push", "fused"):
             from uniql_b200 import tp
-            push = tp.PushAllReduce(group, max_elems=max(16 * 16384, m * INTER), device=device)
-        if collective == "fused":
-            # one channel per call-site shape (o_proj, down_proj): their epochs advance independently
-            fused = [tp.PushAllReduce(group, max_elems=16 * HIDDEN, device=device) for _ in range(2)]
+            # 16 batch rows of the widest activation row (the 14336 intermediate features)
+            comm = tp.PushAllReduce(group, max_elems=16 * 16384, device=device)
         _log(f"collective: {collective}")
-    step = make_step(stack, world, rank, group, push, fused)
+    step = make_step(stack, world, rank, group, collective, comm)
     gen = torch.Generator(device=device).manual_seed(7)
-    x_dev = torch.randn(m, HIDDEN, generator=gen, device=device).to(torch.float16)
+    x_dev = (torch.randn(m, HIDDEN, generator=gen, device=device) * 0.05).to(torch.float16)
     x_host = x_dev.cpu().pin_memory()
     y_host = torch.empty((m, HIDDEN), dtype=torch.float16).pin_memory()
     stream = torch.cuda.Stream(device=device)
@@ -391,8 +576,20 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    launches_per_step = layers * (len(SHAPES) + 1)      # 5 linears + 1 Hadamard per layer
+    launches_per_layer = 4 if (m <= 16 and (world == 1 or collective == "fused")) else None
+    parity = None
     with torch.cuda.stream(stream):
+        # ---- tensor parallel: check the sharded result before timing anything ----
+        if world > 1 and collective == "fused" and m <= 16:
+            parity = tp_parity(stack, world, rank, group, comm, x_dev, device)
+            ok = torch.tensor([1 if (parity is None or parity["ok"]) else 0], device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                if rank == 0:
+                    print(json.dumps({"tp_parity": parity, "error": "tensor-parallel result differs from the unsharded layer"}))
+                sys.stdout.flush()
+                os._exit(4)
+            _log("tp parity ok")
         for _ in range(2):
             y = step(x_dev)
         torch.cuda.synchronize()
@@ -441,6 +638,19 @@ def run_ours(args):
         ms = e0.elapsed_time(e1)
         _log(f"timed region done: {ms / args.steps:.3f} ms/step")
 
+        # ---- spread of single steps: 200 replays, one event pair each ----
+        pct = None
+        if graph is not None:
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
+            barrier()
+            for a, b in evs:
+                a.record(stream)
+                graph.replay()
+                b.record(stream)
+            barrier()
+            ts = sorted(a.elapsed_time(b) for a, b in evs)
+            pct = {"p10_ms": ts[20], "p50_ms": ts[100], "p90_ms": ts[180], "replays": 200}
+
         # ---- end to end through the module API with host buffers (eager calls) ----
         def e2e_step():
             x_in = x_host.to(device, non_blocking=True)
@@ -472,34 +682,56 @@ def run_ours(args):
         clocks = sampler.stop() if rank == 0 else None
         _log("e2e done")
 
-        # ---- dominant kernel alone: gate projection (14336/world x 4096), one launch per layer so every
-        # launch streams different weights (L2-cold), timed with CUDA events on the launching stream ----
+        # ---- the same stack at decode batches 16 and 64 (extra keys; the headline stays batch `m`) ----
+        batch_curve = {}
+        for bm in (16, 64):
+            if bm == m:
+                continue
+            xb = (torch.randn(bm, HIDDEN, generator=gen, device=device) * 0.05).to(torch.float16)
+            bmode = collective if (bm <= 16 or collective != "fused") else "push"
+            bstep = make_step(stack, world, rank, group, bmode, comm)
+            try:
+                gb = _graph_of(lambda: bstep(xb), stream)
+                us = _time_replays(gb, stream, 5)
+            except Exception as e:  # pragma: no cover
+                gb, us = None, None
+                torch.cuda.synchronize()
+                batch_curve[f"batch{bm}"] = {"error": type(e).__name__}
+            if world > 1:
+                barrier()
+            if us is not None:
+                batch_curve[f"batch{bm}"] = {"ms_per_step": us / 1e3, "decode_tok_s": bm / (us * 1e-6) * (layers / LAYERS)}
+            del gb
+
+        # ---- dominant kernel alone: the fused gate+up launch (2 x 14336/world x 4096 + SwiGLU), one launch per layer so
+        # every launch streams different weights (L2-cold), timed with CUDA events on the launching stream ----
+        pairs = [(mods["gate"], mods["up"]) for mods in stack]
+        xg = (torch.randn(m, HIDDEN, generator=gen, device=device) * 0.05).to(torch.float16)
+        n_gate_local = pairs[0][0].out_features
+        og = torch.empty((m, n_gate_local), dtype=torch.float16, device=device)
+
+        def pair_pass():
+            for g, u in pairs:
+                if m <= 16:
+                    ops.w4a16_linear_group(xg, [_triple(g), _triple(u)], epilogue="swiglu", outs=[og])
+                else:
+                    fz.gate_up_swiglu(g, u, xg)
+
+        ggraph = _graph_of(pair_pass, stream)
+        pair_us = _time_replays(ggraph, stream, 10) / len(pairs)
+        # a single projection of the same pair, for comparison with the unfused launch
         gate_mods = [mods["gate"] for mods in stack]
-        xg = torch.randn(m, HIDDEN, generator=gen, device=device).to(torch.float16)
-        og = torch.empty((m, gate_mods[0].out_features), dtype=torch.float16, device=device)
+        og1 = torch.empty((m, n_gate_local), dtype=torch.float16, device=device)
 
         def gate_pass():
             for g in gate_mods:
-                ops.w4a16_linear(xg, g.weight, g.scale, None, g.out_features, out=og)
+                ops.w4a16_linear(xg, g.weight, g.scale, None, g.out_features, out=og1)
 
-        gate_pass()
-        torch.cuda.synchronize()
-        ggraph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(ggraph, stream=stream):
-            gate_pass()
-        for _ in range(3):
-            ggraph.replay()
-        torch.cuda.synchronize()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 10
-        g0.record(stream)
-        for _ in range(reps):
-            ggraph.replay()
-        g1.record(stream)
-        torch.cuda.synchronize()
-        gate_us = g0.elapsed_time(g1) * 1e3 / (reps * len(gate_mods))
+        g1 = _graph_of(gate_pass, stream)
+        gate_us = _time_replays(g1, stream, 10) / len(gate_mods)
+        del ggraph, g1
 
-        # ---- prefill regime: the same gate projection at m = 4096 through the tcgen05 kernel ----
+        # ---- prefill regime: the gate projection at m = 4096 through the tcgen05 kernel ----
         mp = 4096
         xp = torch.randn(mp, HIDDEN, generator=gen, device=device).to(torch.float16)
         op = torch.empty((mp, gate_mods[0].out_features), dtype=torch.float16, device=device)
@@ -516,23 +748,21 @@ def run_ours(args):
         # the same projection at batch 64 (small-batch tcgen05 kernel), one launch per distinct weight set
         x64 = torch.randn(64, HIDDEN, generator=gen, device=device).to(torch.float16)
         o64 = torch.empty((64, gate_mods[0].out_features), dtype=torch.float16, device=device)
-        for g in gate_mods[:3]:
-            ops.w4a16_linear(x64, g.weight, g.scale, None, g.out_features, out=o64)
-        torch.cuda.synchronize()
-        g64 = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g64, stream=stream):
+
+        def pass64():
             for g in gate_mods:
                 ops.w4a16_linear(x64, g.weight, g.scale, None, g.out_features, out=o64)
-        g64.replay()
-        torch.cuda.synchronize()
-        p0.record(stream)
-        g64.replay()
-        p1.record(stream)
-        torch.cuda.synchronize()
-        m64_us = p0.elapsed_time(p1) * 1e3 / len(gate_mods)
-        del xp, op
-        aux = (aux_kernels(device, stream, measured_peaks()[0])
-               if (world == 1 and not os.environ.get("UNIQL_BENCH_NO_AUX")) else None)
+
+        g64 = _graph_of(pass64, stream)
+        m64_us = _time_replays(g64, stream, 3, warm=1) / len(gate_mods)
+        del xp, op, g64
+        aux = qwen = mamba = None
+        if world == 1 and not os.environ.get("UNIQL_BENCH_NO_AUX"):
+            aux = aux_kernels(device, stream, peak)
+            torch.cuda.empty_cache()
+            qwen = qwen_decode_leg(device, stream, peak)
+            torch.cuda.empty_cache()
+            mamba = mamba_decode_leg(device, stream, peak)
 
     def rank_max(v):
         if world == 1:
@@ -545,6 +775,7 @@ def run_ours(args):
     ms_e2e = rank_max(ms_e2e)
     if ms_e2e_graph is not None:
         ms_e2e_graph = rank_max(ms_e2e_graph)
+    pair_us = rank_max(pair_us)
     gate_us = rank_max(gate_us)
     prefill_us = rank_max(prefill_us)
     m64_us = rank_max(m64_us)
@@ -554,10 +785,9 @@ def run_ours(args):
         t_step = ms / args.steps * 1e-3
         scale_l = LAYERS / layers
         nbytes = step_bytes(m) / scale_l
-        peak, peak_kind, _ = measured_peaks()
         n_gate = SHAPES["gate"][0] // world
-        gate_bytes = linear_bytes(n_gate, HIDDEN, m)
-        achieved = gate_bytes / (gate_us * 1e-6) / 1e9
+        pair_bytes = gate_up_bytes(n_gate, HIDDEN, m)
+        achieved = pair_bytes / (pair_us * 1e-6) / 1e9
         t_e2e = ms_e2e / e2e_steps * 1e-3
         line = {
             "metric": "w4a16_linear_m1_hbm_gbs", "value": nbytes / t_step / 1e9, "unit": "GB/s",
@@ -565,10 +795,11 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16xint4->f32acc", "data": "synthetic",
             "config": {"workload": f"Llama-3.1-8B decoder projection set x{layers} layers, W4A16 g128, "
-                                   f"decode batch {m}, 14336-pt online Hadamard on down_proj input",
+                                   f"decode batch {m}: qkv, o, gate+up with SwiGLU, 14336-pt online Hadamard + down",
                        "parallelism": f"tp{world}", "launch": mode,
-                       "collective": {"fused": "sum over ranks fused into the row-parallel decode kernel "
-                                               "(uniql_w4a16_linear_allreduce); feature gather by uniql_allreduce_push",
+                       "launches_per_layer": launches_per_layer,
+                       "collective": {"fused": "row-parallel sums and the feature gather inside the decode kernels "
+                                               "(peer stores over NVLink, epoch-tagged words; no separate collective launch)",
                                       "push": "uniql_allreduce_push (peer stores over NVLink, one kernel)",
                                       "nccl": "NCCL all_reduce / all_gather", "none": "none"}[collective],
                        "l2": "each step streams %.2f GB of distinct weights per GPU (> 126 MB L2): no flush needed"
@@ -576,20 +807,29 @@ def run_ours(args):
             "decode_tok_s": m / (t_step * scale_l),
             "pct_of_hbm_peak": {"of_measured_%.0f" % peak: nbytes / world / t_step / 1e9 / peak,
                                 "of_nominal_8000": nbytes / world / t_step / 1e9 / 8000.0},
-            "roofline": {"bound": "hbm", "kernel": f"w4a16_gemv_kernel<1> {n_gate}x{HIDDEN} m={m}",
+            "roofline": {"bound": "hbm",
+                         "kernel": f"w4a16_decode_kernel, gate+up 2x{n_gate}x{HIDDEN} with SwiGLU epilogue, m={m}",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                         "frac": achieved / peak, "us_per_launch": gate_us,
-                         "traffic": NCU_TRAFFIC_GATE_M1 if (world == 1 and m == 1) else None},
+                         "frac": achieved / peak, "us_per_launch": pair_us, "bytes_per_launch": pair_bytes,
+                         "traffic": NCU_TRAFFIC_GATE_UP_M1 if (world == 1 and m == 1) else None},
+            "single_projection": {"kernel": f"w4a16_decode_kernel, gate {n_gate}x{HIDDEN}, m={m}", "us_per_launch": gate_us,
+                                  "gbs": linear_bytes(n_gate, HIDDEN, m) / (gate_us * 1e-6) / 1e9,
+                                  "frac_of_hbm_peak": linear_bytes(n_gate, HIDDEN, m) / (gate_us * 1e-6) / 1e9 / peak},
+            "step_percentiles": pct,
             "e2e": None,
             "m4096_tflops": {"value": world * 2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12,
                              "kernel": f"w4a16_gemm_tc_kernel {n_gate}x{HIDDEN} m=4096 per GPU", "us_per_launch": prefill_us,
                              "frac_of_measured_bf16_burst": (2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12)
-                             / float(measured_peaks()[2].get("bf16_tflops", 1590.0)),
+                             / float(peaks.get("bf16_tflops", 1590.0)),
                              "frac_of_nominal_2250": (2.0 * 4096 * n_gate * HIDDEN / (prefill_us * 1e-6) / 1e12) / 2250.0},
             "m64_us": {"value": m64_us, "kernel": f"w4a16_gemm_tc_swap_kernel {n_gate}x{HIDDEN} m=64 per GPU",
                        "weight_gbs": (n_gate * HIDDEN / 2 + n_gate * HIDDEN / 64) / (m64_us * 1e-6) / 1e9},
+            "batch_curve": batch_curve,
             "aux_kernels": aux,
-            "gpu_launches": launches_per_step * args.steps,
+            "qwen25_7b_decode": qwen,
+            "mamba2_8b_decode": mamba,
+            "tp_parity": parity,
+            "gpu_launches": (launches_per_layer or 0) * layers * args.steps,
             "clocks": clocks,
             "kernel_status_word": status,
         }

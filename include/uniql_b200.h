@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define UNIQL_ABI_VERSION 1
+#define UNIQL_ABI_VERSION 2
 
 enum {
   UNIQL_OK = 0,
@@ -66,6 +66,7 @@ int uniql_last_cuda_error(void);
  *   hadamard_dim  0, or k: apply y = H_k * x / sqrt(k) to every row of A first
  *              (quantize/quant_hadamard_layers.py:16-18 placed in front of the linear);
  *              the transformed rows are rounded to fp16 exactly as the separate module would.
+ *              For m <= 4 the transform runs inside the linear kernel, otherwise as a kernel in front of it.
  *   scratch    device buffer of at least uniql_w4a16_scratch_bytes(m, n, k, hadamard_dim) bytes,
  *              256-byte aligned.  Its first UNIQL_SCRATCH_COUNTER_BYTES bytes must be zero before the
  *              first call and are left zero by every call; do not share one scratch buffer between
@@ -179,7 +180,9 @@ int uniql_hadamard_base_matrix(int base, int8_t* out);
  *
  *   uniql_comm_create   allocates this rank's staging block (cudaMalloc, once, at set-up) and writes its CUDA IPC
  *                       handle (uniql_comm_handle_bytes() bytes) to `handle_out` (HOST pointer).  max_elems: largest
- *                       message in fp16 elements (multiple of 8, at most 524288).
+ *                       message in fp16 elements (multiple of 8, at most 524288).  The same number sizes the areas the
+ *                       decode linear's own exchanges use: read it as 16 batch rows of the widest activation row
+ *                       (n <= max_elems / 16 for UNIQL_TP_REDUCE, features <= max_elems / 16 for the gather).
  *   uniql_comm_connect  `all_handles` (HOST pointer) = the handles of ranks 0..world-1 concatenated in rank order
  *                       (exchange them with any host-side channel); opens the peers' blocks.
  *   uniql_allreduce_push  out[i] = sum over ranks of in[i], summed in rank order in fp32, identical on every rank;
@@ -194,19 +197,83 @@ int uniql_comm_destroy(void* comm);
 int uniql_allreduce_push(void* comm, const void* in, void* out, int64_t count, int* status_word, void* stream);
 
 /*
- * Row-parallel W4A16 linear with the cross-GPU sum fused into the kernel (decode sizes, m <= 16, m*n within the
- * communicator's max_elems): D = sum over ranks of (A_rank * dequant(B_rank)) (+ bias), identical on every rank.
- * The CTA that finishes a column group stores its fp16 partial, tagged with an epoch, straight into every rank's
- * staging block over NVLink and then adds up the partials that arrived in its own block (rank order, fp32) —
- * the same arithmetic as uniql_w4a16_linear followed by uniql_allreduce_push, in one launch.  No counterpart in
- * the reference.  Use one communicator per call site shape (e.g. one for o_proj, one for down_proj): calls through a
- * communicator must have the same (m, n, k) on all ranks and the same sequence of calls.  Other arguments as for
+ * Row-parallel W4A16 linear with the cross-GPU sum fused into the kernel (decode sizes, m <= 16, n / 64 within the
+ * communicator's block capacity max_elems / 1024): D = sum over ranks of (A_rank * dequant(B_rank)) (+ bias), identical
+ * on every rank.  The warp that finishes a 64-column block stores its fp16 partial, tagged with an epoch, straight into
+ * every rank's staging block over NVLink and then adds up the partials that arrived in its own block (rank order,
+ * fp32): the same arithmetic as uniql_w4a16_linear followed by uniql_allreduce_push, in one launch.  No counterpart in
+ * the reference.  Staging words are addressed per 64-column block and every block keeps its own epoch, so calls of
+ * different shapes may share a communicator; all ranks must issue the same sequence of calls.  Other arguments as for
  * uniql_w4a16_linear (no Hadamard option).
  */
 int uniql_w4a16_linear_allreduce(void* comm, const void* A, int64_t lda, const void* B, const void* s,
                                  const void* bias, void* D, int64_t ldd, int64_t m, int64_t n, int64_t n_out,
                                  int64_t k, int groupsize, void* scratch, size_t scratch_bytes, int* status_word,
                                  void* stream);
+
+/*
+ * Grouped decode launch (m <= 16): up to UNIQL_MAX_PROJ projections that read the same activations run as ONE kernel,
+ * with the elementwise work the reference's blocks do around them folded into its epilogue / prologue.  Replaces
+ *   - gate_proj, up_proj and act_fn(gate) * up as three launches (modeling/llama/llama_qblocks.py:48-51):
+ *     two projections + UNIQL_EPILOGUE_SWIGLU -> proj[0].D = silu(x W_gate + b_gate) * (x W_up + b_up), with the same
+ *     fp16 roundings as the separate modules (proj[1].D is not written); both projections must have the same n, n_out;
+ *   - q_proj, k_proj, v_proj as three launches (:104-106): three projections, UNIQL_EPILOGUE_NONE, each writing its own D;
+ *   - the residual add after o_proj / down_proj: `residual` (fp16 [m, n_out], row stride ldr, may alias D) is added to
+ *     the rounded result (single projection or SwiGLU pair);
+ *   - the Hadamard module in front of down_proj / out_proj (quantize/quant_hadamard_layers.py:16-18): hadamard_dim = k
+ *     transforms every activation row first (rounded to fp16 as the module would); for m <= 4 the transform runs in the
+ *     kernel's own prologue, no separate launch and no round trip through memory.
+ * Each projection is described by plain pointers and sizes (see uniql_w4a16_linear for B, s, bias, D, n, n_out).
+ * scratch: at least uniql_w4a16_group_scratch_bytes(...) bytes, 256-byte aligned, first UNIQL_SCRATCH_COUNTER_BYTES
+ * zero before the first call (every call leaves them zero).  The weights and scales must not be written by the kernel
+ * that immediately precedes this call in the stream (the launch starts fetching them before that kernel has ended);
+ * activations, bias, residual and outputs have no such restriction.
+ */
+#define UNIQL_MAX_PROJ 4
+enum { UNIQL_EPILOGUE_NONE = 0, UNIQL_EPILOGUE_SWIGLU = 1 };
+typedef struct uniql_w4a16_proj {
+  const void* B;       /* int32 [k/16, 2*n] */
+  const void* s;       /* fp16 [k/128, n] */
+  const void* bias;    /* fp16 [n_out] or NULL */
+  void* D;             /* fp16 [m, n_out], row stride ldd */
+  int64_t ldd;
+  int64_t n, n_out;
+} uniql_w4a16_proj;
+int uniql_w4a16_linear_group(const void* A, int64_t lda, int64_t m, int64_t k, const uniql_w4a16_proj* proj,
+                             int nproj, int epilogue, const void* residual, int64_t ldr, int64_t hadamard_dim,
+                             void* scratch, size_t scratch_bytes, int* status_word, void* stream);
+size_t uniql_w4a16_group_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue,
+                                       int64_t hadamard_dim);
+
+/*
+ * The same launch as one step of a tensor-parallel layer (one process per GPU, `comm` from uniql_comm_create /
+ * uniql_comm_connect).  No counterpart in the reference.  `flags` selects what crosses NVLink, always as epoch-tagged
+ * 8-byte words stored into the consumer's memory, every wait bounded (UNIQL_STATUS_WAIT_TIMEOUT on give-up):
+ *   UNIQL_TP_REDUCE      row-parallel shard: the result is summed over the ranks inside the kernel (as
+ *                        uniql_w4a16_linear_allreduce; bias and residual are added once, after the sum).
+ *   UNIQL_TP_GATHER_OUT  column-parallel shard (one projection or a SwiGLU pair, n_out even): besides D, the result
+ *                        columns are stored at feature index col_offset + column into every rank's feature area.
+ *   UNIQL_TP_GATHER_IN   the activations are the full row assembled in this rank's feature area by the preceding
+ *                        UNIQL_TP_GATHER_OUT launches of all ranks (A is ignored); requires hadamard_dim (the size of
+ *                        the full row, at most max_elems / 16) with k_offset = first feature of this rank's k range:
+ *                        every rank transforms the row and keeps its own slice.  Call it directly after the
+ *                        GATHER_OUT launch it pairs with, and follow it by a UNIQL_TP_REDUCE (usually the same call).
+ */
+enum { UNIQL_TP_REDUCE = 1, UNIQL_TP_GATHER_OUT = 2, UNIQL_TP_GATHER_IN = 4 };
+int uniql_w4a16_linear_group_tp(void* comm, int flags, int64_t col_offset, int64_t k_offset, const void* A,
+                                int64_t lda, int64_t m, int64_t k, const uniql_w4a16_proj* proj, int nproj,
+                                int epilogue, const void* residual, int64_t ldr, int64_t hadamard_dim, void* scratch,
+                                size_t scratch_bytes, int* status_word, void* stream);
+
+/*
+ * Host-only check of the decode kernel's work split for one launch geometry (no GPU work is enqueued): replays every
+ * warp's slot range with the kernel's own index arithmetic and verifies that each (block, group) slot is streamed
+ * exactly once, that every partial tile has its own place in scratch and that the per-block tickets add up.
+ * Returns 0, a negative UNIQL_E* code for a geometry the kernel does not take, or a positive number naming the
+ * check that failed.  *fused_hadamard_out (may be NULL) tells whether the Hadamard would run in the kernel prologue.
+ */
+int uniql_w4a16_plan_selftest(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t hadamard_dim,
+                              int64_t k_offset, int* fused_hadamard_out);
 
 #ifdef __cplusplus
 }

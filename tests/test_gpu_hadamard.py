@@ -100,11 +100,12 @@ def test_fused_hadamard_linear(n, k, m):
     xh = orc.hadamard_transform(x.double().numpy()).astype(np.float16)
     want = orc.linear_ref(xh, None, None, None, n, w_deq=layer["w_deq"])
     linear_tolerance_check(y, want)
-    # and it equals the two-step module composition bit for bit
+    # and it agrees with the two-step module composition (for m <= 4 the transform runs inside the linear kernel with
+    # its fp32 sums in another order, so a transformed value may round to the neighbouring fp16 now and then)
     xh_gpu = ops.hadamard(x.cuda(), 1.0 / np.sqrt(k))
     y2 = ops.w4a16_linear(xh_gpu, torch.from_numpy(layer["packed"]).cuda(), torch.from_numpy(layer["scales"]).cuda(),
                           None, n).cpu().numpy()
-    assert np.array_equal(y.view(np.uint16), y2.view(np.uint16))
+    linear_tolerance_check(y, y2.astype(np.float32))
 
 
 def test_had_linear_offline_rotation_matches_online():

@@ -143,7 +143,7 @@ def test_c_abi_exports_every_declared_symbol(built_lib):
     for name in declared:
         assert hasattr(handle, name), f"{name} declared in the header but not exported"
     assert declared == set(_lib.SYMBOLS), "ctypes table and header disagree"
-    assert _lib.lib().uniql_abi_version() == 1
+    assert _lib.lib().uniql_abi_version() == 2
     assert b"groupsize" in _lib.lib().uniql_strerror(-2)
 
 

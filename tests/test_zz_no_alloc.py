@@ -29,21 +29,33 @@ def _static_call(x, packed, scales, bias, n_out):
     return out
 
 
-@pytest.mark.parametrize("n,k,m", [(4096, 4096, 1), (1024, 1536, 5), (14336, 4096, 16)])
+@pytest.mark.parametrize("n,k,m", [(4096, 4096, 1), (1024, 1536, 5), (14336, 4096, 16), (4096, 12160, 4),
+                                   (512, 14336, 4)])
 def test_static_scratch_matches_regular_entry_point(n, k, m):
     from uniql_b200 import ops
+    from uniql_b200._lib import lib
     layer = quantized_layer(n + k + m, n, k, bias=True)
     packed = torch.from_numpy(layer["packed"]).cuda()
     scales = torch.from_numpy(layer["scales"]).cuda()
     bias = torch.from_numpy(layer["bias"]).cuda()
+    # the kernel keeps its per-block tickets AND its partial tiles in the array: every shape here needs more than the
+    # ticket region, so a wrong device address or stale contents would show in the result
+    assert lib().uniql_w4a16_scratch_bytes(m, n, k, 0) > 16384
+    # a layer of another width run in between: its tiles and tickets land on the same bytes of the array
+    other = quantized_layer(7, 768, 2304, bias=False)
+    o_packed, o_scales = torch.from_numpy(other["packed"]).cuda(), torch.from_numpy(other["scales"]).cuda()
     ref = None
     for call in range(2):                      # two calls in a row share the built-in array
         x = make_acts(100 * call + m, m, k).cuda()
         got = _static_call(x, packed, scales, bias, n)
+        xo = make_acts(call, 3, 2304).cuda()
+        got_o = _static_call(xo, o_packed, o_scales, None, 768)
         want = ops.w4a16_linear(x, packed, scales, bias, n)
+        want_o = ops.w4a16_linear(xo, o_packed, o_scales, None, 768)
         torch.cuda.synchronize()
         # same kernel, same split: identical bits, and inside the oracle tolerance used by the other linear tests
         assert torch.equal(got, want)
+        assert torch.equal(got_o, want_o)
         ref = orc.linear_ref(x.cpu().numpy(), None, None, layer["bias"], n, w_deq=layer["w_deq"])
         linear_tolerance_check(got.cpu().numpy(), ref)
     assert ref is not None
@@ -60,7 +72,7 @@ def test_static_scratch_limits_are_reported():
     assert L.uniql_w4a16_linear_static(x.data_ptr(), 256, *args, 17, 256, 256, 256, 128, None, None) == -3   # m > 16
     assert L.uniql_w4a16_linear_static(x.data_ptr(), 256, *args, 1, 256, 256, 256, -1, None, None) == -2    # per-channel
     # a width whose split-k partials cannot fit the built-in array is refused, nothing is launched
-    big_n, big_k = 16384, 32768
+    big_n, big_k = 65536, 32768
     assert L.uniql_w4a16_scratch_bytes(16, big_n, big_k, 0) > 8 * 1024 * 1024
     args_big = (w.data_ptr(), s.data_ptr(), None, out.data_ptr(), big_n)
     assert L.uniql_w4a16_linear_static(x.data_ptr(), big_k, *args_big, 16, big_n, big_n, big_k, 128, None, None) == -7

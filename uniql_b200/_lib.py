@@ -12,6 +12,13 @@ from ._build import LIB_PATH
 _c = ctypes
 _lib = None
 
+
+class Proj(ctypes.Structure):
+    """uniql_w4a16_proj of include/uniql_b200.h: one projection of a grouped decode launch."""
+    _fields_ = [("B", _c.c_void_p), ("s", _c.c_void_p), ("bias", _c.c_void_p), ("D", _c.c_void_p),
+                ("ldd", _c.c_int64), ("n", _c.c_int64), ("n_out", _c.c_int64)]
+
+
 # name -> (restype, argtypes); must list every symbol include/uniql_b200.h declares
 SYMBOLS = {
     "uniql_abi_version": (_c.c_int, []),
@@ -28,6 +35,18 @@ SYMBOLS = {
         _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64,
         _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "uniql_w4a16_scratch_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64]),
+    "uniql_w4a16_linear_group": (_c.c_int, [
+        _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.POINTER(Proj), _c.c_int, _c.c_int, _c.c_void_p, _c.c_int64,
+        _c.c_int64, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
+    "uniql_w4a16_group_scratch_bytes": (_c.c_size_t, [
+        _c.c_int64, _c.c_int64, _c.POINTER(_c.c_int64), _c.c_int, _c.c_int, _c.c_int64]),
+    "uniql_w4a16_linear_group_tp": (_c.c_int, [
+        _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64,
+        _c.POINTER(Proj), _c.c_int, _c.c_int, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_size_t,
+        _c.c_void_p, _c.c_void_p]),
+    "uniql_w4a16_plan_selftest": (_c.c_int, [
+        _c.c_int64, _c.c_int64, _c.POINTER(_c.c_int64), _c.c_int, _c.c_int, _c.c_int64, _c.c_int64,
+        _c.POINTER(_c.c_int)]),
     "uniql_w4_embedding": (_c.c_int, [
         _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64,
         _c.c_void_p, _c.c_void_p]),

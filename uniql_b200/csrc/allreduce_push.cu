@@ -29,18 +29,29 @@ constexpr int kArSpinLimit = 1 << 22;
 struct ArLayout {
   size_t staging_bytes;   // 2 parities * world slots * max_elems/2 words * 8 bytes
   size_t flags_off, epoch_off;
-  size_t fused_staging_off, fused_epoch_off;   // same again for the all-reduce fused into the decode linear
+  // areas used by the decode linear's own cross-GPU epilogues / prologue (see CommView):
+  int64_t block_cap, feat_cap;
+  size_t reduce_off, reduce_epoch_off;       // [2][world][block_cap][512] words, then block_cap u32
+  size_t gather_off, gather_epoch_off;       // [2][16][feat_cap / 2] words, then feat_cap / 64 u32
   size_t total;
 };
+
+static inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
 static ArLayout ar_layout(int world, int64_t max_elems) {
   ArLayout L;
   L.staging_bytes = (size_t)2 * world * max_elems * 4;   // 8-byte words {2 halves, epoch}
-  L.flags_off = (L.staging_bytes + 255) / 256 * 256;
+  L.flags_off = up256(L.staging_bytes);
   L.epoch_off = L.flags_off;
-  L.fused_staging_off = (L.epoch_off + (size_t)kArMaxCtas * 4 + 255) / 256 * 256;
-  L.fused_epoch_off = L.fused_staging_off + L.staging_bytes;
-  L.total = L.fused_epoch_off + (size_t)4096 * 4;      // one epoch counter per column group of the fused linear
+  // max_elems is read as "16 batch rows of the widest activation row": blocks of 64 columns and features follow
+  L.block_cap = max_elems / 1024 > 0 ? max_elems / 1024 : 1;
+  L.feat_cap = (max_elems / 16) / 64 * 64;
+  if (L.feat_cap < 64) L.feat_cap = 64;
+  L.reduce_off = up256(L.epoch_off + (size_t)kArMaxCtas * 4);
+  L.reduce_epoch_off = L.reduce_off + (size_t)2 * world * L.block_cap * kFuseBlockWords * 8;
+  L.gather_off = up256(L.reduce_epoch_off + (size_t)L.block_cap * 4);
+  L.gather_epoch_off = L.gather_off + (size_t)2 * 16 * (L.feat_cap / 2) * 8;
+  L.total = up256(L.gather_epoch_off + (size_t)(L.feat_cap / 64) * 4);
   return L;
 }
 
@@ -180,18 +191,21 @@ extern "C" int uniql_comm_destroy(void* comm) {
 }
 
 namespace uniql {
-int comm_fuse_desc(void* comm, int64_t m, int64_t n, ArFuse* out) {
+int comm_view(void* comm, CommView* out) {
   uniql_comm* c = (uniql_comm*)comm;
   if (!c || !out) return UNIQL_EINVAL;
-  if (m * n > c->max_elems || n / 64 > 4096) return UNIQL_ESHAPE;
   for (int r = 0; r < 8; ++r) out->bufs[r] = c->bufs[r];
   for (int r = 0; r < c->world; ++r)
     if (!c->bufs[r]) return UNIQL_EINVAL;            // uniql_comm_connect has not run
   out->rank = c->rank; out->world = c->world;
-  out->staging_off = c->layout.fused_staging_off;
-  out->epoch_off = c->layout.fused_epoch_off;
-  out->words_per_slot = c->max_elems / 2;
-  out->enabled = 1;
+  out->reduce = out->gather_out = out->gather_in = 0;
+  out->reduce_off = c->layout.reduce_off;
+  out->reduce_epoch_off = c->layout.reduce_epoch_off;
+  out->block_cap = c->layout.block_cap;
+  out->gather_off = c->layout.gather_off;
+  out->gather_epoch_off = c->layout.gather_epoch_off;
+  out->feat_cap = c->layout.feat_cap;
+  out->col_offset = 0;
   return UNIQL_OK;
 }
 }  // namespace uniql

@@ -79,6 +79,14 @@ static int base_matrix(int base, int8_t* h) {
   return UNIQL_OK;
 }
 
+void hadamard_base_signs(int base, unsigned long long* rows40) {
+  for (int i = 0; i < 40; ++i) rows40[i] = 0ull;
+  if (base != 12 && base != 20 && base != 28 && base != 40) return;
+  for (int i = 0; i < base; ++i)
+    for (int j = 0; j < base; ++j)
+      if (c_base_entry(base, i, j) < 0) rows40[i] |= (1ull << j);
+}
+
 static bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
 
 int hadamard_base_of(int64_t dim) {
@@ -509,6 +517,9 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
   const int64_t P = dim / base;
   if (P < 8 || dim > 40960) return UNIQL_ESHAPE;
   if (rows == 0) return UNIQL_OK;
+  int cur_dev = 0;
+  cudaGetDevice(&cur_dev);
+  if (cur_dev < 0 || cur_dev >= 64) cur_dev = 0;
   HadSigns signs;
   for (int i = 0; i < 64; ++i) signs.row[i] = 0;
   int8_t h[1600];
@@ -550,11 +561,11 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
     const size_t smem = (size_t)(dim + dim / 8) * sizeof(float);
 #define UNIQL_HAD32_LAUNCH(T)                                                                                 \
   do {                                                                                                        \
-    static thread_local bool attr_done = false;                                                               \
-    if (smem > 48 * 1024 && !attr_done) {                                                                     \
+    static thread_local bool attr_done[64] = {};   /* function attributes are per device */                   \
+    if (smem > 48 * 1024 && !attr_done[cur_dev]) {                                                            \
       UNIQL_CUDA_TRY(cudaFuncSetAttribute(hadamard_rows32_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                           (40960 + 40960 / 8) * (int)sizeof(float)));                         \
-      attr_done = true;                                                                                       \
+      attr_done[cur_dev] = true;                                                                              \
     }                                                                                                         \
     for (int64_t r0 = 0; r0 < rows; r0 += (int64_t)1 << 30) {                                                 \
       const int64_t nr = rows - r0 < ((int64_t)1 << 30) ? rows - r0 : ((int64_t)1 << 30);                     \
@@ -587,11 +598,11 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
 
 #define UNIQL_HAD_LAUNCH(T)                                                                                   \
   do {                                                                                                        \
-    static thread_local bool attr_done = false;                                                               \
-    if (smem > 48 * 1024 && !attr_done) {                                                                     \
+    static thread_local bool attr_done[64] = {};   /* function attributes are per device */                   \
+    if (smem > 48 * 1024 && !attr_done[cur_dev]) {                                                            \
       UNIQL_CUDA_TRY(cudaFuncSetAttribute(hadamard_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                           40960 * (int)sizeof(float)));                                       \
-      attr_done = true;                                                                                       \
+      attr_done[cur_dev] = true;                                                                              \
     }                                                                                                         \
     const int64_t step = ((int64_t)1 << 30) * rpc;                                                            \
     for (int64_t r0 = 0; r0 < rows; r0 += step) {                                                             \

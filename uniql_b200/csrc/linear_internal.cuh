@@ -5,17 +5,60 @@
 
 namespace uniql {
 
-// Optional cross-GPU sum fused into the decode kernel's epilogue (row-parallel linears): where each rank would
-// store its fp16 partial, it stores {2 halves, epoch} words into every rank's staging block instead and then
-// sums the words that arrived in its own block.
-struct ArFuse {
+constexpr int kMaxProj = 4;      // projections that can share one decode launch (same activations, same k)
+constexpr int kFuseBlockWords = 512;   // 8-byte words per 64-column block in a fused all-reduce slot (16 rows x 32)
+
+// Cross-GPU traffic of a decode launch (tensor parallelism).  Everything moves as 8-byte words {2 halves, epoch}
+// stored into the consumer's own memory; the word is its own ready flag.
+//   reduce : where a rank would store the fp16 result of a row-parallel linear it stores its partial into every rank's
+//            block instead and adds up what arrived in its own block (rank order, fp32)
+//   gather_out : a column-parallel launch also stores its result columns into every rank's feature area, so that the
+//            next launch on each rank can read the full activation row
+//   gather_in : the activations are read from this rank's feature area (bounded poll per word) instead of A
+struct CommView {
   unsigned char* bufs[8];     // every rank's communication block, addressable from this GPU
   int rank, world;
-  size_t staging_off;         // byte offset of the fused staging area inside a block
-  size_t epoch_off;           // byte offset of the per-column-group epoch counters
-  int64_t words_per_slot;     // 8-byte words per (parity, source rank) slot
-  int enabled;
+  int reduce, gather_out, gather_in;
+  size_t reduce_off;          // byte offset of the reduce staging area: [2 parities][world][block_cap][512] words
+  size_t reduce_epoch_off;    // per-block epoch counters (u32) of the reduce area
+  int64_t block_cap;          // 64-column blocks a reduce slot has room for
+  size_t gather_off;          // byte offset of the feature area: [2 parities][16 rows][feat_cap / 2] words
+  size_t gather_epoch_off;    // per-block epoch counters (u32) of this rank's own column shard; counter 0 also tells
+                              // the consumer which epoch the words of the current call carry
+  int64_t feat_cap;           // features (columns) a row of the feature area has room for
+  int64_t col_offset;         // gather_out: global index of this launch's column 0
 };
+
+struct DecodeProjArgs {
+  const void* B;
+  const void* s;
+  const void* bias;
+  void* D;
+  int64_t ldd;
+  int64_t n, n_out;
+};
+
+struct DecodeArgs {
+  const void* A;              // fp16 [m, k] (ignored with comm->gather_in)
+  int64_t lda;
+  int64_t m, k;
+  int nproj;
+  DecodeProjArgs proj[kMaxProj];
+  int epilogue;               // UNIQL_EPILOGUE_*
+  const void* residual;       // fp16 [m, n_out] added to the rounded result, or nullptr
+  int64_t ldr;
+  int64_t hadamard_dim;       // 0, or the size of the transform applied to the activation rows first
+  int64_t k_offset;           // first feature of this launch's k range inside the transformed row (tensor parallel)
+  void* scratch;              // [tickets | partial tiles | transformed activations (separate-kernel route)]
+  size_t scratch_bytes;
+  int* status_word;
+  const CommView* comm;       // nullptr: single GPU
+};
+
+// m <= 16.  Scratch bytes the launch needs (tickets included).
+size_t decode_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t hadamard_dim,
+                            int64_t k_offset);
+int launch_decode(const DecodeArgs& a, cudaStream_t stream);
 
 struct LinearArgs {
   const void* B;
@@ -23,24 +66,8 @@ struct LinearArgs {
   const void* bias;
   int64_t ldd;
   int64_t n, n_out, k;
-  int* counters;      // zeroed ticket counters inside the caller's scratch
-  float* partials;    // split-k partial sums inside the caller's scratch
-  size_t partial_bytes;
   int* status_word;
-  const ArFuse* ar;   // nullptr: plain store
 };
-
-struct GemvPlan {
-  int WN, WK, S, GCH, MT, R, xs_rows;
-  int cluster, ctile_off;
-  size_t smem;
-  size_t partial_bytes;
-};
-
-// m <= 16 per launch.
-GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k);
-int launch_gemv(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m, const GemvPlan& plan,
-                bool pdl, cudaStream_t stream);
 
 // Tensor-core (tcgen05) path for m > 16.
 bool gemm_tc_supported(int64_t m, int64_t n, int64_t k);
@@ -50,9 +77,11 @@ int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D,
 // Hadamard transform of fp16 rows (used by the fused linear); signals dependents early when pdl is set.
 int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
                     int dtype, bool pdl_trigger, cudaStream_t stream);
-int hadamard_base_of(int64_t dim);
+int hadamard_base_of(int64_t dim);   // 40/28/20/12/1, or 0 if dim is not a supported size
+// Sign rows of the base matrix: bit a' of row[a] set <=> H[a][a'] = -1 (all zero for base 1).
+void hadamard_base_signs(int base, unsigned long long* rows40);
 
-// Fills `out` from a communicator made by uniql_comm_create; fails if m*n does not fit its staging area.
-int comm_fuse_desc(void* comm, int64_t m, int64_t n, ArFuse* out);   // 40/28/20/12/1, or 0 if dim is not a supported size
+// Fills `out` from a communicator made by uniql_comm_create.
+int comm_view(void* comm, CommView* out);
 
 }  // namespace uniql

@@ -1,0 +1,1150 @@
+// Decode-regime W4A16 linear (m <= 16) for sm_100a: a persistent, weight-streaming skinny GEMM.
+//
+// Replaces the small-batch instantiations of UniQL's Marlin kernel
+// (csrc/linear/marlin_gemm_kernel.cuh:176-740, tile table :792-800) while consuming the very same
+// packed buffers (quantize/quantize_helpers.py:145-165 weight order, :54-62 scale order), and the separate
+// launches the reference's blocks make around it: gate_proj / up_proj / act_fn(gate) * up
+// (modeling/llama/llama_qblocks.py:48-51), q/k/v (:104-106), the residual add, and the online Hadamard in front of
+// down_proj / out_proj (quantize/quant_hadamard_layers.py:16-18).
+//
+// How the packed layout is consumed.  Packed row kt (16 k-values) holds, for every 64-column block,
+// 512 contiguous bytes; lane i of a warp owns bytes 16i..16i+15 = four words j=0..3.  With g = i/4 and
+// c = i%4, word j carries W[k, n] for k = 16kt + {2c, 2c+1, 2c+8, 2c+9} and n = 64blk + 16j + g + {0, 8}.
+// That is exactly the A-operand fragment of mma.m16n8k16 when the *weights* are the 16-row operand
+// (rows = 16 output columns) and the activations are the 8-column operand (columns = batch rows).
+// So one 16-byte load per lane feeds four tensor-core instructions per 8 batch rows with no data
+// movement between lanes, and all 16 rows of the MMA do useful work even at m = 1.
+//
+// Work split.  The unit of work is a *slot*: one quantisation group (128 k-values = 8 packed rows) of one 64-column
+// block = 4 KB of packed weights.  A launch is one CTA per SM; the T slots of all projections of the launch are
+// laid out in one fixed order and warp w of the W = SMs x warps takes slots [T w / W, T (w+1) / W): every SM streams
+// the same number of bytes (to within one slot) whatever the matrix shape.  Each warp owns a two-slot ring; one
+// elected lane fills a slot with one 2-D TMA tile (weights) while all lanes fetch the group's 64 scales and the
+// m x 128 activations with 16-byte asynchronous copies, everything landing on the slot's mbarrier (bounded wait,
+// status bit on give-up).
+// A run of slots of one block ends in a 64 x m fp32 tile that goes to scratch; a ticket counts the slots that have
+// arrived for the block and the warp that brings the last one adds the tiles up in a fixed order (no spinning, no
+// floating-point atomics: same bits on every run) and applies the epilogue: bias, SwiGLU product of a gate/up pair,
+// residual add, fp16 store, or the cross-GPU exchange of a tensor-parallel layer.
+//
+// Overlap between launches.  The kernel is sized so that TWO launches fit on an SM (<= 113 KB of shared memory and
+// <= 64 K registers together).  Every launch carries the programmatic-dependent-launch attribute, fills its rings,
+// releases its own dependents and only then waits for its predecessor: while one launch drains (ticket, tile sum,
+// stores, grid completion) and the next one fetches its activations, the next one's first 100 KB per SM of weights
+// are already on their way, so HBM does not idle between dependent GEMVs.
+//
+// Roofline: HBM.  Algorithmic bytes per launch = sum over projections of k*n/2 + (k/128)*n*2 + m*n_out*2, + m*k*2.
+#include "common.cuh"
+#include "linear_internal.cuh"
+#include "tma.cuh"
+
+#include <cuda.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace uniql {
+
+constexpr int kSlotScaleBytes = 128;   // 64 fp16 scales
+constexpr int kXRowBytes = 272;        // one batch row of one group: 256 bytes + 16 (rows fall on distinct banks)
+constexpr int kMaxSeg = 3;             // Hadamard segments a CTA may need in the fused prologue
+constexpr int kSegRowBytes = 2048;     // room per (segment, batch row) in the prologue: 512 floats
+constexpr int kSegRowStride = 1040;    // bytes between batch rows of a transformed segment (1024 + 16)
+constexpr int kSpinLimit = 1 << 22;    // polls of a word another GPU has to write before giving up
+
+struct DecodeProj {
+  const __half* S;
+  const __half* bias;
+  __half* D;
+  long long ldd;
+  int N, n_out;
+};
+
+struct DecodeParams {
+  CUtensorMap wmap[kMaxProj];
+  DecodeProj proj[kMaxProj];
+  int vb_start[kMaxProj + 1];     // first virtual block of each projection (plain order)
+  const __half* A;
+  long long lda;
+  const __half* residual;
+  long long ldr;
+  float* partials;
+  int* tickets;
+  int* status_word;
+  long long T;                    // slots of the launch
+  int M, NG, nproj, vbT, W, epilogue;
+  int kc, koff, nchunks, Pc;      // k is cut into chunks of kc groups (chunk c = local groups [c kc - koff, ...))
+  int xbytes;                     // bytes of staged activations per ring slot
+  int had;                        // 1: the activations are H a / sqrt(dim), formed by each CTA for the chunks it streams
+  int hP, hlogP, hlogQ, hMdim;    // dim = base * Q * P, P <= 512 the segment length, Mdim = base * Q segments
+  int seg0;                       // global segment index of chunk 0
+  float hscale;
+  unsigned long long hsign[40];   // base matrix: bit a' of hsign[a] set <=> H[a][a'] = -1
+  CommView cv;
+};
+
+// ------------------------------------------------------------------------------------------------ slot order
+// Slots are ordered chunk by chunk, inside a chunk block by block, inside a block by group.  Without a Hadamard
+// prologue there is one chunk (kc = NG): block-major order, the warps that share a block are neighbours.  With it a
+// chunk is one Hadamard segment, so that a CTA's slots touch at most kMaxSeg segments of the transformed row.
+struct SlotIt {
+  int c, vb, g, g_lo, g_hi;
+};
+__host__ __device__ inline int chunk_lo(int c, int kc, int koff) { const int v = c * kc - koff; return v < 0 ? 0 : v; }
+__host__ __device__ inline int chunk_hi(int c, int kc, int koff, int NG) {
+  const int v = (c + 1) * kc - koff;
+  return v > NG ? NG : v;
+}
+__host__ __device__ inline SlotIt slot_decode(long long s, int vbT, int NG, int kc, int koff) {
+  SlotIt it;
+  const int q = (int)(s / vbT);
+  it.c = (q + koff) / kc;
+  it.g_lo = chunk_lo(it.c, kc, koff);
+  it.g_hi = chunk_hi(it.c, kc, koff, NG);
+  const int w = it.g_hi - it.g_lo;
+  const int rem = (int)(s - (long long)vbT * it.g_lo);
+  it.vb = rem / w;
+  it.g = it.g_lo + (rem - it.vb * w);
+  return it;
+}
+// CH = false: a single chunk, so c, g_lo and g_hi are constants and cost no registers
+template <bool CH>
+__host__ __device__ __forceinline__ SlotIt slot_at(long long s, int vbT, int NG, int kc, int koff) {
+  if (CH) return slot_decode(s, vbT, NG, kc, koff);
+  SlotIt it;
+  it.c = 0; it.g_lo = 0; it.g_hi = NG;
+  it.vb = (int)(s / NG);
+  it.g = (int)(s - (long long)it.vb * NG);
+  return it;
+}
+template <bool CH>
+__host__ __device__ __forceinline__ void slot_next(SlotIt& it, int vbT, int NG, int kc) {
+  if (!CH) {
+    if (++it.g == NG) { it.g = 0; ++it.vb; }
+    return;
+  }
+  if (++it.g == it.g_hi) {
+    it.g = it.g_lo;
+    if (++it.vb == vbT) {
+      it.vb = 0;
+      ++it.c;
+      it.g_lo = it.g_hi;
+      it.g_hi = it.g_hi + kc > NG ? NG : it.g_hi + kc;
+      it.g = it.g_lo;
+    }
+  }
+}
+// warp that owns slot s: the largest w with T w / W <= s
+__host__ __device__ inline int warp_of_slot(long long s, long long T, int W) { return (int)(((s + 1) * W - 1) / T); }
+// Number of tiles block vb receives inside chunk [g_lo, g_hi): the warps whose slot ranges touch it.  With fewer slots
+// than warps every busy warp holds exactly one slot (and idle warps sit between them), so each slot is its own tile.
+__host__ __device__ inline int runs_of(int vb, int g_lo, int g_hi, int vbT, long long T, int W) {
+  const int w = g_hi - g_lo;
+  if (T < W) return w;
+  const long long first = (long long)vbT * g_lo + (long long)vb * w;
+  return warp_of_slot(first + w - 1, T, W) - warp_of_slot(first, T, W) + 1;
+}
+// Index of a run among the tiles of its block and chunk: `first` is the first slot of the block inside the chunk,
+// `run_first` the first slot of the run, wg the warp that holds it.
+__host__ __device__ inline int run_index(long long first, long long run_first, int wg, long long T, int W) {
+  if (T < W) return (int)(run_first - first);
+  return wg - warp_of_slot(first, T, W);
+}
+
+// ------------------------------------------------------------------------------------------------ device helpers
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol)
+      : "memory");
+}
+// Per-thread 16-byte asynchronous copy global -> shared (no copy-engine request, no registers held) ...
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint64_t pol) {
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(pol) : "memory");
+}
+// ... and one arrival on the slot's mbarrier once every copy this thread has issued so far has landed
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void st_word_sys(uint2* p, uint32_t data, uint32_t flag) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(flag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_word_sys(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ void proj_of_block(const DecodeParams& p, int vb, int& pi, int& lb) {
+  if (p.epilogue == UNIQL_EPILOGUE_SWIGLU) {
+    pi = vb & 1;
+    lb = vb >> 1;
+    return;
+  }
+  pi = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxProj; ++i)
+    if (i < p.nproj && vb >= p.vb_start[i]) pi = i;
+  lb = vb - p.vb_start[pi];
+}
+
+// One quantisation group of one 64-column block out of a ring slot.  Nibbles become fp16 values (1024 + q) and
+// (64 + q) by a single LOP3 each; the offsets come out again through `corr`, the product of the same activations
+// with the constant weights (1032 | 72):  sum (off + q) x - sum (off + 8) x = sum (q - 8) x.
+template <int MT>
+__device__ __forceinline__ void decode_group(uint32_t wslot, uint32_t xl, uint32_t xts, float (&accg)[MT][4][4],
+                                             float (&corr)[MT][4]) {
+  const uint32_t kcorr[4] = {0x64086408u, 0x64086408u, 0x54805480u, 0x54805480u};   // 1032, 1032, 72, 72
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const uint4 w4 = lds128(wslot + u * 512);
+    uint32_t b0[MT], b1[MT];
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      b0[t] = lds32(xl + t * xts + u * 32);
+      b1[t] = lds32(xl + t * xts + u * 32 + 16);
+    }
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      if (u == 0) mma_m16n8k16_init(corr[t], kcorr, b0[t], b1[t], 0.f, 0.f);
+      else mma_m16n8k16(corr[t], kcorr, b0[t], b1[t]);
+    }
+    const uint32_t wq[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t a[4];
+      const uint32_t q = wq[j], qs = wq[j] >> 8;
+      a[0] = lop3_and_or(q, 0x000f000fu, 0x64006400u);     // n = 16j+g,   k = 2c, 2c+1    : 1024 + q
+      a[2] = lop3_and_or(q, 0x00f000f0u, 0x54005400u);     // n = 16j+g,   k = 2c+8, 2c+9  :   64 + q
+      a[1] = lop3_and_or(qs, 0x000f000fu, 0x64006400u);    // n = 16j+g+8, k = 2c, 2c+1
+      a[3] = lop3_and_or(qs, 0x00f000f0u, 0x54005400u);    // n = 16j+g+8, k = 2c+8, 2c+9
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        if (u == 0) mma_m16n8k16_init(accg[t][j], a, b0[t], b1[t], 0.f, 0.f);
+        else mma_m16n8k16(accg[t][j], a, b0[t], b1[t]);
+      }
+    }
+  }
+}
+
+// Final values of two adjacent columns of one batch row -> fp16 (bias, optional SwiGLU partner, optional residual),
+// stored to D and, in a tensor-parallel column shard, into every rank's feature area.
+__device__ __forceinline__ void store_pair(const DecodeParams& p, const DecodeProj& pr, const DecodeProj& pr2, int m,
+                                           int n0, float2 v, float2 v2, bool swiglu, uint32_t gepoch) {
+  if (n0 >= pr.n_out) return;
+  const bool two = n0 + 1 < pr.n_out;
+  if (pr.bias) {
+    v.x += __half2float(pr.bias[n0]);
+    if (two) v.y += __half2float(pr.bias[n0 + 1]);
+  }
+  __half h0 = __float2half_rn(v.x), h1 = __float2half_rn(v.y);
+  if (swiglu) {
+    // act_fn(gate) * up with the roundings of the separate modules: fp16 gate, fp16 up, fp16 SiLU, fp16 product
+    if (pr2.bias) {
+      v2.x += __half2float(pr2.bias[n0]);
+      if (two) v2.y += __half2float(pr2.bias[n0 + 1]);
+    }
+    const __half u0 = __float2half_rn(v2.x), u1 = __float2half_rn(v2.y);
+    const __half a0 = __float2half_rn(silu_f(__half2float(h0))), a1 = __float2half_rn(silu_f(__half2float(h1)));
+    h0 = __float2half_rn(__half2float(a0) * __half2float(u0));
+    h1 = __float2half_rn(__half2float(a1) * __half2float(u1));
+  }
+  if (p.residual) {
+    const __half* r = p.residual + (size_t)m * p.ldr + n0;
+    h0 = __float2half_rn(__half2float(h0) + __half2float(r[0]));
+    if (two) h1 = __float2half_rn(__half2float(h1) + __half2float(r[1]));
+  }
+  __half* d = pr.D + (size_t)m * pr.ldd + n0;
+  if (two && ((reinterpret_cast<uintptr_t>(d) & 3u) == 0)) {
+    *reinterpret_cast<__half2*>(d) = __halves2half2(h0, h1);
+  } else {
+    d[0] = h0;
+    if (two) d[1] = h1;
+  }
+  if (p.cv.gather_out) {
+    // only real columns travel (n_out is even here): the consumer's row is the concatenation of the ranks' real columns
+    const __half2 hv = __halves2half2(h0, two ? h1 : __float2half_rn(0.f));
+    const size_t word = ((size_t)(gepoch & 1u) * 16 + m) * (size_t)(p.cv.feat_cap >> 1) + (size_t)((p.cv.col_offset + n0) >> 1);
+    for (int r = 0; r < p.cv.world; ++r)
+      st_word_sys(reinterpret_cast<uint2*>(p.cv.bufs[r] + p.cv.gather_off) + word, *reinterpret_cast<const uint32_t*>(&hv),
+                  gepoch);
+  }
+}
+
+// All slots of a block (or of a gate/up pair of blocks) have arrived: the calling warp adds the tiles up in a fixed
+// order and finishes the 64 columns, two per lane.  Returns false if a wait on another GPU's words gave up.
+__device__ __noinline__ bool finish_block(const DecodeParams& p, int unit, int lane) {
+  const bool swiglu = p.epilogue == UNIQL_EPILOGUE_SWIGLU;
+  const size_t tile_elems = (size_t)p.M * 64;
+  bool ok = true;
+  int pi, lb;
+  proj_of_block(p, swiglu ? 2 * unit : unit, pi, lb);
+  const DecodeProj& pr = p.proj[pi];
+  const DecodeProj& pr2 = p.proj[swiglu ? 1 : pi];
+  // tiles per chunk of the block(s), chunk cc in lane cc % 32
+  int pc[2][3];
+#pragma unroll
+  for (int wh = 0; wh < 2; ++wh)
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      const int cc = lane + 32 * q;
+      pc[wh][q] = 0;
+      if ((wh == 0 || swiglu) && cc < p.nchunks)
+        pc[wh][q] = runs_of(swiglu ? 2 * unit + wh : unit, chunk_lo(cc, p.kc, p.koff), chunk_hi(cc, p.kc, p.koff, p.NG),
+                            p.vbT, p.T, p.W);
+    }
+  const int total = p.nchunks * p.Pc;
+  uint32_t repoch = 0, gepoch = 0;
+  if (p.cv.reduce)
+    repoch = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_epoch_off + 4 * (size_t)unit) + 1;
+  if (p.cv.gather_out)
+    gepoch = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off + 4 * (size_t)unit) + 1;
+  for (int m = 0; m < p.M; ++m) {
+    float2 v[2];
+#pragma unroll
+    for (int wh = 0; wh < 2; ++wh) {
+      v[wh] = make_float2(0.f, 0.f);
+      if (wh == 1 && !swiglu) continue;
+      const int vb = swiglu ? 2 * unit + wh : unit;
+      const float* base = p.partials + (size_t)vb * p.nchunks * p.Pc * tile_elems + (size_t)m * 64 + 2 * lane;
+      for (int i0 = 0; i0 < total; i0 += 16) {      // up to 16 independent L2 loads in flight, summed in order
+        float2 t8[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const int idx = i0 + q;
+          const int cc = idx / p.Pc, jj = idx - cc * p.Pc;
+          const int src = cc < 32 ? pc[wh][0] : cc < 64 ? pc[wh][1] : pc[wh][2];
+          const int runs = __shfl_sync(0xffffffffu, src, cc & 31);
+          t8[q] = (idx < total && jj < runs) ? __ldcg(reinterpret_cast<const float2*>(base + (size_t)idx * tile_elems))
+                                             : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int q = 0; q < 16; ++q) { v[wh].x += t8[q].x; v[wh].y += t8[q].y; }
+      }
+    }
+    const int n0 = lb * 64 + 2 * lane;
+    if (p.cv.reduce) {
+      // row-parallel shard: push this rank's fp16 partial of the two columns to every rank, then add up the
+      // words of all ranks that arrived in this GPU's own block (rank order, fp32: same bits everywhere)
+      const __half2 hv = __floats2half2_rn(v[0].x, v[0].y);
+      const size_t word = (size_t)unit * kFuseBlockWords + (size_t)m * 32 + lane;
+      const size_t per_rank = (size_t)p.cv.block_cap * kFuseBlockWords;
+      const size_t par = (size_t)(repoch & 1u) * p.cv.world;
+      for (int r = 0; r < p.cv.world; ++r)
+        st_word_sys(reinterpret_cast<uint2*>(p.cv.bufs[r] + p.cv.reduce_off) + (par + p.cv.rank) * per_rank + word,
+                    *reinterpret_cast<const uint32_t*>(&hv), repoch);
+      float2 sum = make_float2(0.f, 0.f);
+      for (int r = 0; r < p.cv.world; ++r) {
+        const uint2* src = reinterpret_cast<const uint2*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_off) + (par + r) * per_rank + word;
+        uint2 wv = ld_word_sys(src);
+        int spin = 0;
+        while (wv.y != repoch && ok) {
+          if (++spin > kSpinLimit) { ok = false; break; }
+          wv = ld_word_sys(src);
+        }
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv.x));
+        sum.x += f.x;
+        sum.y += f.y;
+      }
+      v[0] = sum;
+    }
+    store_pair(p, pr, pr2, m, n0, v[0], v[1], swiglu, gepoch);
+  }
+  if (p.cv.reduce || p.cv.gather_out) {
+    __syncwarp();
+    if (lane == 0) {
+      if (p.cv.reduce)
+        *reinterpret_cast<volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_epoch_off + 4 * (size_t)unit) = repoch;
+      if (p.cv.gather_out)
+        *reinterpret_cast<volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off + 4 * (size_t)unit) = gepoch;
+    }
+  }
+  return ok;
+}
+
+// Hadamard prologue of a CTA: forms, in shared memory, the segments of  H a / sqrt(dim)  that the CTA's slots multiply
+// with (nseg consecutive segments from global segment seg0 + c_first, every batch row), rounded to fp16.
+// dim = Mdim x P with commuting factors: segment s of the result is the P-point Walsh-Hadamard transform of
+// sum_a' sign(s, a') a[a' P .. a' P + P).  FEAT: the row comes from this rank's feature area (epoch-tagged words written
+// by all ranks, bounded poll) instead of A.  Returns false if a poll gave up.
+template <bool FEAT>
+__device__ __noinline__ bool hadamard_prologue(const DecodeParams& p, uint8_t* area, uint32_t* s_mask, int c_first,
+                                               int nseg, int nthreads) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int P = p.hP, half_p = P >> 1;
+  const int Q1 = (1 << p.hlogQ) - 1;
+  float* zbuf = reinterpret_cast<float*>(area);
+  bool ok = true;
+  // sign of the (segment, source segment) pairs: base matrix on the slow index, Sylvester on the fast one
+  if (warp < nseg) {
+    const int seg = p.seg0 + c_first + warp;
+    for (int i = 0; i < 3; ++i) {
+      const int ap = lane + 32 * i;
+      int neg = 0;
+      if (ap < p.hMdim) {
+        neg = (int)((p.hsign[seg >> p.hlogQ] >> (ap >> p.hlogQ)) & 1ull);
+        neg ^= __popc((unsigned)((seg & Q1) & (ap & Q1))) & 1;
+      }
+      const uint32_t mk = __ballot_sync(0xffffffffu, neg);
+      if (lane == 0) s_mask[warp * 3 + i] = mk;
+    }
+  }
+  __syncthreads();
+  // epoch the feature words of this call carry: this rank's own column shard was produced by the launch before
+  uint32_t in_epoch = 0;
+  const uint2* feat = nullptr;
+  if (FEAT) {
+    in_epoch = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off);
+    feat = reinterpret_cast<const uint2*>(p.cv.bufs[p.cv.rank] + p.cv.gather_off) +
+           (size_t)(in_epoch & 1u) * 16 * (size_t)(p.cv.feat_cap >> 1);
+  }
+  // z[seg][row][b] = sum_a' sign(seg, a') a[row][a' P + b]: a thread owns two adjacent b of one row
+  for (int item = tid; item < p.M * half_p; item += nthreads) {
+    const int row = item >> (p.hlogP - 1), cp = item & (half_p - 1);
+    float2 z[kMaxSeg];
+#pragma unroll
+    for (int s = 0; s < kMaxSeg; ++s) z[s] = make_float2(0.f, 0.f);
+    for (int a0 = 0; a0 < p.hMdim; a0 += 8) {
+      uint32_t hv[8];
+      if (!FEAT) {
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.A + (size_t)row * p.lda) + cp;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (a0 + i < p.hMdim) hv[i] = __ldcg(src + (size_t)(a0 + i) * half_p);
+      } else {
+        const uint2* src = feat + (size_t)row * (size_t)(p.cv.feat_cap >> 1) + cp;
+        uint2 wv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (a0 + i < p.hMdim) wv[i] = ld_word_sys(src + (size_t)(a0 + i) * half_p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (a0 + i < p.hMdim) {
+            int spin = 0;
+            while (wv[i].y != in_epoch && ok) {
+              if (++spin > kSpinLimit) { ok = false; break; }
+              wv[i] = ld_word_sys(src + (size_t)(a0 + i) * half_p);
+            }
+            hv[i] = wv[i].x;
+          }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (a0 + i < p.hMdim) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hv[i]));
+          const int ap = a0 + i;
+#pragma unroll
+          for (int s = 0; s < kMaxSeg; ++s)
+            if (s < nseg) {
+              const bool neg = (s_mask[s * 3 + (ap >> 5)] >> (ap & 31)) & 1u;
+              z[s].x += neg ? -f.x : f.x;
+              z[s].y += neg ? -f.y : f.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < kMaxSeg; ++s)
+      if (s < nseg) *reinterpret_cast<float2*>(zbuf + (size_t)(s * p.M + row) * 512 + 2 * cp) = z[s];
+  }
+  __syncthreads();
+  // P-point Walsh-Hadamard transform of every (segment, row) vector, radix 8 / 4 / 2 out of shared memory
+  const int ntask = nseg * p.M;
+  for (int h = 1; h < P;) {
+    const int rem = P / h;
+    const int R = rem >= 8 ? 8 : rem;
+    const int lh = __ffs(h) - 1, lgr = p.hlogP - (R == 8 ? 3 : R == 4 ? 2 : 1);   // log2(groups per vector)
+    for (int idx = tid; idx < (ntask << lgr); idx += nthreads) {
+      const int task = idx >> lgr, gi = idx & ((1 << lgr) - 1);
+      const int low = gi & (h - 1), high = gi >> lh;
+      float* q = zbuf + (size_t)task * 512 + (size_t)high * h * R + low;
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < R) v[i] = q[(size_t)i * h];
+#pragma unroll
+      for (int st = 1; st < 8; st <<= 1)
+        if (st < R) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i < R && !(i & st)) {
+              const float a = v[i], b = v[i | st];
+              v[i] = a + b;
+              v[i | st] = a - b;
+            }
+        }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < R) q[(size_t)i * h] = v[i];
+    }
+    __syncthreads();
+    h *= R;
+  }
+  // scale, round to fp16 (as the separate Hadamard module would), repack as rows of kSegRowStride bytes
+  uint32_t packed[12];
+  const int nitems = ntask * half_p;
+#pragma unroll
+  for (int i = 0; i < 12; ++i) {
+    const int item = tid + i * nthreads;
+    if (item < nitems) {
+      const int task = item >> (p.hlogP - 1), cp = item & (half_p - 1);
+      const float2 f = *reinterpret_cast<const float2*>(zbuf + (size_t)task * 512 + 2 * cp);
+      const __half2 hh = __floats2half2_rn(f.x * p.hscale, f.y * p.hscale);
+      packed[i] = *reinterpret_cast<const uint32_t*>(&hh);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 12; ++i) {
+    const int item = tid + i * nthreads;
+    if (item < nitems) {
+      const int task = item >> (p.hlogP - 1), cp = item & (half_p - 1);
+      *reinterpret_cast<uint32_t*>(area + (size_t)task * kSegRowStride + cp * 4) = packed[i];
+    }
+  }
+  __syncthreads();
+  return ok;
+}
+
+template <int MT, int WARPS, int MINB, bool HAD, int kRing>
+__global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t s_bars[WARPS * kRing];
+  __shared__ uint32_t s_mask[kMaxSeg][3];
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int wg = blockIdx.x * WARPS + warp;
+  const long long s0 = p.T * wg / p.W, s1 = p.T * (wg + 1) / p.W;
+  const int nsl = (int)(s1 - s0);
+
+  // ---- shared memory: [weights: WARPS x kRing x 4 KB][scales: WARPS x kRing x 128 B][activations] ----
+  const uint32_t smem_base = smem_addr(smem_raw);
+  const uint32_t wring = smem_base + warp * (kRing * kSlotBytes);
+  const uint32_t sring = smem_base + WARPS * (kRing * kSlotBytes) + warp * (kRing * kSlotScaleBytes);
+  const uint32_t xarea = smem_base + WARPS * (kRing * (kSlotBytes + kSlotScaleBytes));
+  const uint32_t xring = xarea + warp * (kRing * p.xbytes);
+  const uint32_t bar0 = smem_addr(&s_bars[warp * kRing]);
+  const uint64_t pol_w = make_evict_first_policy();
+  const uint64_t pol_x = make_evict_last_policy();
+
+  if (lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&p.wmap[0]) : "memory");
+    // a slot is complete when its weight tile has landed (one arrival with the byte count, by the issuing lane) and
+    // every lane's asynchronous copies of the group's scales and activations have (32 arrivals)
+    for (int s = 0; s < kRing; ++s) mbar_init(bar0 + s * 8, 33);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+
+  // One copy-engine request per slot (the 4 KB weight tile); the 64 scales of the group and the m x 128 activations
+  // travel as per-thread 16-byte asynchronous copies: small bulk copies cost the copy engine as much as a tile.
+  auto issue_weights = [&](int slot, const SlotIt& it) {   // all lanes
+    int pi, lb;
+    proj_of_block(p, it.vb, pi, lb);
+    const uint32_t bar = bar0 + slot * 8;
+    if (lane == 0) {
+      mbar_expect_tx(bar, kSlotBytes);
+      tma_load_slot(wring + slot * kSlotBytes, &p.wmap[pi], lb * 128, 8 * it.g, bar, pol_w);
+    }
+    if (lane < 8)
+      cp_async16(sring + slot * kSlotScaleBytes + lane * 16,
+                 p.proj[pi].S + ((size_t)it.g * p.proj[pi].N + (size_t)lb * 64 + lane * 8), pol_w);
+  };
+  auto issue_acts = [&](int slot, int grp) {               // all lanes: 16 chunks of 16 bytes per batch row
+    for (int idx = lane; idx < p.M * 16; idx += 32) {
+      const int row = idx >> 4, ch = idx & 15;
+      cp_async16(xring + slot * p.xbytes + row * kXRowBytes + ch * 16, p.A + (size_t)row * p.lda + (size_t)grp * 128 + ch * 8,
+                 pol_x);
+    }
+  };
+
+  // ---- start streaming weights before anything else ----
+  SlotIt it_issue = slot_at<HAD>(s0, p.vbT, p.NG, p.kc, p.koff);
+  int g_pre[kRing];
+#pragma unroll
+  for (int s = 0; s < kRing; ++s) {
+    g_pre[s] = it_issue.g;
+    if (s < nsl) {
+      issue_weights(s, it_issue);
+      if (HAD) cp_async_arrive(bar0 + s * 8);
+      slot_next<HAD>(it_issue, p.vbT, p.NG, p.kc);
+    }
+  }
+  // Let the next kernel in the stream start its own weight prefetch, then wait for the producer of the activations.
+  pdl_launch_dependents();
+  pdl_wait();
+
+  bool timed_out = false;
+  // chunk range of this CTA (Hadamard prologue) -- CTA-uniform
+  int c_first = 0;
+  if (HAD) {
+    const long long cs0 = p.T * (long long)(blockIdx.x * WARPS) / p.W;
+    const long long cs1 = p.T * (long long)((blockIdx.x + 1) * WARPS) / p.W;
+    if (cs1 > cs0) {
+      c_first = slot_decode(cs0, p.vbT, p.NG, p.kc, p.koff).c;
+      const int c_last = slot_decode(cs1 - 1, p.vbT, p.NG, p.kc, p.koff).c;
+      int nseg = c_last - c_first + 1;
+      if (nseg > kMaxSeg) nseg = kMaxSeg;                 // excluded by the host plan
+      bool ok;
+      if (p.cv.gather_in) ok = hadamard_prologue<true>(p, smem_raw + (xarea - smem_base), &s_mask[0][0], c_first, nseg, WARPS * 32);
+      else ok = hadamard_prologue<false>(p, smem_raw + (xarea - smem_base), &s_mask[0][0], c_first, nseg, WARPS * 32);
+      if (!ok) timed_out = true;
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < kRing; ++s)
+      if (s < nsl) {
+        issue_acts(s, g_pre[s]);
+        cp_async_arrive(bar0 + s * 8);
+      }
+  }
+
+  // this lane's B-fragment origin: batch row g (tile 0) and 8 + g (tile 1), clamped to a row that exists --
+  // batch columns past m only feed accumulator columns that are never stored
+  const int row_t0 = min(g, p.M - 1), row_t1 = min(8 + g, p.M - 1);
+  const uint32_t xrs = HAD ? (uint32_t)kSegRowStride : (uint32_t)kXRowBytes;
+  const uint32_t xl_off = (uint32_t)row_t0 * xrs + c * 4;
+  const uint32_t xts = (uint32_t)(row_t1 - row_t0) * xrs;
+
+  float acc[MT][4][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) acc[t][j][r] = 0.f;
+
+  SlotIt it = slot_at<HAD>(s0, p.vbT, p.NG, p.kc, p.koff);
+  int run_cnt = 0;
+  const size_t tile_elems = (size_t)p.M * 64;
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int i = 0; i < nsl; ++i) {
+    if (!mbar_wait(bar0 + slot * 8, parity)) timed_out = true;
+    const uint4 sc = lds128(sring + slot * kSlotScaleBytes + 16 * g);
+    uint32_t xl;
+    if (HAD)
+      xl = xarea + (uint32_t)((it.c - c_first) * p.M) * kSegRowStride + (uint32_t)(it.g + p.koff - it.c * p.kc) * 256u + xl_off;
+    else
+      xl = xring + slot * p.xbytes + xl_off;
+    float accg[MT][4][4], corr[MT][4];
+    decode_group<MT>(wring + slot * kSlotBytes + lane * 16, xl, xts, accg, corr);
+    // the slot has been read by every lane: hand it back to the copy engine
+    __syncwarp();
+    if (i + kRing < nsl) {
+      issue_weights(slot, it_issue);
+      if (!HAD) issue_acts(slot, it_issue.g);
+      cp_async_arrive(bar0 + slot * 8);
+      slot_next<HAD>(it_issue, p.vbT, p.NG, p.kc);
+    }
+    // ---- apply this group's scales: lane holds s[64blk + 8g + 2j + b] for j=0..3, b=0..1 ----
+    const __half2* sh = reinterpret_cast<const __half2*>(&sc);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 sf = __half22float2(sh[j]);   // .x -> columns 16j+g, .y -> 16j+g+8
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        acc[t][j][0] = fmaf(accg[t][j][0] - corr[t][0], sf.x, acc[t][j][0]);
+        acc[t][j][1] = fmaf(accg[t][j][1] - corr[t][1], sf.x, acc[t][j][1]);
+        acc[t][j][2] = fmaf(accg[t][j][2] - corr[t][2], sf.y, acc[t][j][2]);
+        acc[t][j][3] = fmaf(accg[t][j][3] - corr[t][3], sf.y, acc[t][j][3]);
+      }
+    }
+    ++run_cnt;
+    const bool run_end = (i == nsl - 1) || (it.g + 1 == it.g_hi);
+    if (run_end) {
+      // ---- this warp's tile of block it.vb goes to scratch; the ticket counts slots ----
+      const int wc = it.g_hi - it.g_lo;
+      const long long first = (long long)p.vbT * it.g_lo + (long long)it.vb * wc;
+      const int jrun = run_index(first, s0 + i - (run_cnt - 1), wg, p.T, p.W);
+      float* tile = p.partials + ((size_t)((size_t)it.vb * p.nchunks + it.c) * p.Pc + jrun) * tile_elems;
+#pragma unroll
+      for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int m = 8 * t + 2 * c + (r & 1);
+            if (m < p.M) tile[m * 64 + 16 * j + g + 8 * (r >> 1)] = acc[t][j][r];
+            acc[t][j][r] = 0.f;
+          }
+      const bool swiglu = p.epilogue == UNIQL_EPILOGUE_SWIGLU;
+      const int unit = swiglu ? (it.vb >> 1) : it.vb;
+      const int need = swiglu ? 2 * p.NG : p.NG;
+      bool last;
+      if (run_cnt == need) {
+        __syncwarp();                     // the tile was written by this warp alone
+        last = true;
+      } else {
+        __threadfence();
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) {
+          old = atomicAdd(p.tickets + unit, run_cnt);
+          if (old + run_cnt == need) p.tickets[unit] = 0;   // leave the ticket clean for the next launch
+        }
+        old = __shfl_sync(0xffffffffu, old, 0);
+        last = (old + run_cnt == need);
+        if (last) __threadfence();
+      }
+      if (last && !finish_block(p, unit, lane)) timed_out = true;
+      run_cnt = 0;
+    }
+    slot_next<HAD>(it, p.vbT, p.NG, p.kc);
+    if (++slot == kRing) { slot = 0; parity ^= 1u; }
+  }
+  if (timed_out && p.status_word) atomicOr(p.status_word, UNIQL_STATUS_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+
+EncodeTiledFn encode_tiled_fn() {
+  static const EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      return (EncodeTiledFn)ptr;
+    return (EncodeTiledFn) nullptr;
+  }();
+  return fn;
+}
+
+int make_weight_map(CUtensorMap* map, const void* B, int64_t n, int64_t kt) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return cuda_fail(cudaErrorNotSupported);
+  cuuint64_t dims[2] = {(cuuint64_t)(2 * n), (cuuint64_t)kt};
+  cuuint64_t strides[1] = {(cuuint64_t)(2 * n) * 4};
+  cuuint32_t box[2] = {128, 8};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(B), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  return UNIQL_OK;
+}
+
+// Encoded tensor maps are pure functions of (address, n, k): keep them instead of encoding on every launch.
+struct MapKey {
+  const void* B;
+  int64_t n, kt;
+  bool operator==(const MapKey& o) const { return B == o.B && n == o.n && kt == o.kt; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.B) ^ (std::hash<int64_t>()(k.n) * 1000003u) ^ (std::hash<int64_t>()(k.kt) * 7919u);
+  }
+};
+static int cached_weight_map(CUtensorMap* out, const void* B, int64_t n, int64_t kt) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{B, n, kt};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto f = cache.find(key);
+    if (f != cache.end()) {
+      *out = f->second;
+      return UNIQL_OK;
+    }
+  }
+  int st = make_weight_map(out, B, n, kt);
+  if (st != UNIQL_OK) return st;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache[key] = *out;
+  return UNIQL_OK;
+}
+
+struct DecodePlan {
+  int variant;        // 0: 12 warps, m <= 2;  1: 8 warps, m <= 8;  2: 8 warps, two batch tiles (m <= 16);  3: 10 warps, m <= 4;
+                      // 4: 8 warps with three ring slots, m <= 2
+  int ring;
+  int warps, grid, W;
+  long long T;
+  int vbT, NG, kc, koff, nchunks, Pc, units;
+  int fused_had;      // the Hadamard transform runs in the kernel prologue
+  int hP, hlogP, hlogQ, hMdim, hbase, seg0;
+  int xbytes;
+  size_t smem;
+  size_t partial_bytes;
+};
+
+static int ilog2(int64_t v) {
+  int l = 0;
+  while ((1ll << l) < v) ++l;
+  return l;
+}
+
+// Geometry of a launch: depends on the shapes only (and on the SM count of the current device).
+static int make_plan(DecodePlan* pl, int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue,
+                     int64_t hadamard_dim, int64_t k_offset) {
+  if (m < 1 || m > 16 || nproj < 1 || nproj > kMaxProj || k <= 0 || k % 128) return UNIQL_ESHAPE;
+  DecodePlan P{};
+  P.variant = m <= 2 ? 0 : m <= 8 ? 1 : 2;
+  static const int force_variant = env_int("UNIQL_B200_DECODE_VARIANT", -1);
+  if (force_variant >= 0 && force_variant <= 4 && !(force_variant == 0 && m > 2) && !(force_variant == 1 && m > 8) &&
+      !(force_variant == 3 && m > 4) && !(force_variant == 4 && m > 2))
+    P.variant = force_variant;
+  P.warps = P.variant == 0 ? 12 : P.variant == 3 ? 10 : 8;
+  P.ring = P.variant == 4 ? 3 : 2;
+  P.grid = device_info().sm_count;
+  P.W = P.grid * P.warps;
+  P.NG = (int)(k / 128);
+  int64_t vb = 0;
+  for (int i = 0; i < nproj; ++i) {
+    if (n[i] <= 0 || n[i] % 64) return UNIQL_ESHAPE;
+    vb += n[i] / 64;
+  }
+  if (epilogue == UNIQL_EPILOGUE_SWIGLU && (nproj != 2 || n[0] != n[1])) return UNIQL_EINVAL;
+  if (epilogue != UNIQL_EPILOGUE_NONE && epilogue != UNIQL_EPILOGUE_SWIGLU) return UNIQL_EINVAL;
+  P.units = (int)(epilogue == UNIQL_EPILOGUE_SWIGLU ? vb / 2 : vb);
+  if ((size_t)P.units * sizeof(int) > UNIQL_SCRATCH_COUNTER_BYTES) return UNIQL_ESHAPE;
+  P.vbT = (int)vb;
+  P.T = (long long)vb * P.NG;
+  P.kc = P.NG; P.koff = 0; P.nchunks = 1;
+  P.fused_had = 0;
+  if (hadamard_dim) {
+    const int base = hadamard_base_of(hadamard_dim);
+    if (base == 0 || hadamard_dim > 40960 || k_offset < 0 || k_offset % 128 || k_offset + k > hadamard_dim) return UNIQL_ESHAPE;
+    int64_t pw = hadamard_dim / base;             // power-of-two part
+    int64_t seg = pw < 512 ? pw : 512;
+    P.hP = (int)seg; P.hlogP = ilog2(seg); P.hlogQ = ilog2(pw / seg); P.hMdim = (int)(hadamard_dim / seg);
+    P.hbase = base;
+    // the prologue holds one transformed segment per 128-value group or more, batches of at most 4 rows, and a base
+    // index that fits the 96-bit sign masks
+    if (seg >= 128 && m <= 4 && P.hMdim <= 96 && env_int("UNIQL_B200_FUSED_HADAMARD", 1)) {
+      P.kc = (int)(seg / 128);
+      const int64_t g0 = k_offset / 128;
+      P.koff = (int)(g0 % P.kc);
+      P.seg0 = (int)(g0 / P.kc);
+      P.nchunks = (P.NG + P.koff + P.kc - 1) / P.kc;
+      // every CTA must touch at most kMaxSeg segments
+      int worst = 0;
+      for (int cta = 0; cta < P.grid; ++cta) {
+        const long long a = P.T * (long long)(cta * P.warps) / P.W, b = P.T * (long long)((cta + 1) * P.warps) / P.W;
+        if (b <= a) continue;
+        const int c0 = slot_decode(a, P.vbT, P.NG, P.kc, P.koff).c, c1 = slot_decode(b - 1, P.vbT, P.NG, P.kc, P.koff).c;
+        if (c1 - c0 + 1 > worst) worst = c1 - c0 + 1;
+      }
+      if (worst <= kMaxSeg && P.nchunks <= 96) P.fused_had = 1;
+      else { P.kc = P.NG; P.koff = 0; P.nchunks = 1; }
+    }
+  }
+  // tiles a block can receive per chunk
+  int pc = 1;
+  for (int cc = 0; cc < P.nchunks; ++cc) {
+    const int lo = chunk_lo(cc, P.kc, P.koff), hi = chunk_hi(cc, P.kc, P.koff, P.NG);
+    for (int b = 0; b < P.vbT; ++b) {
+      const int r = runs_of(b, lo, hi, P.vbT, P.T, P.W);
+      if (r > pc) pc = r;
+    }
+  }
+  P.Pc = pc;
+  P.partial_bytes = (size_t)P.vbT * P.nchunks * P.Pc * (size_t)m * 64 * sizeof(float);
+  P.xbytes = P.fused_had ? 0 : (int)m * kXRowBytes;
+  const size_t rings = (size_t)P.warps * P.ring * (kSlotBytes + kSlotScaleBytes);
+  const size_t xs = P.fused_had ? (size_t)kMaxSeg * m * kSegRowBytes : (size_t)P.warps * P.ring * P.xbytes;
+  P.smem = rings + xs;
+  *pl = P;
+  return UNIQL_OK;
+}
+
+struct PlanKey {
+  int64_t m, k, n[kMaxProj], had, koff;
+  int nproj, epilogue, dev;
+  bool operator==(const PlanKey& o) const {
+    if (m != o.m || k != o.k || had != o.had || koff != o.koff || nproj != o.nproj || epilogue != o.epilogue || dev != o.dev)
+      return false;
+    for (int i = 0; i < kMaxProj; ++i)
+      if (n[i] != o.n[i]) return false;
+    return true;
+  }
+};
+struct PlanKeyHash {
+  size_t operator()(const PlanKey& k) const {
+    size_t h = (size_t)k.m * 1000003u ^ (size_t)k.k * 7919u ^ (size_t)k.had * 31u ^ (size_t)k.koff * 131u ^
+               (size_t)k.nproj * 17u ^ (size_t)k.epilogue * 13u ^ (size_t)k.dev * 11u;
+    for (int i = 0; i < kMaxProj; ++i) h = h * 1315423911u ^ (size_t)k.n[i];
+    return h;
+  }
+};
+static int cached_plan(DecodePlan* pl, int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue,
+                       int64_t hadamard_dim, int64_t k_offset) {
+  static std::mutex mu;
+  static std::unordered_map<PlanKey, DecodePlan, PlanKeyHash> cache;
+  PlanKey key{};
+  key.m = m; key.k = k; key.had = hadamard_dim; key.koff = k_offset; key.nproj = nproj; key.epilogue = epilogue;
+  cudaGetDevice(&key.dev);
+  for (int i = 0; i < kMaxProj; ++i) key.n[i] = (i < nproj && nproj <= kMaxProj) ? n[i] : 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto f = cache.find(key);
+    if (f != cache.end()) {
+      *pl = f->second;
+      return UNIQL_OK;
+    }
+  }
+  int st = make_plan(pl, m, k, n, nproj, epilogue, hadamard_dim, k_offset);
+  if (st != UNIQL_OK) return st;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *pl;
+  return UNIQL_OK;
+}
+
+static inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+size_t decode_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t hadamard_dim,
+                            int64_t k_offset) {
+  DecodePlan pl;
+  if (cached_plan(&pl, m, k, n, nproj, epilogue, hadamard_dim, k_offset) != UNIQL_OK) return UNIQL_SCRATCH_COUNTER_BYTES;
+  size_t total = UNIQL_SCRATCH_COUNTER_BYTES + align256(pl.partial_bytes);
+  if (hadamard_dim && !pl.fused_had) total += align256((size_t)m * hadamard_dim * 2);   // separate transform kernel
+  return total;
+}
+
+template <int MT, int WARPS, int MINB, bool HAD, int RING>
+static int launch_variant(const DecodeParams& p, const DecodePlan& pl, cudaStream_t stream) {
+  auto kern = w4a16_decode_kernel<MT, WARPS, MINB, HAD, RING>;
+  {
+    // function attributes are per device
+    static thread_local bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_set[dev]) {
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      attr_set[dev] = true;
+    }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)pl.grid);
+  cfg.blockDim = dim3(WARPS * 32);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int nattr = 0;
+  // Every launch may start early behind its predecessor; the kernel itself waits (griddepcontrol.wait)
+  // before it touches anything another kernel could have written.
+  static const int pdl_on = env_int("UNIQL_B200_PDL", 1);
+  if (pdl_on) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
+  UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+  return UNIQL_OK;
+}
+
+int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
+  int64_t n[kMaxProj] = {0, 0, 0, 0};
+  if (a.nproj < 1 || a.nproj > kMaxProj) return UNIQL_EINVAL;
+  for (int i = 0; i < a.nproj; ++i) n[i] = a.proj[i].n;
+  DecodePlan pl;
+  int st = cached_plan(&pl, a.m, a.k, n, a.nproj, a.epilogue, a.hadamard_dim, a.k_offset);
+  if (st != UNIQL_OK) return st;
+  const CommView* cv = a.comm;
+  if (cv && cv->gather_in && !pl.fused_had) return UNIQL_ESHAPE;     // the feature area is read by the prologue only
+  const size_t part_off = UNIQL_SCRATCH_COUNTER_BYTES;
+  const size_t xh_off = part_off + align256(pl.partial_bytes);
+  const size_t need = xh_off + ((a.hadamard_dim && !pl.fused_had) ? align256((size_t)a.m * a.hadamard_dim * 2) : 0);
+  if (!a.scratch || a.scratch_bytes < need || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return UNIQL_ESCRATCH;
+
+  const __half* Ain = (const __half*)a.A;
+  int64_t lda = a.lda;
+  if (a.hadamard_dim && !pl.fused_had) {
+    // separate transform kernel in front (rows of more than 4, or a split the prologue does not cover); the decode
+    // kernel's weight stream overlaps it through the programmatic dependent launch
+    if (a.k_offset != 0 || a.k != a.hadamard_dim) return UNIQL_ESHAPE;
+    __half* xh = (__half*)((char*)a.scratch + xh_off);
+    st = launch_hadamard(a.A, a.lda, xh, a.k, a.m, a.k, (float)(1.0 / sqrt((double)a.k)), UNIQL_F16, true, stream);
+    if (st != UNIQL_OK) return st;
+    Ain = xh;
+    lda = a.k;
+  }
+
+  DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  int vb = 0;
+  for (int i = 0; i < a.nproj; ++i) {
+    const DecodeProjArgs& q = a.proj[i];
+    st = cached_weight_map(&p.wmap[i], q.B, q.n, a.k / 16);
+    if (st != UNIQL_OK) return st;
+    p.proj[i].S = (const __half*)q.s; p.proj[i].bias = (const __half*)q.bias; p.proj[i].D = (__half*)q.D;
+    p.proj[i].ldd = q.ldd; p.proj[i].N = (int)q.n; p.proj[i].n_out = (int)q.n_out;
+    p.vb_start[i] = vb;
+    vb += (int)(q.n / 64);
+  }
+  for (int i = a.nproj; i <= kMaxProj; ++i) p.vb_start[i] = vb;
+  for (int i = a.nproj; i < kMaxProj; ++i) { p.wmap[i] = p.wmap[0]; p.proj[i] = p.proj[0]; }
+  p.A = Ain; p.lda = lda;
+  p.residual = (const __half*)a.residual; p.ldr = a.ldr;
+  p.tickets = (int*)a.scratch;
+  p.partials = (float*)((char*)a.scratch + part_off);
+  p.status_word = a.status_word;
+  p.T = pl.T; p.M = (int)a.m; p.NG = pl.NG; p.nproj = a.nproj; p.vbT = pl.vbT; p.W = pl.W; p.epilogue = a.epilogue;
+  p.kc = pl.kc; p.koff = pl.koff; p.nchunks = pl.nchunks; p.Pc = pl.Pc; p.xbytes = pl.xbytes;
+  p.had = pl.fused_had;
+  if (pl.fused_had) {
+    p.hP = pl.hP; p.hlogP = pl.hlogP; p.hlogQ = pl.hlogQ; p.hMdim = pl.hMdim; p.seg0 = pl.seg0;
+    p.hscale = (float)(1.0 / sqrt((double)a.hadamard_dim));
+    hadamard_base_signs(pl.hbase, p.hsign);
+  }
+  if (cv) {
+    p.cv = *cv;
+    if (cv->reduce && pl.units > cv->block_cap) return UNIQL_ESHAPE;
+    if (cv->gather_out && (cv->col_offset % 64 || cv->col_offset + (int64_t)pl.units * 64 > cv->feat_cap)) return UNIQL_ESHAPE;
+    if (cv->gather_in && a.hadamard_dim > cv->feat_cap) return UNIQL_ESHAPE;
+    if (cv->reduce && a.epilogue != UNIQL_EPILOGUE_NONE) return UNIQL_EINVAL;
+  }
+  if (pl.fused_had) {
+    if (pl.variant == 0) return launch_variant<1, 12, 2, true, 2>(p, pl, stream);
+    if (pl.variant == 3) return launch_variant<1, 10, 2, true, 2>(p, pl, stream);
+    if (pl.variant == 4) return launch_variant<1, 8, 2, true, 3>(p, pl, stream);
+    return launch_variant<1, 8, 2, true, 2>(p, pl, stream);     // m <= 4 here
+  }
+  if (pl.variant == 0) return launch_variant<1, 12, 2, false, 2>(p, pl, stream);
+  if (pl.variant == 3) return launch_variant<1, 10, 2, false, 2>(p, pl, stream);
+  if (pl.variant == 4) return launch_variant<1, 8, 2, false, 3>(p, pl, stream);
+  if (pl.variant == 1) return launch_variant<1, 8, 2, false, 2>(p, pl, stream);
+  return launch_variant<2, 8, 1, false, 2>(p, pl, stream);
+}
+
+// Host-side replay of the kernel's work split for one launch geometry: walks every warp's slots with the kernel's own
+// iterator and checks that each slot is taken exactly once, that every run of slots lands in its own tile below the
+// reserved count, and that the tickets of every block add up to what the last arriver waits for.
+template <bool CH>
+static int replay_plan(const DecodePlan& pl, int epilogue) {
+  const bool swiglu = epilogue == UNIQL_EPILOGUE_SWIGLU;
+  std::unordered_map<long long, int> tiles;
+  std::unordered_map<int, long long> tickets;
+  std::unordered_map<long long, int> seen;
+  for (int wg = 0; wg < pl.W; ++wg) {
+    const long long s0 = pl.T * wg / pl.W, s1 = pl.T * (wg + 1) / pl.W;
+    if (s1 <= s0) continue;
+    if (warp_of_slot(s0, pl.T, pl.W) != wg || warp_of_slot(s1 - 1, pl.T, pl.W) != wg) return 1;
+    SlotIt it = slot_at<CH>(s0, pl.vbT, pl.NG, pl.kc, pl.koff);
+    int run = 0;
+    for (long long i = 0; i < s1 - s0; ++i) {
+      const SlotIt ref = slot_decode(s0 + i, pl.vbT, pl.NG, pl.kc, pl.koff);
+      if (ref.vb != it.vb || ref.g != it.g || ref.c != it.c || ref.g_lo != it.g_lo || ref.g_hi != it.g_hi) return 2;
+      if (it.vb < 0 || it.vb >= pl.vbT || it.g < 0 || it.g >= pl.NG) return 3;
+      const long long id = (long long)it.vb * pl.NG + it.g;
+      if (seen[id]++) return 4;
+      ++run;
+      if (i == s1 - s0 - 1 || it.g + 1 == it.g_hi) {
+        const int wc = it.g_hi - it.g_lo;
+        const long long first = (long long)pl.vbT * it.g_lo + (long long)it.vb * wc;
+        const int jrun = run_index(first, s0 + i - (run - 1), wg, pl.T, pl.W);
+        if (jrun < 0 || jrun >= pl.Pc || it.c < 0 || it.c >= pl.nchunks) return 5;
+        if (jrun >= runs_of(it.vb, it.g_lo, it.g_hi, pl.vbT, pl.T, pl.W)) return 6;
+        const long long tile = ((long long)it.vb * pl.nchunks + it.c) * pl.Pc + jrun;
+        if (tiles[tile]++) return 7;
+        tickets[swiglu ? it.vb >> 1 : it.vb] += run;
+        run = 0;
+      }
+      slot_next<CH>(it, pl.vbT, pl.NG, pl.kc);
+    }
+  }
+  if ((long long)seen.size() != pl.T) return 8;
+  if ((int)tickets.size() != pl.units) return 9;
+  for (auto& kv : tickets)
+    if (kv.second != (swiglu ? 2 : 1) * (long long)pl.NG) return 10;
+  // the number of tiles a block's finisher reads equals the number written
+  long long expect = 0;
+  for (int cc = 0; cc < pl.nchunks; ++cc)
+    for (int b = 0; b < pl.vbT; ++b)
+      expect += runs_of(b, chunk_lo(cc, pl.kc, pl.koff), chunk_hi(cc, pl.kc, pl.koff, pl.NG), pl.vbT, pl.T, pl.W);
+  if (expect != (long long)tiles.size()) return 11;
+  return 0;
+}
+
+// ------------------------------------------------------------------ entry point without allocation
+// Scratch for uniql_w4a16_linear_static: ticket counters followed by the partial tiles.  It lives in the
+// library image: every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[UNIQL_STATIC_SCRATCH_BYTES];
+
+struct StaticScratchState {
+  void* ptr;      // device address of g_static_scratch on that device
+  bool ready;
+};
+static StaticScratchState g_static_state[64];
+static std::mutex g_static_mutex;
+
+// Resolves the device address of the array (its name is only a host-side handle) once per device, with that
+// device current, and clears the counter region through the caller's stream.
+static int static_scratch_for_current_device(void** out, cudaStream_t stream) {
+  int dev = 0;
+  UNIQL_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return UNIQL_EINVAL;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticScratchState& st = g_static_state[dev];
+  if (!st.ready) {
+    void* ptr = nullptr;
+    UNIQL_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    UNIQL_CUDA_TRY(cudaMemsetAsync(ptr, 0, UNIQL_SCRATCH_COUNTER_BYTES, stream));
+    st.ptr = ptr;
+    st.ready = true;
+  }
+  *out = st.ptr;
+  return UNIQL_OK;
+}
+
+}  // namespace uniql
+
+extern "C" int uniql_w4a16_plan_selftest(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue,
+                                         int64_t hadamard_dim, int64_t k_offset, int* fused_hadamard_out) {
+  using namespace uniql;
+  if (!n) return UNIQL_EINVAL;
+  DecodePlan pl;
+  int st = make_plan(&pl, m, k, n, nproj, epilogue, hadamard_dim, k_offset);
+  if (st != UNIQL_OK) return st;
+  if (fused_hadamard_out) *fused_hadamard_out = pl.fused_had;
+  return pl.fused_had ? replay_plan<true>(pl, epilogue) : replay_plan<false>(pl, epilogue);
+}
+
+extern "C" int uniql_w4a16_linear_static(const void* A, int64_t lda, const void* B, const void* s, const void* bias,
+                                         void* D, int64_t ldd, int64_t m, int64_t n, int64_t n_out, int64_t k,
+                                         int groupsize, int* status_word, void* stream_) {
+  using namespace uniql;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (groupsize != 128) return groupsize == -1 ? UNIQL_EGROUPSIZE : UNIQL_EINVAL;
+  if (m < 0 || n <= 0 || k <= 0 || n_out <= 0 || n_out > n) return UNIQL_EINVAL;
+  if (m > 16) return UNIQL_ESHAPE;                       // decode kernel only
+  if (n % 64 != 0 || k % 128 != 0 || n > (int64_t)1 << 22 || k > (int64_t)1 << 22) return UNIQL_ESHAPE;
+  if (lda < k || ldd < n_out || lda % 8 != 0) return UNIQL_EINVAL;
+  if (m == 0) return UNIQL_OK;
+  if (!A || !B || !s || !D) return UNIQL_EINVAL;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(s) || (reinterpret_cast<uintptr_t>(D) & 1u)) return UNIQL_EINVAL;
+  const size_t need = decode_scratch_bytes(m, k, &n, 1, UNIQL_EPILOGUE_NONE, 0, 0);
+  if (need > (size_t)UNIQL_STATIC_SCRATCH_BYTES) return UNIQL_ESTATIC;
+  void* scratch = nullptr;
+  int st = static_scratch_for_current_device(&scratch, stream);
+  if (st != UNIQL_OK) return st;
+  DecodeArgs a{};
+  a.A = A; a.lda = lda; a.m = m; a.k = k; a.nproj = 1;
+  a.proj[0].B = B; a.proj[0].s = s; a.proj[0].bias = bias; a.proj[0].D = D; a.proj[0].ldd = ldd;
+  a.proj[0].n = n; a.proj[0].n_out = n_out;
+  a.epilogue = UNIQL_EPILOGUE_NONE;
+  a.scratch = scratch; a.scratch_bytes = UNIQL_STATIC_SCRATCH_BYTES;
+  a.status_word = status_word;
+  a.comm = nullptr;
+  return launch_decode(a, stream);
+}

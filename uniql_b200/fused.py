@@ -1,0 +1,87 @@
+"""Block-level entry points that run what UniQL's decoder blocks issue as several launches in one.
+
+The reference's blocks call their quantized linears one by one and glue them with elementwise kernels:
+`down_proj(act_fn(gate_proj(x)) * up_proj(x))` (modeling/llama/llama_qblocks.py:48-51), three q/k/v linears
+(:104-106), `residual + o_proj(...)`.  At decode sizes every one of those launches costs more than the bytes it
+moves, so for up to 16 rows the functions below issue one grouped kernel (uniql_w4a16_linear_group) per step;
+larger batches run the same modules one after the other on the tensor-core kernels, with the elementwise maths
+in PyTorch exactly as the reference does it.  All take and return the tensors the reference's code would.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+
+DECODE_ROWS = 16
+
+
+def _layer(mod):
+    return (mod.weight, mod.scale, mod.bias, mod.out_features)
+
+
+def _flat(x, mod):
+    x2 = x.reshape(-1, x.shape[-1])
+    if mod.pad_in:
+        x2 = F.pad(x2, (0, mod.pad_in), "constant", 0)
+    return x2
+
+
+@torch.no_grad()
+def gate_up_swiglu(gate_proj, up_proj, x):
+    """silu(gate_proj(x)) * up_proj(x) for two W4A16B16O16Linear modules of the same shape."""
+    x2 = _flat(x, gate_proj)
+    if x2.shape[0] <= DECODE_ROWS:
+        (h,) = ops.w4a16_linear_group(x2, [_layer(gate_proj), _layer(up_proj)], epilogue="swiglu")
+    else:
+        h = F.silu(gate_proj(x2)) * up_proj(x2)
+    return h.view(*x.shape[:-1], gate_proj.out_features)
+
+
+@torch.no_grad()
+def qkv_proj(q_proj, k_proj, v_proj, x):
+    """(q_proj(x), k_proj(x), v_proj(x)) for three W4A16B16O16Linear modules with the same in_features."""
+    x2 = _flat(x, q_proj)
+    mods = (q_proj, k_proj, v_proj)
+    if x2.shape[0] <= DECODE_ROWS:
+        outs = ops.w4a16_linear_group(x2, [_layer(m) for m in mods])
+    else:
+        outs = [m(x2) for m in mods]
+    return tuple(o.view(*x.shape[:-1], m.out_features) for o, m in zip(outs, mods))
+
+
+@torch.no_grad()
+def linear_residual(proj, x, residual):
+    """residual + proj(x) (o_proj / down_proj / out_proj with the block's skip connection); when `proj` is a
+    W4A16B16O16HadLinear its Hadamard transform of x is part of the same call."""
+    x2 = _flat(x, proj)
+    r2 = residual.reshape(-1, residual.shape[-1])
+    had = proj.size_k if getattr(proj, "hadamard_dim", 0) else 0
+    if x2.shape[0] <= DECODE_ROWS and r2.stride(-1) == 1:
+        (y,) = ops.w4a16_linear_group(x2, [_layer(proj)], residual=r2, hadamard_dim=had)
+    else:
+        y = r2 + proj(x2)
+    return y.view(*residual.shape[:-1], proj.out_features)
+
+
+class W4A16GateUp(torch.nn.Module):
+    """Holds a block's gate_proj and up_proj and returns act_fn(gate) * up in one launch at decode sizes."""
+
+    def __init__(self, gate_proj, up_proj):
+        super().__init__()
+        self.gate_proj, self.up_proj = gate_proj, up_proj
+
+    def forward(self, x):
+        return gate_up_swiglu(self.gate_proj, self.up_proj, x)
+
+
+class W4A16QKV(torch.nn.Module):
+    """Holds a block's q/k/v projections and returns the three results of one launch at decode sizes."""
+
+    def __init__(self, q_proj, k_proj, v_proj):
+        super().__init__()
+        self.q_proj, self.k_proj, self.v_proj = q_proj, k_proj, v_proj
+
+    def forward(self, x):
+        return qkv_proj(self.q_proj, self.k_proj, self.v_proj, x)

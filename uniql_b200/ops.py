@@ -7,7 +7,9 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import check, lib
+import ctypes
+
+from ._lib import Proj, check, lib
 
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
 
@@ -131,6 +133,90 @@ def w4a16_linear(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, bia
     if code != 0:
         check(code, "uniql_w4a16_linear")
     return out
+
+
+_EPILOGUES = {"none": 0, "swiglu": 1}
+TP_REDUCE, TP_GATHER_OUT, TP_GATHER_IN = 1, 2, 4
+_group_need_cache: dict = {}
+
+
+def w4a16_linear_group(x: torch.Tensor | None, layers, epilogue: str = "none", residual: torch.Tensor | None = None,
+                       hadamard_dim: int = 0, outs=None, comm=None, tp_flags: int = 0, col_offset: int = 0,
+                       k_offset: int = 0, m: int | None = None):
+    """One decode launch (m <= 16) for up to four projections that read the same activations.
+
+    layers: sequence of (weight int32 [k/16, 2n], scale fp16 [k/128, n], bias fp16 or None, n_out).
+    epilogue "swiglu": two layers (gate, up) -> one output silu(gate) * up.  residual: fp16 [m, n_out] added to the
+    result (single layer or swiglu).  hadamard_dim: size of the Hadamard transform applied to the rows of x first.
+    With `comm` (communicator handle) and tp_flags (TP_REDUCE / TP_GATHER_OUT / TP_GATHER_IN) the launch is a step of a
+    tensor-parallel layer; with TP_GATHER_IN x may be None and m must be given.
+    Returns the list of outputs (one tensor for swiglu)."""
+    if epilogue not in _EPILOGUES:
+        raise RuntimeError(f"unknown epilogue {epilogue!r}")
+    layers = list(layers)
+    w0 = layers[0][0]
+    if not w0.is_cuda:
+        raise RuntimeError("weights must be CUDA tensors (uniql_b200 has no CPU path)")
+    dev = w0.device
+    k = w0.shape[0] * 16
+    if x is not None:
+        if not x.is_cuda or x.dtype != torch.float16 or x.dim() != 2:
+            raise RuntimeError("x must be a 2-D float16 CUDA tensor")
+        if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
+            x = x.contiguous() if x.stride(1) != 1 else x.clone(memory_format=torch.contiguous_format)
+        m = x.shape[0]
+        if x.shape[1] != k:
+            raise RuntimeError(f"size_k mismatch: x has {x.shape[1]} columns, packed weight covers {k}")
+        lda = x.stride(0) if m > 1 else k
+        x_ptr = x.data_ptr()
+    else:
+        if not (tp_flags & TP_GATHER_IN) or m is None:
+            raise RuntimeError("x may only be omitted for a TP_GATHER_IN launch with m given")
+        lda, x_ptr = k, None
+    n_outputs = 1 if epilogue == "swiglu" else len(layers)
+    if outs is None:
+        outs = [torch.empty((m, layers[i][3]), dtype=torch.float16, device=dev) for i in range(n_outputs)]
+    arr = (Proj * len(layers))()
+    ns = (ctypes.c_int64 * len(layers))()
+    for i, (w, s, b, n_out) in enumerate(layers):
+        if w.dtype != torch.int32 or s.dtype != torch.float16 or not w.is_contiguous() or not s.is_contiguous():
+            raise RuntimeError("weight must be contiguous int32 and scale contiguous float16")
+        if w.shape[0] * 16 != k or s.shape[0] * 128 != k or s.shape[1] * 2 != w.shape[1]:
+            raise RuntimeError("projections of one launch must share k, with group-128 scales")
+        if b is not None and (b.dtype != torch.float16 or b.numel() < n_out or not b.is_contiguous()):
+            raise RuntimeError("bias must be a contiguous float16 tensor with at least n_out elements")
+        d = outs[min(i, n_outputs - 1)]
+        arr[i].B, arr[i].s = w.data_ptr(), s.data_ptr()
+        arr[i].bias = b.data_ptr() if b is not None else None
+        arr[i].D, arr[i].ldd = d.data_ptr(), d.stride(0)
+        arr[i].n, arr[i].n_out = s.shape[1], n_out
+        ns[i] = s.shape[1]
+    res_ptr, ldr = None, 0
+    if residual is not None:
+        if residual.dtype != torch.float16 or residual.dim() != 2 or residual.stride(1) != 1:
+            raise RuntimeError("residual must be a 2-D float16 tensor with unit column stride")
+        res_ptr, ldr = residual.data_ptr(), residual.stride(0)
+    idx = dev.index
+    L = lib()
+    with torch.cuda.device(dev):
+        key = (m, k, tuple(ns), _EPILOGUES[epilogue], hadamard_dim)
+        nbytes = _group_need_cache.get(key)
+        if nbytes is None:
+            nbytes = _group_need_cache[key] = L.uniql_w4a16_group_scratch_bytes(m, k, ns, len(layers), _EPILOGUES[epilogue],
+                                                                                 hadamard_dim)
+        scratch = _scratch_for(dev, nbytes)
+        st = status_word(dev)
+        stream = torch._C._cuda_getCurrentRawStream(idx)
+        if comm is not None:
+            code = L.uniql_w4a16_linear_group_tp(comm, tp_flags, col_offset, k_offset, x_ptr, lda, m, k, arr, len(layers),
+                                                 _EPILOGUES[epilogue], res_ptr, ldr, hadamard_dim, scratch.data_ptr(),
+                                                 scratch.numel(), st.data_ptr(), stream)
+        else:
+            code = L.uniql_w4a16_linear_group(x_ptr, lda, m, k, arr, len(layers), _EPILOGUES[epilogue], res_ptr, ldr,
+                                              hadamard_dim, scratch.data_ptr(), scratch.numel(), st.data_ptr(), stream)
+    if code != 0:
+        check(code, "uniql_w4a16_linear_group")
+    return outs
 
 
 def w4_embedding(ids: torch.Tensor, weight: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:

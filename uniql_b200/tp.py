@@ -100,8 +100,8 @@ class RowParallelW4A16Linear(nn.Module):
     """This rank's slice of the input features; partial outputs are summed over the process group."""
 
     def __init__(self, full: W4A16B16O16Linear, rank: int, world: int, group=None, bounds=None, fused=None):
-        """fused: a PushAllReduce dedicated to this call-site shape; when given, decode-size calls (m <= 16) do
-        the cross-GPU sum inside the linear kernel instead of a separate collective."""
+        """fused: a PushAllReduce; when given, decode-size calls (m <= 16) do the cross-GPU sum inside the linear
+        kernel instead of a separate collective."""
         super().__init__()
         self.fused = fused
         bounds = bounds or row_bounds(full.size_k, world)
@@ -116,8 +116,8 @@ class RowParallelW4A16Linear(nn.Module):
         if self.world > 1 and self.fused is not None:
             x2 = x_local.reshape(-1, x_local.shape[-1])
             if self.fused.fits_fused(x2.shape[0], self.local.size_n):
-                y = self.fused.linear_all_reduce(x2, self.local.weight, self.local.scale, self.bias,
-                                                 self.local.out_features)
+                b = self.bias.data if self.bias is not None else None
+                y = self.fused.linear_all_reduce(x2, self.local.weight, self.local.scale, b, self.local.out_features)
                 return y.view(*x_local.shape[:-1], self.local.out_features)
         y = self.local(x_local)
         if self.world > 1:
@@ -192,13 +192,31 @@ class PushAllReduce:
         return self.all_reduce(full)
 
     def fits_fused(self, m: int, n_stored: int) -> bool:
-        return m <= 16 and m * n_stored <= self.max_elems
+        """The fused exchanges hold 16 batch rows of up to max_elems / 16 columns."""
+        return m <= 16 and 16 * n_stored <= self.max_elems
 
-    def linear_all_reduce(self, x, weight, scale, bias, n_out):
-        """Row-parallel W4A16 linear + sum over ranks in one kernel launch (uniql_w4a16_linear_allreduce).
-        Keep one PushAllReduce per call-site shape: the epochs of its staging area advance per call."""
+    def linear_all_reduce(self, x, weight, scale, bias, n_out, residual=None):
+        """Row-parallel W4A16 linear + sum over ranks (+ bias, + residual) in one kernel launch.  Calls of different
+        shapes may share the communicator (staging is addressed per 64-column block, each with its own epoch)."""
         from . import ops
-        return ops.w4a16_linear(x, weight, scale, bias, n_out, comm=self._comm)
+        return ops.w4a16_linear_group(x, [(weight, scale, bias, n_out)], residual=residual, comm=self._comm,
+                                      tp_flags=ops.TP_REDUCE)[0]
+
+    def gate_up_gather(self, x, gate, up, col_offset: int):
+        """Column-parallel gate/up shard: h = silu(gate x) * (up x) in one launch whose epilogue also stores the
+        result columns, from feature index col_offset on, into every rank's feature area.  gate / up are
+        (weight, scale, bias, n_out).  Returns this rank's shard of h."""
+        from . import ops
+        return ops.w4a16_linear_group(x, [gate, up], epilogue="swiglu", comm=self._comm, tp_flags=ops.TP_GATHER_OUT,
+                                      col_offset=col_offset)[0]
+
+    def down_gather_reduce(self, m: int, down, hadamard_dim: int, k_offset: int, residual=None):
+        """Row-parallel down/out projection of the row gathered by the preceding gate_up_gather: every rank
+        transforms the full row (Hadamard of hadamard_dim points) in the kernel prologue, multiplies its own k slice
+        (from feature k_offset on) and the partial results are summed over the ranks in the epilogue.  One launch."""
+        from . import ops
+        return ops.w4a16_linear_group(None, [down], residual=residual, hadamard_dim=hadamard_dim, comm=self._comm,
+                                      tp_flags=ops.TP_GATHER_IN | ops.TP_REDUCE, k_offset=k_offset, m=m)[0]
 
     def close(self):
         if self._comm:
