@@ -40,7 +40,9 @@ enum { UNIQL_F16 = 0, UNIQL_BF16 = 1, UNIQL_F32 = 2 };
 /* Bits that kernels OR into *status_word (device int, may be NULL). */
 enum {
   UNIQL_STATUS_BAD_TOKEN_ID = 1,  /* an embedding id was outside [0, vocab); row written as zeros */
-  UNIQL_STATUS_WAIT_TIMEOUT = 2   /* a bounded wait on an asynchronous copy gave up; the output is invalid */
+  UNIQL_STATUS_WAIT_TIMEOUT = 2,  /* a bounded wait (asynchronous copy, or words another GPU has to write) gave up;
+                                     the output is invalid */
+  UNIQL_STATUS_BAD_INDEX = 4      /* a slicing index pointed outside the source layer; that column / row was written as zeros */
 };
 
 int uniql_abi_version(void);
@@ -156,19 +158,21 @@ int uniql_w4a16_quantize(const void* W, int64_t ldw, int64_t n_out, int64_t k_in
  * reference drops the k padding before slicing and pads with zeros afterwards); pass size_k to keep every row.
  *   packed_in  int32 [size_k/16, 2*n_src_pad]   scales_in  fp16 [size_k/128, n_src_pad] (permuted)
  *   packed_out int32 [size_k/16, 2*n_out_pad]   scales_out fp16 [size_k/128, n_out_pad] (permuted)
- *   col_index  DEVICE int32 [n_new], values in [0, n_src_pad) or negative
+ *   col_index  DEVICE int32 [n_new], values in [0, n_src_pad) or negative; a value >= n_src_pad is treated like a
+ *              negative one and raises UNIQL_STATUS_BAD_INDEX in *status_word (device int, may be NULL)
  *
  * uniql_w4a16_dequantize_rows: out[n][j] = fp16((q - 8) * s) of source row row_index[j], column n, for n < n_real and
  * j < k_new, row stride ld (elements): the [out_features, in_features] layout uniql_w4a16_quantize reads, so that
  * "keep these input rows and quantise again" (slice_w4a16_o_proj :632-650, slice_w4a16_out_proj :845-862) is two calls.
- *   row_index  DEVICE int32 [k_new], values in [0, size_k)
+ *   row_index  DEVICE int32 [k_new], values in [0, size_k); any other value writes zeros for that row and raises
+ *              UNIQL_STATUS_BAD_INDEX in *status_word
  */
 int uniql_w4a16_gather_columns(const void* packed_in, const void* scales_in, int64_t size_k, int64_t n_src_pad,
                                const int32_t* col_index, int64_t n_new, int64_t zero_rows_from,
-                               void* packed_out, void* scales_out, int64_t n_out_pad, void* stream);
+                               void* packed_out, void* scales_out, int64_t n_out_pad, int* status_word, void* stream);
 int uniql_w4a16_dequantize_rows(const void* packed, const void* scales, int64_t size_k, int64_t n_src_pad,
                                 const int32_t* row_index, int64_t k_new, int64_t n_real, void* out, int64_t ld,
-                                void* stream);
+                                int* status_word, void* stream);
 
 /* Host helper: writes the base x base ±1 matrix (row-major int8) this library uses for
  * base in {12, 20, 28, 40}; `out` is a HOST pointer.  Returns UNIQL_ESHAPE for other orders. */
@@ -239,9 +243,18 @@ typedef struct uniql_w4a16_proj {
   int64_t ldd;
   int64_t n, n_out;
 } uniql_w4a16_proj;
+/* Optional hint: byte ranges (at most UNIQL_MAX_PREFETCH, 128-byte aligned device pointers) that the launch asks L2
+ * for as soon as its own weight stream ends -- the packed weights of the launches that come next in the decode step.
+ * HBM then keeps working while this launch drains and the next one starts.  Pure hint: no effect on results. */
+#define UNIQL_MAX_PREFETCH 4
+typedef struct uniql_prefetch {
+  const void* ptr;
+  size_t bytes;
+} uniql_prefetch;
 int uniql_w4a16_linear_group(const void* A, int64_t lda, int64_t m, int64_t k, const uniql_w4a16_proj* proj,
                              int nproj, int epilogue, const void* residual, int64_t ldr, int64_t hadamard_dim,
-                             void* scratch, size_t scratch_bytes, int* status_word, void* stream);
+                             const uniql_prefetch* next, int nnext, void* scratch, size_t scratch_bytes,
+                             int* status_word, void* stream);
 size_t uniql_w4a16_group_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue,
                                        int64_t hadamard_dim);
 
@@ -262,8 +275,9 @@ size_t uniql_w4a16_group_scratch_bytes(int64_t m, int64_t k, const int64_t* n, i
 enum { UNIQL_TP_REDUCE = 1, UNIQL_TP_GATHER_OUT = 2, UNIQL_TP_GATHER_IN = 4 };
 int uniql_w4a16_linear_group_tp(void* comm, int flags, int64_t col_offset, int64_t k_offset, const void* A,
                                 int64_t lda, int64_t m, int64_t k, const uniql_w4a16_proj* proj, int nproj,
-                                int epilogue, const void* residual, int64_t ldr, int64_t hadamard_dim, void* scratch,
-                                size_t scratch_bytes, int* status_word, void* stream);
+                                int epilogue, const void* residual, int64_t ldr, int64_t hadamard_dim,
+                                const uniql_prefetch* next, int nnext, void* scratch, size_t scratch_bytes,
+                                int* status_word, void* stream);
 
 /*
  * Host-only check of the decode kernel's work split for one launch geometry (no GPU work is enqueued): replays every

@@ -135,3 +135,48 @@ def test_gather_and_dequantize_kernels_against_the_host_path(n, k, keep):
     want = deq[rows].t().contiguous()
     got = ops.w4a16_dequantize_rows(packed.cuda(), scale.cuda(), rows, n)
     assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.gpu
+def test_out_of_range_indices_are_refused_and_flagged():
+    """An index outside the source layer never reads out of bounds: the wrapper raises, and the kernels themselves
+    (called through the C ABI without the wrapper's check) write zeros and raise a status bit."""
+    from uniql_b200 import ops
+    from uniql_b200._lib import lib
+    n, k = 320, 256
+    g = torch.Generator().manual_seed(1)
+    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.float16)
+    _, packed, scale = qh.w4a16_quantize(w.t().contiguous(), 4, 128, None, (256 - n % 256) % 256)
+    packed, scale = packed.cuda(), scale.cuda()
+    n_src = scale.shape[1]
+    with pytest.raises(RuntimeError):
+        ops.w4a16_gather_columns(packed, scale, torch.tensor([0, n_src, 3]), 64)
+    with pytest.raises(RuntimeError):
+        ops.w4a16_dequantize_rows(packed, scale, torch.tensor([0, k, 3]), n)
+    ops.read_and_clear_status("cuda")
+    st = ops.status_word(torch.device("cuda", 0))
+    idx = torch.tensor([5, n_src + 7, 9], dtype=torch.int32, device="cuda")
+    out_p = torch.full((k // 16, 128), -1, dtype=torch.int32, device="cuda")
+    out_s = torch.ones((k // 128, 64), dtype=torch.float16, device="cuda")
+    assert lib().uniql_w4a16_gather_columns(packed.data_ptr(), scale.data_ptr(), k, n_src, idx.data_ptr(), 3, k,
+                                            out_p.data_ptr(), out_s.data_ptr(), 64, st.data_ptr(), None) == 0
+    assert ops.read_and_clear_status("cuda") == 4
+    codes = qh.unpack_w4a16_permute_weights(out_p.cpu(), k, 64, 4, qh.get_w4a16_weight_perms(), 128)
+    want = qh.unpack_w4a16_permute_weights(packed.cpu(), k, n_src, 4, qh.get_w4a16_weight_perms(), 128)
+    assert torch.equal(codes[:, 0], want[:, 5]) and torch.equal(codes[:, 2], want[:, 9]) and int(codes[:, 1].abs().max()) == 0
+    rows = torch.tensor([3, -2, k + 100, 7], dtype=torch.int32, device="cuda")
+    deq = torch.full((n, 4), 9.0, dtype=torch.float16, device="cuda")
+    assert lib().uniql_w4a16_dequantize_rows(packed.data_ptr(), scale.data_ptr(), k, n_src, rows.data_ptr(), 4, n,
+                                             deq.data_ptr(), 4, st.data_ptr(), None) == 0
+    assert ops.read_and_clear_status("cuda") == 4
+    full = qh.w4a16_dequantize(packed.cpu(), scale.cpu())[:, :n]
+    assert torch.equal(deq[:, 0].cpu(), full[3]) and torch.equal(deq[:, 3].cpu(), full[7])
+    assert float(deq[:, 1:3].abs().max()) == 0.0
+
+
+def test_host_path_raises_on_out_of_range_columns():
+    g = torch.Generator().manual_seed(2)
+    w = (torch.randn(192, 256, generator=g) * 0.02).to(torch.float16)
+    _, packed, scale = qh.w4a16_quantize(w.t().contiguous(), 4, 128, None, 64)
+    with pytest.raises(IndexError):
+        mh._select_columns(packed, scale, 256, 256, torch.tensor([0, 999]), True)

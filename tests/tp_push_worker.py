@@ -55,24 +55,55 @@ def main():
     for r, sz in enumerate(sizes):
         ok &= bool((gathered[:, off:off + sz] == r + 1).all())
         off += sz
-    # ---- fused row-parallel linear + all-reduce equals linear followed by the stand-alone push all-reduce ----
-    from uniql_b200.quantize.quant_linear_layers import W4A16B16O16Linear
-    torch.manual_seed(5)                                    # same full layer on every rank
-    for n, k, m in [(4096, 4096, 1), (1024, 2048, 16), (4096, 14336, 4)]:
+    # ---- fused row-parallel linear + all-reduce equals linear followed by the stand-alone push all-reduce.
+    # ONE communicator serves every shape, and the shapes alternate call by call: the staging words are addressed per
+    # 64-column block with per-block epochs, so a change of width must not pick up words of an earlier call ----
+    from uniql_b200.quantize.quant_linear_layers import W4A16B16O16HadLinear, W4A16B16O16Linear
+    torch.manual_seed(5)                                    # same full layers on every rank
+    chan = tp.PushAllReduce(max_elems=16 * 16384)
+    cases = []
+    for n, k, m in [(4096, 4096, 1), (1024, 2048, 16), (4096, 14336, 4), (512, 1024, 2)]:
         full = W4A16B16O16Linear.from_fp16(torch.nn.Linear(k, n, bias=True).half()).to(dev)
-        chan = tp.PushAllReduce(max_elems=16 * 4096)          # one channel per call-site shape
-        row_fused = tp.RowParallelW4A16Linear(full, rank, world, fused=chan)
-        row_plain = tp.RowParallelW4A16Linear(full, rank, world)
-        g = torch.Generator(device=dev).manual_seed(77)
-        xin = torch.randn(m, k, device=dev, generator=g).half()[:, row_plain.k0:row_plain.k1]
-        for call in range(3):
-            y_f = row_fused(xin * (call + 1))
-            part = row_plain.local(xin * (call + 1))
+        cases.append((full, tp.RowParallelW4A16Linear(full, rank, world, fused=chan),
+                      tp.RowParallelW4A16Linear(full, rank, world), m, k))
+    for call in range(3):
+        for full, row_fused, row_plain, m, k in cases:
+            xfull = torch.randn(m, k, device=dev, generator=torch.Generator(device=dev).manual_seed(77 + call)).half()
+            xin = xfull[:, row_plain.k0:row_plain.k1]
+            y_f = row_fused(xin)
+            part = row_plain.local(xin)
             y_p = ar.all_reduce(part.clone().view(-1)).view_as(part)
             torch.cuda.synchronize()
             ok &= bool(torch.allclose(y_f.float(), (y_p.float() + full.bias.float()), rtol=2e-3, atol=2e-3))
-            y_full = full(torch.randn(m, k, device=dev, generator=torch.Generator(device=dev).manual_seed(77)).half() * (call + 1))
+            y_full = full(xfull)
             ok &= bool(torch.allclose(y_f.float(), y_full.float(), rtol=2e-2, atol=2e-2 * float(y_full.float().abs().max())))
+    # ---- the decode MLP of a tensor-parallel layer in two launches: gate/up shard with SwiGLU whose epilogue stores
+    # the activated columns into every rank's feature area, then the down shard that reads the full row there,
+    # transforms it (Hadamard in the prologue), multiplies its k slice and sums over the ranks in its epilogue ----
+    from uniql_b200 import fused as fz
+    for hidden, inter, m in [(1024, 3584, 1), (4096, 14336, 1), (4096, 14336, 4), (4096, 8192, 2)]:
+        if (inter // 64) % world or (inter // 128) % world:
+            continue
+        gate = W4A16B16O16Linear.from_fp16(torch.nn.Linear(hidden, inter, bias=False).half()).to(dev)
+        up = W4A16B16O16Linear.from_fp16(torch.nn.Linear(hidden, inter, bias=False).half()).to(dev)
+        down = W4A16B16O16HadLinear.from_fp16(torch.nn.Linear(inter, hidden, bias=False).half()).to(dev)
+        c0, c1 = tp.column_bounds(inter, world)[rank]
+        k0, k1 = tp.row_bounds(inter, world)[rank]
+        assert (c0, c1) == (k0, k1)
+        gw, gs = tp.shard_columns(gate.weight, gate.scale, c0, c1)
+        uw, us = tp.shard_columns(up.weight, up.scale, c0, c1)
+        dw, ds = tp.shard_rows(down.weight, down.scale, k0, k1)
+        for call in range(3):
+            x = torch.randn(m, hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(9 + call)).half()
+            res = torch.randn(m, hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(19 + call)).half()
+            h_loc = chan.gate_up_gather(x, (gw, gs, None, c1 - c0), (uw, us, None, c1 - c0), c0)
+            y = chan.down_gather_reduce(m, (dw, ds, None, hidden), inter, k0, residual=res)
+            torch.cuda.synchronize()
+            h_full = fz.gate_up_swiglu(gate, up, x)
+            ok &= bool(torch.equal(h_loc, h_full[:, c0:c1]))
+            y_full = fz.linear_residual(down, h_full, res)
+            lin = (y_full.float() - res.float())
+            ok &= bool(torch.allclose(y.float(), y_full.float(), rtol=2e-2, atol=2e-2 * float(lin.abs().max())))
     ok &= ops.read_and_clear_status(dev) == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -13,6 +13,11 @@ _c = ctypes
 _lib = None
 
 
+class Prefetch(ctypes.Structure):
+    """uniql_prefetch of include/uniql_b200.h: a byte range to pull into L2 when a decode launch ends."""
+    _fields_ = [("ptr", _c.c_void_p), ("bytes", _c.c_size_t)]
+
+
 class Proj(ctypes.Structure):
     """uniql_w4a16_proj of include/uniql_b200.h: one projection of a grouped decode launch."""
     _fields_ = [("B", _c.c_void_p), ("s", _c.c_void_p), ("bias", _c.c_void_p), ("D", _c.c_void_p),
@@ -37,13 +42,13 @@ SYMBOLS = {
     "uniql_w4a16_scratch_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64]),
     "uniql_w4a16_linear_group": (_c.c_int, [
         _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.POINTER(Proj), _c.c_int, _c.c_int, _c.c_void_p, _c.c_int64,
-        _c.c_int64, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
+        _c.c_int64, _c.POINTER(Prefetch), _c.c_int, _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "uniql_w4a16_group_scratch_bytes": (_c.c_size_t, [
         _c.c_int64, _c.c_int64, _c.POINTER(_c.c_int64), _c.c_int, _c.c_int, _c.c_int64]),
     "uniql_w4a16_linear_group_tp": (_c.c_int, [
         _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64,
-        _c.POINTER(Proj), _c.c_int, _c.c_int, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_size_t,
-        _c.c_void_p, _c.c_void_p]),
+        _c.POINTER(Proj), _c.c_int, _c.c_int, _c.c_void_p, _c.c_int64, _c.c_int64, _c.POINTER(Prefetch), _c.c_int,
+        _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "uniql_w4a16_plan_selftest": (_c.c_int, [
         _c.c_int64, _c.c_int64, _c.POINTER(_c.c_int64), _c.c_int, _c.c_int, _c.c_int64, _c.c_int64,
         _c.POINTER(_c.c_int)]),
@@ -55,10 +60,10 @@ SYMBOLS = {
     "uniql_hadamard_base_matrix": (_c.c_int, [_c.c_int, _c.c_void_p]),
     "uniql_w4a16_gather_columns": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p,
-        _c.c_void_p, _c.c_int64, _c.c_void_p]),
+        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p]),
     "uniql_w4a16_dequantize_rows": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p,
-        _c.c_int64, _c.c_void_p]),
+        _c.c_int64, _c.c_void_p, _c.c_void_p]),
     "uniql_w4a16_quantize": (_c.c_int, [
         _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
         _c.c_int64, _c.c_void_p]),

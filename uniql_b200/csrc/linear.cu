@@ -59,8 +59,8 @@ static int check_proj(const uniql_w4a16_proj& q, int64_t k) {
 
 static int group_launch(const CommView* cv, int64_t k_offset, const void* A, int64_t lda, int64_t m, int64_t k,
                         const uniql_w4a16_proj* proj, int nproj, int epilogue, const void* residual, int64_t ldr,
-                        int64_t hadamard_dim, void* scratch, size_t scratch_bytes, int* status_word,
-                        cudaStream_t stream) {
+                        int64_t hadamard_dim, const uniql_prefetch* next, int nnext, void* scratch,
+                        size_t scratch_bytes, int* status_word, cudaStream_t stream) {
   if (!proj || nproj < 1 || nproj > UNIQL_MAX_PROJ || m < 0 || k <= 0) return UNIQL_EINVAL;
   if (m > 16 || k % 128 != 0) return UNIQL_ESHAPE;
   if (epilogue != UNIQL_EPILOGUE_NONE && epilogue != UNIQL_EPILOGUE_SWIGLU) return UNIQL_EINVAL;
@@ -100,6 +100,14 @@ static int group_launch(const CommView* cv, int64_t k_offset, const void* A, int
   a.scratch = scratch; a.scratch_bytes = scratch_bytes;
   a.status_word = status_word;
   a.comm = cv;
+  a.nprefetch = 0;
+  if (next)
+    for (int i = 0; i < nnext && a.nprefetch < UNIQL_MAX_PREFETCH; ++i)
+      if (next[i].ptr && next[i].bytes) {
+        a.prefetch_ptr[a.nprefetch] = next[i].ptr;
+        a.prefetch_bytes[a.nprefetch] = next[i].bytes;
+        ++a.nprefetch;
+      }
   return launch_decode(a, stream);
 }
 
@@ -147,8 +155,8 @@ extern "C" int uniql_w4a16_linear(const void* A, int64_t lda, const void* B, con
   uniql_w4a16_proj q;
   q.B = B; q.s = s; q.bias = bias; q.D = D; q.ldd = ldd; q.n = n; q.n_out = n_out;
   if (m <= 16)
-    return group_launch(nullptr, 0, A, lda, m, k, &q, 1, UNIQL_EPILOGUE_NONE, nullptr, 0, hadamard_dim, scratch,
-                        scratch_bytes, status_word, stream);
+    return group_launch(nullptr, 0, A, lda, m, k, &q, 1, UNIQL_EPILOGUE_NONE, nullptr, 0, hadamard_dim, nullptr, 0,
+                        scratch, scratch_bytes, status_word, stream);
 
   // m > 16: Hadamard (if any) as its own kernel into scratch, then the tensor-core kernels
   const __half* Ain = (const __half*)A;
@@ -173,8 +181,8 @@ extern "C" int uniql_w4a16_linear(const void* A, int64_t lda, const void* B, con
   for (int64_t m0 = 0; m0 < m; m0 += 16) {
     const int64_t mc = m - m0 < 16 ? m - m0 : 16;
     q.D = (__half*)D + m0 * ldd;
-    int st = group_launch(nullptr, 0, Ain + m0 * lda, lda, mc, k, &q, 1, UNIQL_EPILOGUE_NONE, nullptr, 0, 0, scratch,
-                          slab_bytes, status_word, stream);
+    int st = group_launch(nullptr, 0, Ain + m0 * lda, lda, mc, k, &q, 1, UNIQL_EPILOGUE_NONE, nullptr, 0, 0, nullptr, 0,
+                          scratch, slab_bytes, status_word, stream);
     if (st != UNIQL_OK) return st;
   }
   return UNIQL_OK;
@@ -182,16 +190,17 @@ extern "C" int uniql_w4a16_linear(const void* A, int64_t lda, const void* B, con
 
 extern "C" int uniql_w4a16_linear_group(const void* A, int64_t lda, int64_t m, int64_t k,
                                         const uniql_w4a16_proj* proj, int nproj, int epilogue, const void* residual,
-                                        int64_t ldr, int64_t hadamard_dim, void* scratch, size_t scratch_bytes,
-                                        int* status_word, void* stream) {
-  return uniql::group_launch(nullptr, 0, A, lda, m, k, proj, nproj, epilogue, residual, ldr, hadamard_dim, scratch,
-                             scratch_bytes, status_word, (cudaStream_t)stream);
+                                        int64_t ldr, int64_t hadamard_dim, const uniql_prefetch* next, int nnext,
+                                        void* scratch, size_t scratch_bytes, int* status_word, void* stream) {
+  return uniql::group_launch(nullptr, 0, A, lda, m, k, proj, nproj, epilogue, residual, ldr, hadamard_dim, next, nnext,
+                             scratch, scratch_bytes, status_word, (cudaStream_t)stream);
 }
 
 extern "C" int uniql_w4a16_linear_group_tp(void* comm, int flags, int64_t col_offset, int64_t k_offset, const void* A,
                                            int64_t lda, int64_t m, int64_t k, const uniql_w4a16_proj* proj, int nproj,
                                            int epilogue, const void* residual, int64_t ldr, int64_t hadamard_dim,
-                                           void* scratch, size_t scratch_bytes, int* status_word, void* stream) {
+                                           const uniql_prefetch* next, int nnext, void* scratch,
+                                           size_t scratch_bytes, int* status_word, void* stream) {
   using namespace uniql;
   if (!comm || (flags & ~(UNIQL_TP_REDUCE | UNIQL_TP_GATHER_OUT | UNIQL_TP_GATHER_IN))) return UNIQL_EINVAL;
   if ((flags & UNIQL_TP_REDUCE) && (flags & UNIQL_TP_GATHER_OUT)) return UNIQL_EINVAL;
@@ -204,8 +213,8 @@ extern "C" int uniql_w4a16_linear_group_tp(void* comm, int flags, int64_t col_of
   cv.gather_out = (flags & UNIQL_TP_GATHER_OUT) ? 1 : 0;
   cv.gather_in = (flags & UNIQL_TP_GATHER_IN) ? 1 : 0;
   cv.col_offset = col_offset;
-  return group_launch(&cv, k_offset, A, lda, m, k, proj, nproj, epilogue, residual, ldr, hadamard_dim, scratch,
-                      scratch_bytes, status_word, (cudaStream_t)stream);
+  return group_launch(&cv, k_offset, A, lda, m, k, proj, nproj, epilogue, residual, ldr, hadamard_dim, next, nnext,
+                      scratch, scratch_bytes, status_word, (cudaStream_t)stream);
 }
 
 extern "C" int uniql_w4a16_linear_allreduce(void* comm, const void* A, int64_t lda, const void* B, const void* s,
@@ -217,7 +226,7 @@ extern "C" int uniql_w4a16_linear_allreduce(void* comm, const void* A, int64_t l
   uniql_w4a16_proj q;
   q.B = B; q.s = s; q.bias = bias; q.D = D; q.ldd = ldd; q.n = n; q.n_out = n_out;
   return uniql_w4a16_linear_group_tp(comm, UNIQL_TP_REDUCE, 0, 0, A, lda, m, k, &q, 1, UNIQL_EPILOGUE_NONE, nullptr, 0,
-                                     0, scratch, scratch_bytes, status_word, stream);
+                                     0, nullptr, 0, scratch, scratch_bytes, status_word, stream);
 }
 
 extern "C" int uniql_abi_version(void) { return UNIQL_ABI_VERSION; }

@@ -53,6 +53,9 @@ struct DecodeArgs {
   size_t scratch_bytes;
   int* status_word;
   const CommView* comm;       // nullptr: single GPU
+  int nprefetch;              // byte ranges to pull into L2 as the launch ends (weights of the launches that follow)
+  const void* prefetch_ptr[4];
+  size_t prefetch_bytes[4];
 };
 
 // m <= 16.  Scratch bytes the launch needs (tickets included).

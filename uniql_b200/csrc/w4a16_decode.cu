@@ -19,9 +19,9 @@
 // block = 4 KB of packed weights.  A launch is one CTA per SM; the T slots of all projections of the launch are
 // laid out in one fixed order and warp w of the W = SMs x warps takes slots [T w / W, T (w+1) / W): every SM streams
 // the same number of bytes (to within one slot) whatever the matrix shape.  Each warp owns a two-slot ring; one
-// elected lane fills a slot with one 2-D TMA tile (weights) while all lanes fetch the group's 64 scales and the
-// m x 128 activations with 16-byte asynchronous copies, everything landing on the slot's mbarrier (bounded wait,
-// status bit on give-up).
+// elected lane fills a slot with one 2-D TMA tile (weights, landing on the slot's mbarrier: bounded wait, status bit
+// on give-up) while all lanes fetch the group's 64 scales and the m x 128 activations with 16-byte asynchronous
+// copies (one commit group per slot).
 // A run of slots of one block ends in a 64 x m fp32 tile that goes to scratch; a ticket counts the slots that have
 // arrived for the block and the warp that brings the last one adds the tiles up in a fixed order (no spinning, no
 // floating-point atomics: same bits on every run) and applies the epilogue: bias, SwiGLU product of a gate/up pair,
@@ -43,6 +43,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -53,7 +54,125 @@ constexpr int kXRowBytes = 272;        // one batch row of one group: 256 bytes 
 constexpr int kMaxSeg = 3;             // Hadamard segments a CTA may need in the fused prologue
 constexpr int kSegRowBytes = 2048;     // room per (segment, batch row) in the prologue: 512 floats
 constexpr int kSegRowStride = 1040;    // bytes between batch rows of a transformed segment (1024 + 16)
+constexpr int kMaxPrefetch = 4;
 constexpr int kSpinLimit = 1 << 22;    // polls of a word another GPU has to write before giving up
+
+// ------------------------------------------------------------------------------------------------ index arithmetic
+// Every divisor of the slot arithmetic is a constant of the launch, so divisions are multiplications by a reciprocal
+// prepared on the host (an emulated 64-bit division costs ~100 instructions, and a warp does several of them on its
+// critical path: range, first slot, tile index).  q = (((n - t) >> 1) + t) >> shift with t = mulhi(magic, n) is exact
+// for every 64-bit n (Granlund-Montgomery, round-up variant); powers of two have magic = 0.
+struct FastDiv {
+  unsigned long long magic;
+  int shift;       // -1: divisor 1
+  int pad;
+};
+__host__ __device__ inline unsigned long long mulhi_u64(unsigned long long a, unsigned long long b) {
+#ifdef __CUDA_ARCH__
+  return __umul64hi(a, b);
+#else
+  return (unsigned long long)(((unsigned __int128)a * b) >> 64);
+#endif
+}
+__host__ __device__ inline unsigned long long fdiv(unsigned long long n, const FastDiv& d) {
+  if (d.shift < 0) return n;
+  const unsigned long long t = mulhi_u64(d.magic, n);
+  return (((n - t) >> 1) + t) >> d.shift;
+}
+static FastDiv make_fastdiv(unsigned long long d) {
+  FastDiv f{0, -1, 0};
+  if (d <= 1) return f;
+  int l = 63;
+  while (!((d >> l) & 1ull)) --l;                       // floor(log2 d)
+  if ((d & (d - 1)) == 0) { f.magic = 0; f.shift = l - 1; return f; }
+  const unsigned __int128 num = (unsigned __int128)(1ull << l) << 64;
+  unsigned long long m = (unsigned long long)(num / d);
+  const unsigned long long rem = (unsigned long long)(num % d);
+  m += m;
+  const unsigned long long twice = rem + rem;
+  if (twice >= d || twice < rem) m += 1;
+  f.magic = m + 1;
+  f.shift = l;
+  return f;
+}
+
+// Constants of the slot order, shared by the kernel, the host plan and the host replay.
+struct SlotGeom {
+  long long T;                    // slots of the launch
+  int W, vbT, NG, kc, koff, nchunks, Pc;
+  FastDiv dT, dW, dNG, dvbT, dkc;
+};
+
+// Slots are ordered chunk by chunk, inside a chunk block by block, inside a block by group.  Without a Hadamard
+// prologue there is one chunk (kc = NG): block-major order, the warps that share a block are neighbours.  With it a
+// chunk is one Hadamard segment, so that a CTA's slots touch at most kMaxSeg segments of the transformed row.
+struct SlotIt {
+  int c, vb, g, g_lo, g_hi;
+};
+__host__ __device__ inline int chunk_lo(int c, int kc, int koff) { const int v = c * kc - koff; return v < 0 ? 0 : v; }
+__host__ __device__ inline int chunk_hi(int c, int kc, int koff, int NG) {
+  const int v = (c + 1) * kc - koff;
+  return v > NG ? NG : v;
+}
+// first slot of warp w
+__host__ __device__ inline long long warp_begin(const SlotGeom& G, int w) { return (long long)fdiv((unsigned long long)G.T * w, G.dW); }
+__host__ __device__ inline SlotIt slot_decode(const SlotGeom& G, long long s) {
+  SlotIt it;
+  const int q = (int)fdiv((unsigned long long)s, G.dvbT);
+  it.c = (int)fdiv((unsigned long long)(q + G.koff), G.dkc);
+  it.g_lo = chunk_lo(it.c, G.kc, G.koff);
+  it.g_hi = chunk_hi(it.c, G.kc, G.koff, G.NG);
+  const int w = it.g_hi - it.g_lo;
+  const int rem = (int)(s - (long long)G.vbT * it.g_lo);
+  it.vb = rem / w;                                      // w <= kc is small and varies at the row's edges: plain division
+  it.g = it.g_lo + (rem - it.vb * w);
+  return it;
+}
+// CH = false: a single chunk, so c, g_lo and g_hi are constants and cost no registers
+template <bool CH>
+__host__ __device__ __forceinline__ SlotIt slot_at(const SlotGeom& G, long long s) {
+  if (CH) return slot_decode(G, s);
+  SlotIt it;
+  it.c = 0; it.g_lo = 0; it.g_hi = G.NG;
+  it.vb = (int)fdiv((unsigned long long)s, G.dNG);
+  it.g = (int)(s - (long long)it.vb * G.NG);
+  return it;
+}
+template <bool CH>
+__host__ __device__ __forceinline__ void slot_next(const SlotGeom& G, SlotIt& it) {
+  if (!CH) {
+    if (++it.g == G.NG) { it.g = 0; ++it.vb; }
+    return;
+  }
+  if (++it.g == it.g_hi) {
+    it.g = it.g_lo;
+    if (++it.vb == G.vbT) {
+      it.vb = 0;
+      ++it.c;
+      it.g_lo = it.g_hi;
+      it.g_hi = it.g_hi + G.kc > G.NG ? G.NG : it.g_hi + G.kc;
+      it.g = it.g_lo;
+    }
+  }
+}
+// warp that owns slot s: the largest w with T w / W <= s
+__host__ __device__ inline int warp_of_slot(const SlotGeom& G, long long s) {
+  return (int)fdiv((unsigned long long)(s + 1) * G.W - 1, G.dT);
+}
+// Number of tiles block vb receives inside chunk [g_lo, g_hi): the warps whose slot ranges touch it.  With fewer slots
+// than warps every busy warp holds exactly one slot (and idle warps sit between them), so each slot is its own tile.
+__host__ __device__ inline int runs_of(const SlotGeom& G, int vb, int g_lo, int g_hi) {
+  const int w = g_hi - g_lo;
+  if (G.T < G.W) return w;
+  const long long first = (long long)G.vbT * g_lo + (long long)vb * w;
+  return warp_of_slot(G, first + w - 1) - warp_of_slot(G, first) + 1;
+}
+// Index of a run among the tiles of its block and chunk: `first` is the first slot of the block inside the chunk,
+// `run_first` the first slot of the run, wg the warp that holds it.
+__host__ __device__ inline int run_index(const SlotGeom& G, long long first, long long run_first, int wg) {
+  if (G.T < G.W) return (int)(run_first - first);
+  return wg - warp_of_slot(G, first);
+}
 
 struct DecodeProj {
   const __half* S;
@@ -71,88 +190,23 @@ struct DecodeParams {
   long long lda;
   const __half* residual;
   long long ldr;
-  float* partials;
-  int* tickets;
+  uint2* partials;                // partial tiles as tagged words {fp32 bits, tag}: [block][chunk][Pc][M][64]
+  uint32_t tag;                   // tag of this launch's words (never 0: consumed words are cleared to 0)
   int* status_word;
-  long long T;                    // slots of the launch
-  int M, NG, nproj, vbT, W, epilogue;
-  int kc, koff, nchunks, Pc;      // k is cut into chunks of kc groups (chunk c = local groups [c kc - koff, ...))
+  SlotGeom G;                     // T slots over W warps; k cut into chunks of kc groups (chunk c = local groups
+                                  // [c kc - koff, (c+1) kc - koff)); Pc tiles reserved per block and chunk
+  int M, nproj, epilogue;
   int xbytes;                     // bytes of staged activations per ring slot
   int had;                        // 1: the activations are H a / sqrt(dim), formed by each CTA for the chunks it streams
   int hP, hlogP, hlogQ, hMdim;    // dim = base * Q * P, P <= 512 the segment length, Mdim = base * Q segments
   int seg0;                       // global segment index of chunk 0
   float hscale;
   unsigned long long hsign[40];   // base matrix: bit a' of hsign[a] set <=> H[a][a'] = -1
+  const unsigned char* pf_ptr[kMaxPrefetch];   // byte ranges to pull into L2 when this launch's own stream ends
+  long long pf_lines[kMaxPrefetch];            // (the weights of the launches that follow), in 128-byte lines
+  int npf;
   CommView cv;
 };
-
-// ------------------------------------------------------------------------------------------------ slot order
-// Slots are ordered chunk by chunk, inside a chunk block by block, inside a block by group.  Without a Hadamard
-// prologue there is one chunk (kc = NG): block-major order, the warps that share a block are neighbours.  With it a
-// chunk is one Hadamard segment, so that a CTA's slots touch at most kMaxSeg segments of the transformed row.
-struct SlotIt {
-  int c, vb, g, g_lo, g_hi;
-};
-__host__ __device__ inline int chunk_lo(int c, int kc, int koff) { const int v = c * kc - koff; return v < 0 ? 0 : v; }
-__host__ __device__ inline int chunk_hi(int c, int kc, int koff, int NG) {
-  const int v = (c + 1) * kc - koff;
-  return v > NG ? NG : v;
-}
-__host__ __device__ inline SlotIt slot_decode(long long s, int vbT, int NG, int kc, int koff) {
-  SlotIt it;
-  const int q = (int)(s / vbT);
-  it.c = (q + koff) / kc;
-  it.g_lo = chunk_lo(it.c, kc, koff);
-  it.g_hi = chunk_hi(it.c, kc, koff, NG);
-  const int w = it.g_hi - it.g_lo;
-  const int rem = (int)(s - (long long)vbT * it.g_lo);
-  it.vb = rem / w;
-  it.g = it.g_lo + (rem - it.vb * w);
-  return it;
-}
-// CH = false: a single chunk, so c, g_lo and g_hi are constants and cost no registers
-template <bool CH>
-__host__ __device__ __forceinline__ SlotIt slot_at(long long s, int vbT, int NG, int kc, int koff) {
-  if (CH) return slot_decode(s, vbT, NG, kc, koff);
-  SlotIt it;
-  it.c = 0; it.g_lo = 0; it.g_hi = NG;
-  it.vb = (int)(s / NG);
-  it.g = (int)(s - (long long)it.vb * NG);
-  return it;
-}
-template <bool CH>
-__host__ __device__ __forceinline__ void slot_next(SlotIt& it, int vbT, int NG, int kc) {
-  if (!CH) {
-    if (++it.g == NG) { it.g = 0; ++it.vb; }
-    return;
-  }
-  if (++it.g == it.g_hi) {
-    it.g = it.g_lo;
-    if (++it.vb == vbT) {
-      it.vb = 0;
-      ++it.c;
-      it.g_lo = it.g_hi;
-      it.g_hi = it.g_hi + kc > NG ? NG : it.g_hi + kc;
-      it.g = it.g_lo;
-    }
-  }
-}
-// warp that owns slot s: the largest w with T w / W <= s
-__host__ __device__ inline int warp_of_slot(long long s, long long T, int W) { return (int)(((s + 1) * W - 1) / T); }
-// Number of tiles block vb receives inside chunk [g_lo, g_hi): the warps whose slot ranges touch it.  With fewer slots
-// than warps every busy warp holds exactly one slot (and idle warps sit between them), so each slot is its own tile.
-__host__ __device__ inline int runs_of(int vb, int g_lo, int g_hi, int vbT, long long T, int W) {
-  const int w = g_hi - g_lo;
-  if (T < W) return w;
-  const long long first = (long long)vbT * g_lo + (long long)vb * w;
-  return warp_of_slot(first + w - 1, T, W) - warp_of_slot(first, T, W) + 1;
-}
-// Index of a run among the tiles of its block and chunk: `first` is the first slot of the block inside the chunk,
-// `run_first` the first slot of the run, wg the warp that holds it.
-__host__ __device__ inline int run_index(long long first, long long run_first, int wg, long long T, int W) {
-  if (T < W) return (int)(run_first - first);
-  return wg - warp_of_slot(first, T, W);
-}
 
 // ------------------------------------------------------------------------------------------------ device helpers
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
@@ -161,14 +215,33 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
       ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol)
       : "memory");
 }
-// Per-thread 16-byte asynchronous copy global -> shared (no copy-engine request, no registers held) ...
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint64_t pol) {
-  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(pol) : "memory");
+// Per-thread 16-byte asynchronous copy global -> shared (no copy-engine request, no registers held).  The copies of one
+// ring slot form one commit group; a slot is consumed after cp.async.wait_group has retired its group.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-// ... and one arrival on the slot's mbarrier once every copy this thread has issued so far has landed
-__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+// Predicated forms: one instruction under a predicate instead of a divergent branch around it (the source address is
+// not touched when the predicate is false).
+__device__ __forceinline__ void cp_async16_if(bool pred, uint32_t dst, const void* src) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %0, 0;\n\t@p cp.async.cg.shared.global [%1], [%2], 16;\n\t}"
+      ::"r"((int)pred), "r"(dst), "l"(src)
+      : "memory");
 }
+// Lane `pred` arms the slot's barrier with the tile's byte count and issues the 2-D TMA tile (no multicast).
+__device__ __forceinline__ void tma_slot_if(bool pred, uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar,
+                                            uint64_t pol) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %0, 0;\n\t"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%5], 4096;\n\t"
+      "@p cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%1], [%2, {%3, %4}], [%5], %6;\n\t}"
+      ::"r"((int)pred), "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -181,6 +254,25 @@ __device__ __forceinline__ uint2 ld_word_sys(const uint2* p) {
   uint2 v;
   asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
+}
+// A partial sum travels between warps as an 8-byte word {fp32 bits, tag}: one store, one load, and the tag says whether
+// the value of THIS launch has arrived -- no fence and no counter between producer and consumer.
+template <int BYTE_OFF>
+__device__ __forceinline__ void st_tagged(uint2* p, float v, uint32_t tag) {
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0 + %3], {%1, %2};"
+               ::"l"(p), "r"(__float_as_uint(v)), "r"(tag), "n"(BYTE_OFF)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_tagged2(const uint2* p) {   // two adjacent words
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void clear_tagged2(uint2* p) {
+  asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1, %1, %1, %1};" ::"l"(p), "r"(0u) : "memory");
 }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
@@ -202,8 +294,8 @@ __device__ __forceinline__ void proj_of_block(const DecodeParams& p, int vb, int
 // with the constant weights (1032 | 72):  sum (off + q) x - sum (off + 8) x = sum (q - 8) x.
 template <int MT>
 __device__ __forceinline__ void decode_group(uint32_t wslot, uint32_t xl, uint32_t xts, float (&accg)[MT][4][4],
-                                             float (&corr)[MT][4]) {
-  const uint32_t kcorr[4] = {0x64086408u, 0x64086408u, 0x54805480u, 0x54805480u};   // 1032, 1032, 72, 72
+                                             float (&corr)[MT][4], uint32_t kc_lo, uint32_t kc_hi) {
+  const uint32_t kcorr[4] = {kc_lo, kc_lo, kc_hi, kc_hi};   // halves 1032, 1032, 72, 72
 #pragma unroll
   for (int u = 0; u < 8; ++u) {
     const uint4 w4 = lds128(wslot + u * 512);
@@ -233,6 +325,19 @@ __device__ __forceinline__ void decode_group(uint32_t wslot, uint32_t xl, uint32
         else mma_m16n8k16(accg[t][j], a, b0[t], b1[t]);
       }
     }
+  }
+}
+
+// Stores a warp's accumulators as tagged words and clears them.  `lane_tile` points at (row 2c, column g) of the tile.
+template <int MT, int T = 0, int J = 0, int R = 0>
+__device__ __forceinline__ void flush_tile(uint2* lane_tile, float (&acc)[MT][4][4], int row0, int M, uint32_t tag) {
+  if constexpr (T < MT) {
+    constexpr int kOff = ((8 * T + (R & 1)) * 64 + 16 * J + 8 * (R >> 1)) * 8;
+    if (row0 + 8 * T + (R & 1) < M) st_tagged<kOff>(lane_tile, acc[T][J][R], tag);
+    acc[T][J][R] = 0.f;
+    if constexpr (R < 3) flush_tile<MT, T, J, R + 1>(lane_tile, acc, row0, M, tag);
+    else if constexpr (J < 3) flush_tile<MT, T, J + 1, 0>(lane_tile, acc, row0, M, tag);
+    else flush_tile<MT, T + 1, 0, 0>(lane_tile, acc, row0, M, tag);
   }
 }
 
@@ -280,11 +385,13 @@ __device__ __forceinline__ void store_pair(const DecodeParams& p, const DecodePr
   }
 }
 
-// All slots of a block (or of a gate/up pair of blocks) have arrived: the calling warp adds the tiles up in a fixed
-// order and finishes the 64 columns, two per lane.  Returns false if a wait on another GPU's words gave up.
-__device__ __noinline__ bool finish_block(const DecodeParams& p, int unit, int lane) {
+// Finishes one block (or one gate/up pair of blocks): the calling warp -- the one that streamed the block's last slot --
+// waits for the tiles of all the warps that worked on it (words tagged with this launch's tag, bounded poll), adds
+// them up in a fixed order and finishes the 64 columns, two per lane.  Consumed words are cleared to tag 0 for the
+// launches to come.  Returns false if a wait gave up.
+__device__ __forceinline__ bool finish_block(const DecodeParams& p, int unit, int lane) {
   const bool swiglu = p.epilogue == UNIQL_EPILOGUE_SWIGLU;
-  const size_t tile_elems = (size_t)p.M * 64;
+  const size_t tile_elems = (size_t)p.M * 64;   // words per tile
   bool ok = true;
   int pi, lb;
   proj_of_block(p, swiglu ? 2 * unit : unit, pi, lb);
@@ -298,11 +405,11 @@ __device__ __noinline__ bool finish_block(const DecodeParams& p, int unit, int l
     for (int q = 0; q < 3; ++q) {
       const int cc = lane + 32 * q;
       pc[wh][q] = 0;
-      if ((wh == 0 || swiglu) && cc < p.nchunks)
-        pc[wh][q] = runs_of(swiglu ? 2 * unit + wh : unit, chunk_lo(cc, p.kc, p.koff), chunk_hi(cc, p.kc, p.koff, p.NG),
-                            p.vbT, p.T, p.W);
+      if ((wh == 0 || swiglu) && cc < p.G.nchunks)
+        pc[wh][q] = runs_of(p.G, swiglu ? 2 * unit + wh : unit, chunk_lo(cc, p.G.kc, p.G.koff),
+                            chunk_hi(cc, p.G.kc, p.G.koff, p.G.NG));
     }
-  const int total = p.nchunks * p.Pc;
+  const int total = p.G.nchunks * p.G.Pc;
   uint32_t repoch = 0, gepoch = 0;
   if (p.cv.reduce)
     repoch = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_epoch_off + 4 * (size_t)unit) + 1;
@@ -315,20 +422,40 @@ __device__ __noinline__ bool finish_block(const DecodeParams& p, int unit, int l
       v[wh] = make_float2(0.f, 0.f);
       if (wh == 1 && !swiglu) continue;
       const int vb = swiglu ? 2 * unit + wh : unit;
-      const float* base = p.partials + (size_t)vb * p.nchunks * p.Pc * tile_elems + (size_t)m * 64 + 2 * lane;
-      for (int i0 = 0; i0 < total; i0 += 16) {      // up to 16 independent L2 loads in flight, summed in order
-        float2 t8[16];
+      uint2* base = p.partials + (size_t)vb * p.G.nchunks * p.G.Pc * tile_elems + (size_t)m * 64 + 2 * lane;
+      // tiles in (chunk, run) order, up to 8 independent 16-byte loads in flight, summed in that order; (cc, jj) walk
+      // the reserved places of the block and `runs` says how many of a chunk's places hold a tile
+      int cc = 0, jj = 0;
+      int runs = __shfl_sync(0xffffffffu, pc[wh][0], 0);
+      for (int i0 = 0; i0 < total; i0 += 8) {
+        uint4 t8[8];
+        uint32_t use = 0;
 #pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          const int idx = i0 + q;
-          const int cc = idx / p.Pc, jj = idx - cc * p.Pc;
-          const int src = cc < 32 ? pc[wh][0] : cc < 64 ? pc[wh][1] : pc[wh][2];
-          const int runs = __shfl_sync(0xffffffffu, src, cc & 31);
-          t8[q] = (idx < total && jj < runs) ? __ldcg(reinterpret_cast<const float2*>(base + (size_t)idx * tile_elems))
-                                             : make_float2(0.f, 0.f);
+        for (int q = 0; q < 8; ++q) {
+          if ((i0 + q < total) && (jj < runs)) {
+            use |= 1u << q;
+            t8[q] = ld_tagged2(base + (size_t)(i0 + q) * tile_elems);
+          }
+          if (++jj == p.G.Pc) {
+            jj = 0;
+            ++cc;
+            const int src = cc < 32 ? pc[wh][0] : cc < 64 ? pc[wh][1] : pc[wh][2];
+            runs = __shfl_sync(0xffffffffu, src, cc & 31);
+          }
         }
 #pragma unroll
-        for (int q = 0; q < 16; ++q) { v[wh].x += t8[q].x; v[wh].y += t8[q].y; }
+        for (int q = 0; q < 8; ++q)
+          if ((use >> q) & 1u) {
+            uint2* src = base + (size_t)(i0 + q) * tile_elems;
+            int spin = 0;
+            while ((t8[q].y != p.tag || t8[q].w != p.tag) && ok) {
+              if (++spin > kSpinLimit) { ok = false; break; }
+              t8[q] = ld_tagged2(src);
+            }
+            v[wh].x += __uint_as_float(t8[q].x);
+            v[wh].y += __uint_as_float(t8[q].z);
+            clear_tagged2(src);
+          }
       }
     }
     const int n0 = lb * 64 + 2 * lane;
@@ -407,55 +534,73 @@ __device__ __noinline__ bool hadamard_prologue(const DecodeParams& p, uint8_t* a
     feat = reinterpret_cast<const uint2*>(p.cv.bufs[p.cv.rank] + p.cv.gather_off) +
            (size_t)(in_epoch & 1u) * 16 * (size_t)(p.cv.feat_cap >> 1);
   }
-  // z[seg][row][b] = sum_a' sign(seg, a') a[row][a' P + b]: a thread owns two adjacent b of one row
-  for (int item = tid; item < p.M * half_p; item += nthreads) {
+  // z[seg][row][b] = sum_a' sign(seg, a') a[row][a' P + b]: a thread owns two adjacent b of one row and, when there
+  // are threads to spare (one batch row), every `nsplit`-th source segment; the split sums meet in shared memory
+  const int nitems = p.M * half_p;
+  const int nsplit = (p.M == 1 && 2 * nitems <= nthreads) ? 2 : 1;
+  for (int it0 = tid; it0 < nitems * nsplit; it0 += nthreads) {
+    const int split = it0 >= nitems ? 1 : 0;
+    const int item = it0 - split * nitems;
     const int row = item >> (p.hlogP - 1), cp = item & (half_p - 1);
     float2 z[kMaxSeg];
 #pragma unroll
     for (int s = 0; s < kMaxSeg; ++s) z[s] = make_float2(0.f, 0.f);
-    for (int a0 = 0; a0 < p.hMdim; a0 += 8) {
-      uint32_t hv[8];
+    constexpr int NB = 16;                   // source segments fetched per round trip
+    for (int a0 = split; a0 < p.hMdim; a0 += NB * nsplit) {
+      uint32_t hv[NB];
       if (!FEAT) {
         const uint32_t* src = reinterpret_cast<const uint32_t*>(p.A + (size_t)row * p.lda) + cp;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (a0 + i < p.hMdim) hv[i] = __ldcg(src + (size_t)(a0 + i) * half_p);
+        for (int i = 0; i < NB; ++i)
+          if (a0 + i * nsplit < p.hMdim) hv[i] = __ldcg(src + (size_t)(a0 + i * nsplit) * half_p);
       } else {
         const uint2* src = feat + (size_t)row * (size_t)(p.cv.feat_cap >> 1) + cp;
-        uint2 wv[8];
+        uint2 wv[NB];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (a0 + i < p.hMdim) wv[i] = ld_word_sys(src + (size_t)(a0 + i) * half_p);
+        for (int i = 0; i < NB; ++i)
+          if (a0 + i * nsplit < p.hMdim) wv[i] = ld_word_sys(src + (size_t)(a0 + i * nsplit) * half_p);
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (a0 + i < p.hMdim) {
+        for (int i = 0; i < NB; ++i)
+          if (a0 + i * nsplit < p.hMdim) {
             int spin = 0;
             while (wv[i].y != in_epoch && ok) {
               if (++spin > kSpinLimit) { ok = false; break; }
-              wv[i] = ld_word_sys(src + (size_t)(a0 + i) * half_p);
+              wv[i] = ld_word_sys(src + (size_t)(a0 + i * nsplit) * half_p);
             }
             hv[i] = wv[i].x;
           }
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (a0 + i < p.hMdim) {
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hv[i]));
-          const int ap = a0 + i;
+      for (int i = 0; i < NB; ++i)
+        if (a0 + i * nsplit < p.hMdim) {
+          const int ap = a0 + i * nsplit;
+          // flip the sign bits of the two halves where the matrix entry is -1
 #pragma unroll
           for (int s = 0; s < kMaxSeg; ++s)
             if (s < nseg) {
-              const bool neg = (s_mask[s * 3 + (ap >> 5)] >> (ap & 31)) & 1u;
-              z[s].x += neg ? -f.x : f.x;
-              z[s].y += neg ? -f.y : f.y;
+              const uint32_t flip = ((s_mask[s * 3 + (ap >> 5)] >> (ap & 31)) & 1u) * 0x80008000u;
+              const uint32_t hs = hv[i] ^ flip;
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hs));
+              z[s].x += f.x;
+              z[s].y += f.y;
             }
         }
     }
 #pragma unroll
     for (int s = 0; s < kMaxSeg; ++s)
-      if (s < nseg) *reinterpret_cast<float2*>(zbuf + (size_t)(s * p.M + row) * 512 + 2 * cp) = z[s];
+      if (s < nseg) *reinterpret_cast<float2*>(zbuf + (size_t)((split * kMaxSeg + s) * p.M + row) * 512 + 2 * cp) = z[s];
   }
   __syncthreads();
+  if (nsplit == 2) {
+    for (int i = tid; i < nseg * half_p; i += nthreads) {      // one batch row here: (segment, column pair)
+      const int sgi = i >> (p.hlogP - 1), cp = i & (half_p - 1);
+      float2* d = reinterpret_cast<float2*>(zbuf + (size_t)sgi * 512 + 2 * cp);
+      const float2 e = *reinterpret_cast<const float2*>(zbuf + (size_t)(kMaxSeg + sgi) * 512 + 2 * cp);
+      d->x += e.x;
+      d->y += e.y;
+    }
+    __syncthreads();
+  }
   // P-point Walsh-Hadamard transform of every (segment, row) vector, radix 8 / 4 / 2 out of shared memory
   const int ntask = nseg * p.M;
   for (int h = 1; h < P;) {
@@ -490,11 +635,11 @@ __device__ __noinline__ bool hadamard_prologue(const DecodeParams& p, uint8_t* a
   }
   // scale, round to fp16 (as the separate Hadamard module would), repack as rows of kSegRowStride bytes
   uint32_t packed[12];
-  const int nitems = ntask * half_p;
+  const int npack = ntask * half_p;
 #pragma unroll
   for (int i = 0; i < 12; ++i) {
     const int item = tid + i * nthreads;
-    if (item < nitems) {
+    if (item < npack) {
       const int task = item >> (p.hlogP - 1), cp = item & (half_p - 1);
       const float2 f = *reinterpret_cast<const float2*>(zbuf + (size_t)task * 512 + 2 * cp);
       const __half2 hh = __floats2half2_rn(f.x * p.hscale, f.y * p.hscale);
@@ -505,7 +650,7 @@ __device__ __noinline__ bool hadamard_prologue(const DecodeParams& p, uint8_t* a
 #pragma unroll
   for (int i = 0; i < 12; ++i) {
     const int item = tid + i * nthreads;
-    if (item < nitems) {
+    if (item < npack) {
       const int task = item >> (p.hlogP - 1), cp = item & (half_p - 1);
       *reinterpret_cast<uint32_t*>(area + (size_t)task * kSegRowStride + cp * 4) = packed[i];
     }
@@ -513,6 +658,19 @@ __device__ __noinline__ bool hadamard_prologue(const DecodeParams& p, uint8_t* a
   __syncthreads();
   return ok;
 }
+
+#ifdef UNIQL_DECODE_TIMING
+// Development aid (never defined in the shipped build): per-warp timestamps of the phases of one launch.
+__device__ unsigned long long g_decode_stamps[8][4096];
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define STAMP(k) do { if (lane == 0 && wg < 4096) g_decode_stamps[k][wg] = gtime(); } while (0)
+#else
+#define STAMP(k) do { } while (0)
+#endif
 
 template <int MT, int WARPS, int MINB, bool HAD, int kRing>
 __global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __grid_constant__ DecodeParams p) {
@@ -524,7 +682,8 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
   const int wg = blockIdx.x * WARPS + warp;
-  const long long s0 = p.T * wg / p.W, s1 = p.T * (wg + 1) / p.W;
+  STAMP(0);
+  const long long s0 = warp_begin(p.G, wg), s1 = warp_begin(p.G, wg + 1);
   const int nsl = (int)(s1 - s0);
 
   // ---- shared memory: [weights: WARPS x kRing x 4 KB][scales: WARPS x kRing x 128 B][activations] ----
@@ -535,13 +694,12 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __
   const uint32_t xring = xarea + warp * (kRing * p.xbytes);
   const uint32_t bar0 = smem_addr(&s_bars[warp * kRing]);
   const uint64_t pol_w = make_evict_first_policy();
-  const uint64_t pol_x = make_evict_last_policy();
 
   if (lane == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&p.wmap[0]) : "memory");
-    // a slot is complete when its weight tile has landed (one arrival with the byte count, by the issuing lane) and
-    // every lane's asynchronous copies of the group's scales and activations have (32 arrivals)
-    for (int s = 0; s < kRing; ++s) mbar_init(bar0 + s * 8, 33);
+    // the barrier of a slot tracks its weight tile (one arrival with the byte count, by the issuing lane); the lanes'
+    // asynchronous copies of the group's scales and activations are tracked by commit groups
+    for (int s = 0; s < kRing; ++s) mbar_init(bar0 + s * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -549,51 +707,81 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __
 
   // One copy-engine request per slot (the 4 KB weight tile); the 64 scales of the group and the m x 128 activations
   // travel as per-thread 16-byte asynchronous copies: small bulk copies cost the copy engine as much as a tile.
-  auto issue_weights = [&](int slot, const SlotIt& it) {   // all lanes
+  // The issue side keeps its operands as running values: inside a run of slots of one block only the group advances.
+  SlotIt it_issue = slot_at<HAD>(p.G, s0);
+  const CUtensorMap* is_map = &p.wmap[0];
+  int is_x = 0;                              // word coordinate of the block in the packed row
+  const __half* is_sp = p.proj[0].S;         // this lane's 8 scales of the slot to issue (lanes 0..7)
+  long long is_sn = 0;                       // halves between consecutive scale rows
+  auto issue_block = [&]() {                 // operands of the block it_issue points at
     int pi, lb;
-    proj_of_block(p, it.vb, pi, lb);
-    const uint32_t bar = bar0 + slot * 8;
-    if (lane == 0) {
-      mbar_expect_tx(bar, kSlotBytes);
-      tma_load_slot(wring + slot * kSlotBytes, &p.wmap[pi], lb * 128, 8 * it.g, bar, pol_w);
-    }
-    if (lane < 8)
-      cp_async16(sring + slot * kSlotScaleBytes + lane * 16,
-                 p.proj[pi].S + ((size_t)it.g * p.proj[pi].N + (size_t)lb * 64 + lane * 8), pol_w);
+    proj_of_block(p, it_issue.vb, pi, lb);
+    is_map = &p.wmap[pi];
+    is_x = lb * 128;
+    is_sn = p.proj[pi].N;
+    is_sp = p.proj[pi].S + ((size_t)it_issue.g * is_sn + (size_t)lb * 64 + (lane & 7) * 8);
   };
-  auto issue_acts = [&](int slot, int grp) {               // all lanes: 16 chunks of 16 bytes per batch row
-    for (int idx = lane; idx < p.M * 16; idx += 32) {
-      const int row = idx >> 4, ch = idx & 15;
-      cp_async16(xring + slot * p.xbytes + row * kXRowBytes + ch * 16, p.A + (size_t)row * p.lda + (size_t)grp * 128 + ch * 8,
-                 pol_x);
+  // activations: lane l copies chunk l % 16 of batch row l / 16 (+ 2 rows per further pass)
+  const __half* xsrc0 = p.A + (size_t)(lane >> 4) * p.lda + (lane & 15) * 8;
+  const uint32_t xdst0 = xring + (lane >> 4) * kXRowBytes + (lane & 15) * 16;
+  auto issue_weights = [&](int slot) {       // all lanes
+    const uint32_t bar = bar0 + slot * 8;
+    tma_slot_if(lane == 0, wring + slot * kSlotBytes, is_map, is_x, 8 * it_issue.g, bar, pol_w);
+    cp_async16_if(lane < 8, sring + slot * kSlotScaleBytes + lane * 16, is_sp);
+  };
+  auto issue_acts = [&](int slot, int grp) {  // all lanes: 16 chunks of 16 bytes per batch row
+    const __half* src = xsrc0 + (size_t)grp * 128;
+    const uint32_t dst = xdst0 + slot * p.xbytes;
+    cp_async16_if(lane < 16 * p.M, dst, src);
+    for (int r2 = 2; r2 < p.M; r2 += 2)
+      cp_async16_if(lane + 16 * r2 < 16 * p.M, dst + r2 * kXRowBytes, src + (size_t)r2 * p.lda);
+  };
+  auto issue_next = [&]() {                  // advance the issue side by one slot
+    const int vb_before = it_issue.vb;
+    slot_next<HAD>(p.G, it_issue);
+    if (it_issue.vb != vb_before) {
+      if (it_issue.vb < p.G.vbT) issue_block();
+    } else {
+      is_sp += is_sn;
     }
   };
 
+  // When this warp's own stream ends it asks L2 for its share of the weights the following launches will stream:
+  // HBM then stays busy while this launch drains and the next one starts, and the next one finds its first
+  // megabytes in L2.  Plain per-line prefetches (hints: they cost no registers and never fault).
+  auto issue_prefetch = [&]() {
+    const long long nthreads_all = (long long)gridDim.x * (WARPS * 32);
+    const long long gtid = (long long)blockIdx.x * (WARPS * 32) + tid;
+    for (int r = 0; r < p.npf; ++r)
+      for (long long l = gtid; l < p.pf_lines[r]; l += nthreads_all)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.pf_ptr[r] + l * 128));
+  };
+
   // ---- start streaming weights before anything else ----
-  SlotIt it_issue = slot_at<HAD>(s0, p.vbT, p.NG, p.kc, p.koff);
+  if (nsl > 0) issue_block();
   int g_pre[kRing];
 #pragma unroll
   for (int s = 0; s < kRing; ++s) {
     g_pre[s] = it_issue.g;
     if (s < nsl) {
-      issue_weights(s, it_issue);
-      if (HAD) cp_async_arrive(bar0 + s * 8);
-      slot_next<HAD>(it_issue, p.vbT, p.NG, p.kc);
+      issue_weights(s);
+      issue_next();
     }
   }
   // Let the next kernel in the stream start its own weight prefetch, then wait for the producer of the activations.
+  STAMP(1);
   pdl_launch_dependents();
   pdl_wait();
+  STAMP(2);
 
   bool timed_out = false;
   // chunk range of this CTA (Hadamard prologue) -- CTA-uniform
   int c_first = 0;
   if (HAD) {
-    const long long cs0 = p.T * (long long)(blockIdx.x * WARPS) / p.W;
-    const long long cs1 = p.T * (long long)((blockIdx.x + 1) * WARPS) / p.W;
+    const long long cs0 = warp_begin(p.G, blockIdx.x * WARPS), cs1 = warp_begin(p.G, (blockIdx.x + 1) * WARPS);
     if (cs1 > cs0) {
-      c_first = slot_decode(cs0, p.vbT, p.NG, p.kc, p.koff).c;
-      const int c_last = slot_decode(cs1 - 1, p.vbT, p.NG, p.kc, p.koff).c;
+      c_first = slot_decode(p.G, cs0).c;
+      const int c_last = slot_decode(p.G, cs1 - 1).c;
       int nseg = c_last - c_first + 1;
       if (nseg > kMaxSeg) nseg = kMaxSeg;                 // excluded by the host plan
       bool ok;
@@ -601,13 +789,13 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __
       else ok = hadamard_prologue<false>(p, smem_raw + (xarea - smem_base), &s_mask[0][0], c_first, nseg, WARPS * 32);
       if (!ok) timed_out = true;
     }
-  } else {
+  }
+  // one commit group per ring slot, empty ones included: the group of slot i is then always followed by exactly
+  // kRing - 1 younger groups when slot i is consumed (the scales fetched above ride in the first group)
 #pragma unroll
-    for (int s = 0; s < kRing; ++s)
-      if (s < nsl) {
-        issue_acts(s, g_pre[s]);
-        cp_async_arrive(bar0 + s * 8);
-      }
+  for (int s = 0; s < kRing; ++s) {
+    if (!HAD && s < nsl) issue_acts(s, g_pre[s]);
+    cp_async_commit();
   }
 
   // this lane's B-fragment origin: batch row g (tile 0) and 8 + g (tile 1), clamped to a row that exists --
@@ -624,30 +812,41 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int r = 0; r < 4; ++r) acc[t][j][r] = 0.f;
+  // the constant operand of the offset-correction MMA, kept in registers (opaque to the compiler: no re-materialising)
+  uint32_t kc_lo, kc_hi;
+  asm volatile("mov.b32 %0, 0x64086408;" : "=r"(kc_lo));
+  asm volatile("mov.b32 %0, 0x54805480;" : "=r"(kc_hi));
 
-  SlotIt it = slot_at<HAD>(s0, p.vbT, p.NG, p.kc, p.koff);
+  if (nsl == 0) issue_prefetch();
+  SlotIt it = slot_at<HAD>(p.G, s0);
   int run_cnt = 0;
   const size_t tile_elems = (size_t)p.M * 64;
   int slot = 0;
   uint32_t parity = 0;
+  int fin_first = 0, fin_cnt = 0;
   for (int i = 0; i < nsl; ++i) {
+    cp_async_wait<kRing - 1>();          // this lane's copies for slot i have landed ...
+    __syncwarp();                        // ... and so have the other lanes'
     if (!mbar_wait(bar0 + slot * 8, parity)) timed_out = true;
+    if (i == 0) STAMP(3);
+    if (i == nsl - 1) STAMP(4);
     const uint4 sc = lds128(sring + slot * kSlotScaleBytes + 16 * g);
     uint32_t xl;
     if (HAD)
-      xl = xarea + (uint32_t)((it.c - c_first) * p.M) * kSegRowStride + (uint32_t)(it.g + p.koff - it.c * p.kc) * 256u + xl_off;
+      xl = xarea + (uint32_t)((it.c - c_first) * p.M) * kSegRowStride + (uint32_t)(it.g + p.G.koff - it.c * p.G.kc) * 256u + xl_off;
     else
       xl = xring + slot * p.xbytes + xl_off;
     float accg[MT][4][4], corr[MT][4];
-    decode_group<MT>(wring + slot * kSlotBytes + lane * 16, xl, xts, accg, corr);
+    decode_group<MT>(wring + slot * kSlotBytes + lane * 16, xl, xts, accg, corr, kc_lo, kc_hi);
     // the slot has been read by every lane: hand it back to the copy engine
     __syncwarp();
     if (i + kRing < nsl) {
-      issue_weights(slot, it_issue);
+      issue_weights(slot);
       if (!HAD) issue_acts(slot, it_issue.g);
-      cp_async_arrive(bar0 + slot * 8);
-      slot_next<HAD>(it_issue, p.vbT, p.NG, p.kc);
+      issue_next();
     }
+    cp_async_commit();
+    if (i == nsl - 1) issue_prefetch();
     // ---- apply this group's scales: lane holds s[64blk + 8g + 2j + b] for j=0..3, b=0..1 ----
     const __half2* sh = reinterpret_cast<const __half2*>(&sc);
 #pragma unroll
@@ -661,51 +860,49 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __
         acc[t][j][3] = fmaf(accg[t][j][3] - corr[t][3], sf.y, acc[t][j][3]);
       }
     }
+    if (i == nsl - 1) STAMP(5);
     ++run_cnt;
     const bool run_end = (i == nsl - 1) || (it.g + 1 == it.g_hi);
     if (run_end) {
-      // ---- this warp's tile of block it.vb goes to scratch; the ticket counts slots ----
+      // ---- this warp's tile of block it.vb goes to scratch as tagged words ----
       const int wc = it.g_hi - it.g_lo;
-      const long long first = (long long)p.vbT * it.g_lo + (long long)it.vb * wc;
-      const int jrun = run_index(first, s0 + i - (run_cnt - 1), wg, p.T, p.W);
-      float* tile = p.partials + ((size_t)((size_t)it.vb * p.nchunks + it.c) * p.Pc + jrun) * tile_elems;
-#pragma unroll
-      for (int t = 0; t < MT; ++t)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            const int m = 8 * t + 2 * c + (r & 1);
-            if (m < p.M) tile[m * 64 + 16 * j + g + 8 * (r >> 1)] = acc[t][j][r];
-            acc[t][j][r] = 0.f;
-          }
+      const long long first = (long long)p.G.vbT * it.g_lo + (long long)it.vb * wc;
+      const int jrun = run_index(p.G, first, s0 + i - (run_cnt - 1), wg);
+      // this lane's words: batch rows 8t + 2c + (r & 1), columns 16j + g + 8 (r >> 1): one base, constant offsets
+      uint2* tile = p.partials + ((size_t)((size_t)it.vb * p.G.nchunks + it.c) * p.G.Pc + jrun) * tile_elems + (2 * c) * 64 + g;
+      const uint32_t tag = p.tag;
+      flush_tile<MT>(tile, acc, 2 * c, p.M, tag);
+      // The warp that holds the LAST slot of a block (of the up block of a gate/up pair) finishes it: it waits for the
+      // tiles of the warps before it -- always warps of lower index, in CTAs that were dispatched no later than its
+      // own, so the wait cannot deadlock -- adds them up in a fixed order and applies the epilogue.
       const bool swiglu = p.epilogue == UNIQL_EPILOGUE_SWIGLU;
       const int unit = swiglu ? (it.vb >> 1) : it.vb;
-      const int need = swiglu ? 2 * p.NG : p.NG;
-      bool last;
-      if (run_cnt == need) {
-        __syncwarp();                     // the tile was written by this warp alone
-        last = true;
-      } else {
-        __threadfence();
-        __syncwarp();
-        int old = 0;
-        if (lane == 0) {
-          old = atomicAdd(p.tickets + unit, run_cnt);
-          if (old + run_cnt == need) p.tickets[unit] = 0;   // leave the ticket clean for the next launch
-        }
-        old = __shfl_sync(0xffffffffu, old, 0);
-        last = (old + run_cnt == need);
-        if (last) __threadfence();
+      const bool last = (it.g == p.G.NG - 1) && (!swiglu || (it.vb & 1));
+      // Finishing waits for other warps' tiles, so it is put off until this warp has stored all of its own: no warp
+      // ever waits while it still owes a tile to somebody else.  The blocks a warp finishes are consecutive.
+      if (last) {
+        if (fin_cnt == 0) fin_first = unit;
+        ++fin_cnt;
       }
-      if (last && !finish_block(p, unit, lane)) timed_out = true;
+      if (i == nsl - 1) STAMP(6);
       run_cnt = 0;
     }
-    slot_next<HAD>(it, p.vbT, p.NG, p.kc);
+    slot_next<HAD>(p.G, it);
     if (++slot == kRing) { slot = 0; parity ^= 1u; }
   }
+  for (int u = 0; u < fin_cnt; ++u)
+    if (!finish_block(p, fin_first + u, lane)) timed_out = true;
+  STAMP(7);
   if (timed_out && p.status_word) atomicOr(p.status_word, UNIQL_STATUS_WAIT_TIMEOUT);
 }
+
+#ifdef UNIQL_DECODE_TIMING
+}  // namespace uniql
+extern "C" int uniql_debug_read_stamps(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, uniql::g_decode_stamps, sizeof(unsigned long long) * 8 * 4096);
+}
+namespace uniql {
+#endif
 
 // ------------------------------------------------------------------------------------------------ host side
 static int env_int(const char* name, int dflt) {
@@ -771,12 +968,11 @@ static int cached_weight_map(CUtensorMap* out, const void* B, int64_t n, int64_t
 }
 
 struct DecodePlan {
-  int variant;        // 0: 12 warps, m <= 2;  1: 8 warps, m <= 8;  2: 8 warps, two batch tiles (m <= 16);  3: 10 warps, m <= 4;
-                      // 4: 8 warps with three ring slots, m <= 2
+  int variant;        // 0: 16 warps, three ring slots, m <= 2;  1: 16 warps, two slots, m <= 8;
+                      // 2: 12 warps, two batch tiles (m <= 16);  3: 8 warps, two slots, m <= 8 (two launches fit an SM)
   int ring;
-  int warps, grid, W;
-  long long T;
-  int vbT, NG, kc, koff, nchunks, Pc, units;
+  int warps, grid, units;
+  SlotGeom G;
   int fused_had;      // the Hadamard transform runs in the kernel prologue
   int hP, hlogP, hlogQ, hMdim, hbase, seg0;
   int xbytes;
@@ -797,14 +993,13 @@ static int make_plan(DecodePlan* pl, int64_t m, int64_t k, const int64_t* n, int
   DecodePlan P{};
   P.variant = m <= 2 ? 0 : m <= 8 ? 1 : 2;
   static const int force_variant = env_int("UNIQL_B200_DECODE_VARIANT", -1);
-  if (force_variant >= 0 && force_variant <= 4 && !(force_variant == 0 && m > 2) && !(force_variant == 1 && m > 8) &&
-      !(force_variant == 3 && m > 4) && !(force_variant == 4 && m > 2))
-    P.variant = force_variant;
-  P.warps = P.variant == 0 ? 12 : P.variant == 3 ? 10 : 8;
-  P.ring = P.variant == 4 ? 3 : 2;
+  if (force_variant == 3 && m <= 8) P.variant = 3;
+  if (force_variant == 1 && m <= 8) P.variant = 1;
+  P.warps = P.variant == 2 ? 12 : P.variant == 3 ? 8 : 16;
+  P.ring = P.variant == 0 ? 3 : 2;
   P.grid = device_info().sm_count;
-  P.W = P.grid * P.warps;
-  P.NG = (int)(k / 128);
+  P.G.W = P.grid * P.warps;
+  P.G.NG = (int)(k / 128);
   int64_t vb = 0;
   for (int i = 0; i < nproj; ++i) {
     if (n[i] <= 0 || n[i] % 64) return UNIQL_ESHAPE;
@@ -814,9 +1009,15 @@ static int make_plan(DecodePlan* pl, int64_t m, int64_t k, const int64_t* n, int
   if (epilogue != UNIQL_EPILOGUE_NONE && epilogue != UNIQL_EPILOGUE_SWIGLU) return UNIQL_EINVAL;
   P.units = (int)(epilogue == UNIQL_EPILOGUE_SWIGLU ? vb / 2 : vb);
   if ((size_t)P.units * sizeof(int) > UNIQL_SCRATCH_COUNTER_BYTES) return UNIQL_ESHAPE;
-  P.vbT = (int)vb;
-  P.T = (long long)vb * P.NG;
-  P.kc = P.NG; P.koff = 0; P.nchunks = 1;
+  P.G.vbT = (int)vb;
+  P.G.T = (long long)vb * P.G.NG;
+  P.G.kc = P.G.NG; P.G.koff = 0; P.G.nchunks = 1;
+  auto refresh = [&]() {
+    P.G.dT = make_fastdiv((unsigned long long)P.G.T); P.G.dW = make_fastdiv((unsigned long long)P.G.W);
+    P.G.dNG = make_fastdiv((unsigned long long)P.G.NG); P.G.dvbT = make_fastdiv((unsigned long long)P.G.vbT);
+    P.G.dkc = make_fastdiv((unsigned long long)P.G.kc);
+  };
+  refresh();
   P.fused_had = 0;
   if (hadamard_dim) {
     const int base = hadamard_base_of(hadamard_dim);
@@ -828,37 +1029,38 @@ static int make_plan(DecodePlan* pl, int64_t m, int64_t k, const int64_t* n, int
     // the prologue holds one transformed segment per 128-value group or more, batches of at most 4 rows, and a base
     // index that fits the 96-bit sign masks
     if (seg >= 128 && m <= 4 && P.hMdim <= 96 && env_int("UNIQL_B200_FUSED_HADAMARD", 1)) {
-      P.kc = (int)(seg / 128);
+      P.G.kc = (int)(seg / 128);
       const int64_t g0 = k_offset / 128;
-      P.koff = (int)(g0 % P.kc);
-      P.seg0 = (int)(g0 / P.kc);
-      P.nchunks = (P.NG + P.koff + P.kc - 1) / P.kc;
+      P.G.koff = (int)(g0 % P.G.kc);
+      P.seg0 = (int)(g0 / P.G.kc);
+      P.G.nchunks = (P.G.NG + P.G.koff + P.G.kc - 1) / P.G.kc;
+      refresh();
       // every CTA must touch at most kMaxSeg segments
       int worst = 0;
       for (int cta = 0; cta < P.grid; ++cta) {
-        const long long a = P.T * (long long)(cta * P.warps) / P.W, b = P.T * (long long)((cta + 1) * P.warps) / P.W;
+        const long long a = warp_begin(P.G, cta * P.warps), b = warp_begin(P.G, (cta + 1) * P.warps);
         if (b <= a) continue;
-        const int c0 = slot_decode(a, P.vbT, P.NG, P.kc, P.koff).c, c1 = slot_decode(b - 1, P.vbT, P.NG, P.kc, P.koff).c;
+        const int c0 = slot_decode(P.G, a).c, c1 = slot_decode(P.G, b - 1).c;
         if (c1 - c0 + 1 > worst) worst = c1 - c0 + 1;
       }
-      if (worst <= kMaxSeg && P.nchunks <= 96) P.fused_had = 1;
-      else { P.kc = P.NG; P.koff = 0; P.nchunks = 1; }
+      if (worst <= kMaxSeg && P.G.nchunks <= 96) P.fused_had = 1;
+      else { P.G.kc = P.G.NG; P.G.koff = 0; P.G.nchunks = 1; refresh(); }
     }
   }
   // tiles a block can receive per chunk
   int pc = 1;
-  for (int cc = 0; cc < P.nchunks; ++cc) {
-    const int lo = chunk_lo(cc, P.kc, P.koff), hi = chunk_hi(cc, P.kc, P.koff, P.NG);
-    for (int b = 0; b < P.vbT; ++b) {
-      const int r = runs_of(b, lo, hi, P.vbT, P.T, P.W);
+  for (int cc = 0; cc < P.G.nchunks; ++cc) {
+    const int lo = chunk_lo(cc, P.G.kc, P.G.koff), hi = chunk_hi(cc, P.G.kc, P.G.koff, P.G.NG);
+    for (int b = 0; b < P.G.vbT; ++b) {
+      const int r = runs_of(P.G, b, lo, hi);
       if (r > pc) pc = r;
     }
   }
-  P.Pc = pc;
-  P.partial_bytes = (size_t)P.vbT * P.nchunks * P.Pc * (size_t)m * 64 * sizeof(float);
+  P.G.Pc = pc;
+  P.partial_bytes = (size_t)P.G.vbT * P.G.nchunks * P.G.Pc * (size_t)m * 64 * sizeof(uint2);
   P.xbytes = P.fused_had ? 0 : (int)m * kXRowBytes;
   const size_t rings = (size_t)P.warps * P.ring * (kSlotBytes + kSlotScaleBytes);
-  const size_t xs = P.fused_had ? (size_t)kMaxSeg * m * kSegRowBytes : (size_t)P.warps * P.ring * P.xbytes;
+  const size_t xs = P.fused_had ? (size_t)kMaxSeg * m * kSegRowBytes * (m == 1 ? 2 : 1) : (size_t)P.warps * P.ring * P.xbytes;
   P.smem = rings + xs;
   *pl = P;
   return UNIQL_OK;
@@ -922,14 +1124,14 @@ template <int MT, int WARPS, int MINB, bool HAD, int RING>
 static int launch_variant(const DecodeParams& p, const DecodePlan& pl, cudaStream_t stream) {
   auto kern = w4a16_decode_kernel<MT, WARPS, MINB, HAD, RING>;
   {
-    // function attributes are per device
-    static thread_local bool attr_set[64] = {};
+    // function attributes are per device; raise the dynamic shared-memory limit to what this launch needs
+    static thread_local size_t attr_bytes[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
-    if (!attr_set[dev]) {
-      UNIQL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      attr_set[dev] = true;
+    if (pl.smem > attr_bytes[dev]) {
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+      attr_bytes[dev] = pl.smem;
     }
   }
   cudaLaunchConfig_t cfg = {};
@@ -996,17 +1198,29 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   for (int i = a.nproj; i < kMaxProj; ++i) { p.wmap[i] = p.wmap[0]; p.proj[i] = p.proj[0]; }
   p.A = Ain; p.lda = lda;
   p.residual = (const __half*)a.residual; p.ldr = a.ldr;
-  p.tickets = (int*)a.scratch;
-  p.partials = (float*)((char*)a.scratch + part_off);
+  p.partials = (uint2*)((char*)a.scratch + part_off);
+  {
+    // distinct per call where the host can tell calls apart; a captured launch replays with the same tag, which is
+    // why consumers clear what they read
+    static std::atomic<uint32_t> calls{0};
+    p.tag = 1u + (calls.fetch_add(1, std::memory_order_relaxed) & 0x3fffffffu);
+  }
   p.status_word = a.status_word;
-  p.T = pl.T; p.M = (int)a.m; p.NG = pl.NG; p.nproj = a.nproj; p.vbT = pl.vbT; p.W = pl.W; p.epilogue = a.epilogue;
-  p.kc = pl.kc; p.koff = pl.koff; p.nchunks = pl.nchunks; p.Pc = pl.Pc; p.xbytes = pl.xbytes;
+  p.G = pl.G; p.M = (int)a.m; p.nproj = a.nproj; p.epilogue = a.epilogue;
+  p.xbytes = pl.xbytes;
   p.had = pl.fused_had;
   if (pl.fused_had) {
     p.hP = pl.hP; p.hlogP = pl.hlogP; p.hlogQ = pl.hlogQ; p.hMdim = pl.hMdim; p.seg0 = pl.seg0;
     p.hscale = (float)(1.0 / sqrt((double)a.hadamard_dim));
     hadamard_base_signs(pl.hbase, p.hsign);
   }
+  p.npf = 0;
+  for (int i = 0; i < a.nprefetch && i < kMaxPrefetch; ++i)
+    if (a.prefetch_ptr[i] && a.prefetch_bytes[i] >= 128) {
+      p.pf_ptr[p.npf] = (const unsigned char*)a.prefetch_ptr[i];
+      p.pf_lines[p.npf] = (long long)(a.prefetch_bytes[i] / 128);
+      ++p.npf;
+    }
   if (cv) {
     p.cv = *cv;
     if (cv->reduce && pl.units > cv->block_cap) return UNIQL_ESHAPE;
@@ -1015,16 +1229,14 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     if (cv->reduce && a.epilogue != UNIQL_EPILOGUE_NONE) return UNIQL_EINVAL;
   }
   if (pl.fused_had) {
-    if (pl.variant == 0) return launch_variant<1, 12, 2, true, 2>(p, pl, stream);
-    if (pl.variant == 3) return launch_variant<1, 10, 2, true, 2>(p, pl, stream);
-    if (pl.variant == 4) return launch_variant<1, 8, 2, true, 3>(p, pl, stream);
-    return launch_variant<1, 8, 2, true, 2>(p, pl, stream);     // m <= 4 here
+    if (pl.variant == 0) return launch_variant<1, 16, 1, true, 3>(p, pl, stream);
+    if (pl.variant == 3) return launch_variant<1, 8, 2, true, 2>(p, pl, stream);
+    return launch_variant<1, 16, 1, true, 2>(p, pl, stream);     // m <= 4 here
   }
-  if (pl.variant == 0) return launch_variant<1, 12, 2, false, 2>(p, pl, stream);
-  if (pl.variant == 3) return launch_variant<1, 10, 2, false, 2>(p, pl, stream);
-  if (pl.variant == 4) return launch_variant<1, 8, 2, false, 3>(p, pl, stream);
-  if (pl.variant == 1) return launch_variant<1, 8, 2, false, 2>(p, pl, stream);
-  return launch_variant<2, 8, 1, false, 2>(p, pl, stream);
+  if (pl.variant == 0) return launch_variant<1, 16, 1, false, 3>(p, pl, stream);
+  if (pl.variant == 1) return launch_variant<1, 16, 1, false, 2>(p, pl, stream);
+  if (pl.variant == 3) return launch_variant<1, 8, 2, false, 2>(p, pl, stream);
+  return launch_variant<2, 12, 1, false, 2>(p, pl, stream);
 }
 
 // Host-side replay of the kernel's work split for one launch geometry: walks every warp's slots with the kernel's own
@@ -1036,42 +1248,53 @@ static int replay_plan(const DecodePlan& pl, int epilogue) {
   std::unordered_map<long long, int> tiles;
   std::unordered_map<int, long long> tickets;
   std::unordered_map<long long, int> seen;
-  for (int wg = 0; wg < pl.W; ++wg) {
-    const long long s0 = pl.T * wg / pl.W, s1 = pl.T * (wg + 1) / pl.W;
+  const SlotGeom& G = pl.G;
+  // the reciprocal divisions against plain ones
+  for (int wg = 0; wg <= G.W; ++wg)
+    if (warp_begin(G, wg) != G.T * wg / G.W) return 12;
+  for (int wg = 0; wg < G.W; ++wg) {
+    const long long s0 = warp_begin(G, wg), s1 = warp_begin(G, wg + 1);
     if (s1 <= s0) continue;
-    if (warp_of_slot(s0, pl.T, pl.W) != wg || warp_of_slot(s1 - 1, pl.T, pl.W) != wg) return 1;
-    SlotIt it = slot_at<CH>(s0, pl.vbT, pl.NG, pl.kc, pl.koff);
+    if (warp_of_slot(G, s0) != wg || warp_of_slot(G, s1 - 1) != wg) return 1;
+    if (warp_of_slot(G, s0) != (int)(((s0 + 1) * G.W - 1) / G.T)) return 13;
+    SlotIt it = slot_at<CH>(G, s0);
     int run = 0;
     for (long long i = 0; i < s1 - s0; ++i) {
-      const SlotIt ref = slot_decode(s0 + i, pl.vbT, pl.NG, pl.kc, pl.koff);
+      const SlotIt ref = slot_decode(G, s0 + i);
+      {
+        // slot_decode itself against plain division
+        const long long sl = s0 + i;
+        const int q = (int)(sl / G.vbT), cpl = (q + G.koff) / G.kc;
+        if (ref.c != cpl) return 14;
+      }
       if (ref.vb != it.vb || ref.g != it.g || ref.c != it.c || ref.g_lo != it.g_lo || ref.g_hi != it.g_hi) return 2;
-      if (it.vb < 0 || it.vb >= pl.vbT || it.g < 0 || it.g >= pl.NG) return 3;
-      const long long id = (long long)it.vb * pl.NG + it.g;
+      if (it.vb < 0 || it.vb >= G.vbT || it.g < 0 || it.g >= G.NG) return 3;
+      const long long id = (long long)it.vb * G.NG + it.g;
       if (seen[id]++) return 4;
       ++run;
       if (i == s1 - s0 - 1 || it.g + 1 == it.g_hi) {
         const int wc = it.g_hi - it.g_lo;
-        const long long first = (long long)pl.vbT * it.g_lo + (long long)it.vb * wc;
-        const int jrun = run_index(first, s0 + i - (run - 1), wg, pl.T, pl.W);
-        if (jrun < 0 || jrun >= pl.Pc || it.c < 0 || it.c >= pl.nchunks) return 5;
-        if (jrun >= runs_of(it.vb, it.g_lo, it.g_hi, pl.vbT, pl.T, pl.W)) return 6;
-        const long long tile = ((long long)it.vb * pl.nchunks + it.c) * pl.Pc + jrun;
+        const long long first = (long long)G.vbT * it.g_lo + (long long)it.vb * wc;
+        const int jrun = run_index(G, first, s0 + i - (run - 1), wg);
+        if (jrun < 0 || jrun >= G.Pc || it.c < 0 || it.c >= G.nchunks) return 5;
+        if (jrun >= runs_of(G, it.vb, it.g_lo, it.g_hi)) return 6;
+        const long long tile = ((long long)it.vb * G.nchunks + it.c) * G.Pc + jrun;
         if (tiles[tile]++) return 7;
         tickets[swiglu ? it.vb >> 1 : it.vb] += run;
         run = 0;
       }
-      slot_next<CH>(it, pl.vbT, pl.NG, pl.kc);
+      slot_next<CH>(G, it);
     }
   }
-  if ((long long)seen.size() != pl.T) return 8;
+  if ((long long)seen.size() != G.T) return 8;
   if ((int)tickets.size() != pl.units) return 9;
   for (auto& kv : tickets)
-    if (kv.second != (swiglu ? 2 : 1) * (long long)pl.NG) return 10;
+    if (kv.second != (swiglu ? 2 : 1) * (long long)G.NG) return 10;
   // the number of tiles a block's finisher reads equals the number written
   long long expect = 0;
-  for (int cc = 0; cc < pl.nchunks; ++cc)
-    for (int b = 0; b < pl.vbT; ++b)
-      expect += runs_of(b, chunk_lo(cc, pl.kc, pl.koff), chunk_hi(cc, pl.kc, pl.koff, pl.NG), pl.vbT, pl.T, pl.W);
+  for (int cc = 0; cc < G.nchunks; ++cc)
+    for (int b = 0; b < G.vbT; ++b)
+      expect += runs_of(G, b, chunk_lo(cc, G.kc, G.koff), chunk_hi(cc, G.kc, G.koff, G.NG));
   if (expect != (long long)tiles.size()) return 11;
   return 0;
 }
@@ -1146,5 +1369,6 @@ extern "C" int uniql_w4a16_linear_static(const void* A, int64_t lda, const void*
   a.scratch = scratch; a.scratch_bytes = UNIQL_STATIC_SCRATCH_BYTES;
   a.status_word = status_word;
   a.comm = nullptr;
+  a.nprefetch = 0;
   return launch_decode(a, stream);
 }

@@ -30,6 +30,7 @@
 // Every mbarrier wait is bounded; a wait that gives up sets UNIQL_STATUS_WAIT_TIMEOUT and the kernel drains.
 #include "common.cuh"
 #include "linear_internal.cuh"
+#include "tma.cuh"
 
 #include <cuda.h>
 #include <stdlib.h>
@@ -890,23 +891,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn tc_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
+static EncodeTiledFn tc_encode_fn() { return encode_tiled_fn(); }   // shared, initialised once (thread-safe)
 
 bool gemm_tc_supported(int64_t m, int64_t n, int64_t k) {
   return m > 16 && n >= 128 && n % 64 == 0 && k % 128 == 0;
@@ -916,7 +901,7 @@ size_t gemm_tc_scratch_bytes(int64_t, int64_t, int64_t) { return 0; }
 
 // Clusters of `split` CTAs of the small-batch kernel that can be resident together (0 if the query fails).
 static int max_active_clusters(int split, int smem) {
-  static int cache[64][9][2];                   // [device][split] -> {smem the answer is for, answer}
+  static thread_local int cache[64][9][2];      // [device][split] -> {smem the answer is for, answer}; per thread: no races
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || split < 1 || split > 8) return 0;

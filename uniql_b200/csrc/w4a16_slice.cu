@@ -33,7 +33,8 @@ __device__ __forceinline__ int scale_slot(int r) { return 8 * (r & 7) + (r >> 3)
 __global__ void __launch_bounds__(128)
 w4a16_gather_columns_kernel(const uint32_t* __restrict__ packed_in, const __half* __restrict__ scales_in, int n_src_pad,
                             const int* __restrict__ col_index, int n_new, int zero_rows_from,
-                            uint32_t* __restrict__ packed_out, __half* __restrict__ scales_out, int n_out_pad) {
+                            uint32_t* __restrict__ packed_out, __half* __restrict__ scales_out, int n_out_pad,
+                            int* __restrict__ status_word) {
   const int w = threadIdx.x;                     // output word of this 64-column block and packed row
   const int b = blockIdx.x, kt = blockIdx.y;
   const int i = w >> 2, j = w & 3, g = i >> 2, c = i & 3;
@@ -41,7 +42,11 @@ w4a16_gather_columns_kernel(const uint32_t* __restrict__ packed_in, const __half
 #pragma unroll
   for (int hi = 0; hi < 2; ++hi) {
     const int n_out = 64 * b + 16 * j + g + 8 * hi;
-    const int src = n_out < n_new ? col_index[n_out] : -1;
+    int src = n_out < n_new ? col_index[n_out] : -1;
+    if (src >= n_src_pad) {                      // not a column of the source: zero column, and say so
+      if (status_word) atomicOr(status_word, UNIQL_STATUS_BAD_INDEX);
+      src = -1;
+    }
     if (src < 0) continue;
     const ColPos sp = col_pos(src & 63);
     const uint32_t word = packed_in[(size_t)kt * (2 * (size_t)n_src_pad) + (size_t)(src >> 6) * 128 + (sp.g * 4 + c) * 4 + sp.j];
@@ -63,20 +68,25 @@ w4a16_gather_columns_kernel(const uint32_t* __restrict__ packed_in, const __half
     const int n_out = 64 * b + r;
     const int src = n_out < n_new ? col_index[n_out] : -1;
     __half s = __float2half(0.f);
-    if (src >= 0) s = scales_in[(size_t)grp * n_src_pad + (size_t)(src >> 6) * 64 + scale_slot(src & 63)];
+    if (src >= 0 && src < n_src_pad) s = scales_in[(size_t)grp * n_src_pad + (size_t)(src >> 6) * 64 + scale_slot(src & 63)];
     scales_out[(size_t)grp * n_out_pad + 64 * b + w] = s;
   }
 }
 
 __global__ void __launch_bounds__(256)
-w4a16_dequantize_rows_kernel(const uint32_t* __restrict__ packed, const __half* __restrict__ scales, int n_src_pad,
-                             const int* __restrict__ row_index, int k_new, int n_real, __half* __restrict__ out,
-                             int64_t ld) {
+w4a16_dequantize_rows_kernel(const uint32_t* __restrict__ packed, const __half* __restrict__ scales, int size_k,
+                             int n_src_pad, const int* __restrict__ row_index, int k_new, int n_real,
+                             __half* __restrict__ out, int64_t ld, int* __restrict__ status_word) {
   // consecutive threads take consecutive kept rows of one column: coalesced writes, gathered 4-byte reads
   const int kk = blockIdx.x * blockDim.x + threadIdx.x;
   const int n = blockIdx.y;
   if (kk >= k_new || n >= n_real) return;
   const int k = row_index[kk];
+  if (k < 0 || k >= size_k) {                    // not a row of the source: zero, and say so
+    if (status_word) atomicOr(status_word, UNIQL_STATUS_BAD_INDEX);
+    out[(size_t)n * ld + kk] = __float2half(0.f);
+    return;
+  }
   const int kt = k >> 4, k16 = k & 15;
   const int c = (k16 & 7) >> 1, bit1 = k16 & 1, bit8 = k16 >> 3;
   const ColPos p = col_pos(n & 63);
@@ -93,7 +103,8 @@ w4a16_dequantize_rows_kernel(const uint32_t* __restrict__ packed, const __half* 
 
 extern "C" int uniql_w4a16_gather_columns(const void* packed_in, const void* scales_in, int64_t size_k, int64_t n_src_pad,
                                           const int32_t* col_index, int64_t n_new, int64_t zero_rows_from,
-                                          void* packed_out, void* scales_out, int64_t n_out_pad, void* stream) {
+                                          void* packed_out, void* scales_out, int64_t n_out_pad, int* status_word,
+                                          void* stream) {
   using namespace uniql;
   if (size_k <= 0 || size_k % 128 != 0 || n_src_pad <= 0 || n_src_pad % 64 != 0) return UNIQL_ESHAPE;
   if (n_out_pad <= 0 || n_out_pad % 64 != 0 || n_new < 0 || n_new > n_out_pad) return UNIQL_ESHAPE;
@@ -103,13 +114,13 @@ extern "C" int uniql_w4a16_gather_columns(const void* packed_in, const void* sca
   dim3 grid((unsigned)(n_out_pad / 64), (unsigned)(size_k / 16));
   w4a16_gather_columns_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(
       (const uint32_t*)packed_in, (const __half*)scales_in, (int)n_src_pad, col_index, (int)n_new, (int)zero_rows_from,
-      (uint32_t*)packed_out, (__half*)scales_out, (int)n_out_pad);
+      (uint32_t*)packed_out, (__half*)scales_out, (int)n_out_pad, status_word);
   return launch_status();
 }
 
 extern "C" int uniql_w4a16_dequantize_rows(const void* packed, const void* scales, int64_t size_k, int64_t n_src_pad,
                                            const int32_t* row_index, int64_t k_new, int64_t n_real, void* out, int64_t ld,
-                                           void* stream) {
+                                           int* status_word, void* stream) {
   using namespace uniql;
   if (size_k <= 0 || size_k % 128 != 0 || n_src_pad <= 0 || n_src_pad % 64 != 0) return UNIQL_ESHAPE;
   if (k_new < 0 || n_real < 0 || n_real > n_src_pad || n_real > 65535 || ld < k_new) return UNIQL_ESHAPE;
@@ -117,6 +128,7 @@ extern "C" int uniql_w4a16_dequantize_rows(const void* packed, const void* scale
   if (!packed || !scales || !row_index || !out) return UNIQL_EINVAL;
   dim3 grid((unsigned)((k_new + 255) / 256), (unsigned)n_real);
   w4a16_dequantize_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
-      (const uint32_t*)packed, (const __half*)scales, (int)n_src_pad, row_index, (int)k_new, (int)n_real, (__half*)out, ld);
+      (const uint32_t*)packed, (const __half*)scales, (int)size_k, (int)n_src_pad, row_index, (int)k_new, (int)n_real,
+      (__half*)out, ld, status_word);
   return launch_status();
 }

@@ -9,7 +9,7 @@ import torch
 
 import ctypes
 
-from ._lib import Proj, check, lib
+from ._lib import Prefetch, Proj, check, lib
 
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
 
@@ -31,7 +31,8 @@ def status_word(device: torch.device) -> torch.Tensor:
 
 
 def read_and_clear_status(device) -> int:
-    """Synchronising read of the kernel diagnostics word (bit 0: an embedding id was out of range)."""
+    """Synchronising read of the kernel diagnostics word (bit 0: an embedding id was out of range; bit 1: a bounded
+    wait gave up; bit 2: a slicing index was outside the source layer)."""
     t = status_word(torch.device(device))
     v = int(t.item())
     t.zero_()
@@ -142,7 +143,7 @@ _group_need_cache: dict = {}
 
 def w4a16_linear_group(x: torch.Tensor | None, layers, epilogue: str = "none", residual: torch.Tensor | None = None,
                        hadamard_dim: int = 0, outs=None, comm=None, tp_flags: int = 0, col_offset: int = 0,
-                       k_offset: int = 0, m: int | None = None):
+                       k_offset: int = 0, m: int | None = None, prefetch=None):
     """One decode launch (m <= 16) for up to four projections that read the same activations.
 
     layers: sequence of (weight int32 [k/16, 2n], scale fp16 [k/128, n], bias fp16 or None, n_out).
@@ -150,6 +151,8 @@ def w4a16_linear_group(x: torch.Tensor | None, layers, epilogue: str = "none", r
     result (single layer or swiglu).  hadamard_dim: size of the Hadamard transform applied to the rows of x first.
     With `comm` (communicator handle) and tp_flags (TP_REDUCE / TP_GATHER_OUT / TP_GATHER_IN) the launch is a step of a
     tensor-parallel layer; with TP_GATHER_IN x may be None and m must be given.
+    prefetch: up to four tensors (or (tensor, bytes) pairs) -- the packed weights the following launches will stream --
+    that the kernel asks L2 for when its own stream ends.
     Returns the list of outputs (one tensor for swiglu)."""
     if epilogue not in _EPILOGUES:
         raise RuntimeError(f"unknown epilogue {epilogue!r}")
@@ -196,6 +199,14 @@ def w4a16_linear_group(x: torch.Tensor | None, layers, epilogue: str = "none", r
         if residual.dtype != torch.float16 or residual.dim() != 2 or residual.stride(1) != 1:
             raise RuntimeError("residual must be a 2-D float16 tensor with unit column stride")
         res_ptr, ldr = residual.data_ptr(), residual.stride(0)
+    pf_arr, npf = None, 0
+    if prefetch:
+        pf_arr = (Prefetch * 4)()
+        for item in prefetch:
+            t, nb = item if isinstance(item, tuple) else (item, item.numel() * item.element_size())
+            if npf < 4 and nb >= 128:
+                pf_arr[npf].ptr, pf_arr[npf].bytes = t.data_ptr(), min(nb, t.numel() * t.element_size())
+                npf += 1
     idx = dev.index
     L = lib()
     with torch.cuda.device(dev):
@@ -209,11 +220,12 @@ def w4a16_linear_group(x: torch.Tensor | None, layers, epilogue: str = "none", r
         stream = torch._C._cuda_getCurrentRawStream(idx)
         if comm is not None:
             code = L.uniql_w4a16_linear_group_tp(comm, tp_flags, col_offset, k_offset, x_ptr, lda, m, k, arr, len(layers),
-                                                 _EPILOGUES[epilogue], res_ptr, ldr, hadamard_dim, scratch.data_ptr(),
-                                                 scratch.numel(), st.data_ptr(), stream)
+                                                 _EPILOGUES[epilogue], res_ptr, ldr, hadamard_dim, pf_arr, npf,
+                                                 scratch.data_ptr(), scratch.numel(), st.data_ptr(), stream)
         else:
             code = L.uniql_w4a16_linear_group(x_ptr, lda, m, k, arr, len(layers), _EPILOGUES[epilogue], res_ptr, ldr,
-                                              hadamard_dim, scratch.data_ptr(), scratch.numel(), st.data_ptr(), stream)
+                                              hadamard_dim, pf_arr, npf, scratch.data_ptr(), scratch.numel(),
+                                              st.data_ptr(), stream)
     if code != 0:
         check(code, "uniql_w4a16_linear_group")
     return outs
@@ -305,13 +317,18 @@ def w4a16_gather_columns(weight: torch.Tensor, scale: torch.Tensor, col_index: t
     dev = weight.device
     size_k, n_src_pad = weight.shape[0] * 16, weight.shape[1] // 2
     idx = col_index.to(device=dev, dtype=torch.int32).contiguous()
+    # load-time call: a synchronising range check is affordable, and the CPU path would raise IndexError here too
+    # (negative entries are allowed: they produce zero columns)
+    if idx.numel() and int(idx.max()) >= n_src_pad:
+        raise RuntimeError("col_index out of range")
     weight, scale = weight.contiguous(), scale.contiguous()
     packed = torch.empty((size_k // 16, 2 * n_out_pad), dtype=torch.int32, device=dev)
     scales = torch.empty((size_k // 128, n_out_pad), dtype=torch.float16, device=dev)
     with torch.cuda.device(dev):
         code = lib().uniql_w4a16_gather_columns(weight.data_ptr(), scale.data_ptr(), size_k, n_src_pad, idx.data_ptr(),
                                                 idx.numel(), size_k if zero_rows_from is None else zero_rows_from,
-                                                packed.data_ptr(), scales.data_ptr(), n_out_pad, _stream_handle(dev))
+                                                packed.data_ptr(), scales.data_ptr(), n_out_pad,
+                                                status_word(dev).data_ptr(), _stream_handle(dev))
     check(code, "uniql_w4a16_gather_columns")
     return packed, scales
 
@@ -329,6 +346,7 @@ def w4a16_dequantize_rows(weight: torch.Tensor, scale: torch.Tensor, row_index: 
     out = torch.empty((n_real, idx.numel()), dtype=torch.float16, device=dev)
     with torch.cuda.device(dev):
         code = lib().uniql_w4a16_dequantize_rows(weight.data_ptr(), scale.data_ptr(), size_k, n_src_pad, idx.data_ptr(),
-                                                 idx.numel(), n_real, out.data_ptr(), idx.numel(), _stream_handle(dev))
+                                                 idx.numel(), n_real, out.data_ptr(), idx.numel(),
+                                                 status_word(dev).data_ptr(), _stream_handle(dev))
     check(code, "uniql_w4a16_dequantize_rows")
     return out
