@@ -14,6 +14,17 @@ from oracle import uniql_oracle as orc
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["tiled", "slot"], autouse=True)
+def engine(request, monkeypatch):
+    """Both decode kernels take every grouped launch: the CTA-tiled one (default on one GPU) and the slot-balanced one
+    (the kernel tensor-parallel launches use; UNIQL_B200_DECODE_ENGINE=slot selects it here)."""
+    if request.param == "slot":
+        monkeypatch.setenv("UNIQL_B200_DECODE_ENGINE", "slot")
+    else:
+        monkeypatch.delenv("UNIQL_B200_DECODE_ENGINE", raising=False)
+    return request.param
+
+
 def _dev(layer):
     b = torch.from_numpy(layer["bias"]).cuda() if layer["bias"] is not None else None
     return (torch.from_numpy(layer["packed"]).cuda(), torch.from_numpy(layer["scales"]).cuda(), b, layer["n"])

@@ -106,3 +106,21 @@ def test_full_size_qwen_table_checksum():
     for p in range(8):
         want += ((u >> (4 * p)) & 0xF).sum(-1).double()
     assert torch.equal(total, want)
+
+
+def test_from_fp16_on_a_cuda_layer_matches_the_reference_fixture(golden_dir):
+    """W4O16Embedding.from_fp16 (quantize/quant_embedding_layers.py:25-47) run with the layer on the GPU: packed words
+    and row scales equal the fixture the reference's own from_fp16 produced, and the gather of every row equals the
+    oracle's dequantisation bit for bit."""
+    from uniql_b200.quantize.quant_embedding_layers import W4O16Embedding
+    e = np.load(os.path.join(golden_dir, "embedding_module.npz"))
+    emb = torch.nn.Embedding(*e["fp16_weight"].shape).half()
+    emb.weight.data = torch.from_numpy(e["fp16_weight"])
+    q = W4O16Embedding.from_fp16(emb.cuda())
+    assert q.weight.is_cuda and q.scales.is_cuda
+    assert np.array_equal(q.weight.data.cpu().numpy(), e["sd_weight"])
+    assert np.array_equal(q.scales.cpu().numpy().view(np.uint16), e["sd_scales"].view(np.uint16))
+    ids = torch.arange(e["fp16_weight"].shape[0], device="cuda")
+    got = q(ids).cpu().numpy()
+    want = orc.embedding_lookup(ids.cpu().numpy(), e["sd_weight"], e["sd_scales"])
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))

@@ -180,3 +180,50 @@ def test_host_path_raises_on_out_of_range_columns():
     _, packed, scale = qh.w4a16_quantize(w.t().contiguous(), 4, 128, None, 64)
     with pytest.raises(IndexError):
         mh._select_columns(packed, scale, 256, 256, torch.tensor([0, 999]), True)
+
+
+def test_checkpoint_walker_applies_every_slicer(gold):
+    """slice_quantized_weights (modeling/modeling_helpers.py:235-358) over a one-layer state dict with an MLP block and
+    an attention block: every entry equals what the reference's slicers returned for that layer."""
+    from types import SimpleNamespace as NS
+
+    class UniqlMLP:            # stand-ins for the reference's quantised block classes: only names and sizes matter
+        pass
+
+    class UniqlAttention:
+        pass
+
+    def shaped(t):
+        return NS(weight=NS(shape=t.shape))
+
+    layers_in = {tag: _layer(gold, tag) for tag in ("up", "down", "qk", "v", "o")}
+    mlp, attn = UniqlMLP(), UniqlAttention()
+    mlp.intermediate_size = RED
+    mlp.up_proj, mlp.gate_proj, mlp.down_proj = shaped(layers_in["up"][0]), shaped(layers_in["up"][0]), shaped(layers_in["down"][0])
+    attn.head_dim = RHD
+    attn.q_proj = attn.k_proj = shaped(layers_in["qk"][0])
+    attn.v_proj, attn.o_proj = shaped(layers_in["v"][0]), shaped(layers_in["o"][0])
+    layer = NS(named_children=lambda: [("mlp", mlp), ("self_attn", attn)])
+    model = NS(config=NS(hidden_size=HIDDEN, intermediate_size=INTER, num_attention_heads=NHEADS,
+                         num_key_value_heads=NHEADS, head_dim=HD))
+    helper = NS(get_layers=lambda m: [layer], mlp_w4a16_uniql_class_name="UniqlMLP",
+                attn_w4a16_uniql_class_name="UniqlAttention", mamba_w4a16_uniql_class_name="UniqlMamba",
+                get_mlp_key=lambda i: f"model.layers.{i}.mlp", get_attn_key=lambda i: f"model.layers.{i}.self_attn")
+    sd = {}
+    for name, tag in (("mlp.up_proj", "up"), ("mlp.gate_proj", "up"), ("mlp.down_proj", "down"), ("self_attn.q_proj", "qk"),
+                      ("self_attn.k_proj", "qk"), ("self_attn.v_proj", "v"), ("self_attn.o_proj", "o")):
+        for part, t in zip(("weight", "scale", "workspace"), layers_in[tag]):
+            sd[f"model.layers.0.{name}.{part}"] = t.clone()
+    sd["model.layers.0.self_attn.q_proj.bias"] = torch.from_numpy(gold["qk_bias_in"])
+    idx = torch.arange(NHEADS * HD, dtype=torch.int64).reshape(NHEADS, HD)
+    sd["model.layers.0.self_attn.indices"] = idx.clone()
+    out = mh.slice_quantized_weights(model, helper, sd)
+    assert out is sd
+    for name, tag in (("mlp.up_proj", "up"), ("mlp.gate_proj", "up"), ("mlp.down_proj", "down"), ("self_attn.q_proj", "qk"),
+                      ("self_attn.k_proj", "qk"), ("self_attn.v_proj", "v"), ("self_attn.o_proj", "o")):
+        _same(sd[f"model.layers.0.{name}.weight"], gold[tag + "_packed"])
+        _same(sd[f"model.layers.0.{name}.scale"], gold[tag + "_scale"])
+        _same(sd[f"model.layers.0.{name}.workspace"], gold[tag + "_ws"])
+    _same(sd["model.layers.0.self_attn.q_proj.bias"], gold["qk_bias"])
+    assert "model.layers.0.self_attn.k_proj.bias" not in sd
+    assert torch.equal(sd["model.layers.0.self_attn.indices"], mh.slice_indices(idx, HD, RHD))

@@ -71,9 +71,15 @@ def test_static_scratch_limits_are_reported():
     args = (w.data_ptr(), s.data_ptr(), None, out.data_ptr(), 256)
     assert L.uniql_w4a16_linear_static(x.data_ptr(), 256, *args, 17, 256, 256, 256, 128, None, None) == -3   # m > 16
     assert L.uniql_w4a16_linear_static(x.data_ptr(), 256, *args, 1, 256, 256, 256, -1, None, None) == -2    # per-channel
-    # a width whose split-k partials cannot fit the built-in array is refused, nothing is launched
-    big_n, big_k = 65536, 32768
-    assert L.uniql_w4a16_scratch_bytes(16, big_n, big_k, 0) > 8 * 1024 * 1024
-    args_big = (w.data_ptr(), s.data_ptr(), None, out.data_ptr(), big_n)
-    assert L.uniql_w4a16_linear_static(x.data_ptr(), big_k, *args_big, 16, big_n, big_n, big_k, 128, None, None) == -7
+    # a problem whose scratch need is beyond the built-in array is refused, nothing is launched.  The buffers are real
+    # and large enough all the same: this call must never be able to touch memory it does not own.
+    big_n, big_k, big_m = 65536, 8192, 16
+    assert L.uniql_w4a16_scratch_bytes(big_m, big_n, big_k, 0) > 8 * 1024 * 1024
+    xb = torch.zeros(big_m, big_k, dtype=torch.float16, device="cuda")
+    wb = torch.zeros(big_k // 16, 2 * big_n, dtype=torch.int32, device="cuda")
+    sb = torch.zeros(big_k // 128, big_n, dtype=torch.float16, device="cuda")
+    ob = torch.zeros(big_m, big_n, dtype=torch.float16, device="cuda")
+    assert L.uniql_w4a16_linear_static(xb.data_ptr(), big_k, wb.data_ptr(), sb.data_ptr(), None, ob.data_ptr(), big_n,
+                                       big_m, big_n, big_n, big_k, 128, None, None) == -7
+    torch.cuda.synchronize()
     assert b"built-in scratch" in L.uniql_strerror(-7)

@@ -510,6 +510,124 @@ __global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict
   Elem<T>::store8(yr + tid * 8, v);
 }
 
+// The few-row kernel again, for a tensor-parallel layer: the fp16 rows are read from this rank's feature area, where
+// the column shards of all ranks arrive as 8-byte words {2 halves, epoch} (stored there by the epilogue of the
+// column-parallel launch before this one).  A word whose epoch is not this call's yet is read again (bounded; a wait
+// that gives up raises UNIQL_STATUS_WAIT_TIMEOUT).  The epoch of the call is this rank's own counter of block 0, which
+// its own producer launch has already advanced.
+__global__ void __launch_bounds__(128) hadamard_split_feat_kernel(const unsigned char* area, size_t gather_off,
+                                                                  size_t epoch_off, int64_t feat_cap, __half* __restrict__ y,
+                                                                  int64_t ldy, int P, int B, float scale,
+                                                                  const HadSigns signs, int* status_word) {
+  __shared__ __align__(16) float buf[1024];
+  pdl_launch_dependents();                       // the linear behind this kernel only prefetches until it waits on us
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int seg = blockIdx.x, row = blockIdx.y;
+  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(area + epoch_off);
+  const uint2* xr = reinterpret_cast<const uint2*>(area + gather_off) +
+                    ((size_t)(epoch & 1u) * 16 + row) * (size_t)(feat_cap >> 1);
+  __half* yr = y + (int64_t)row * ldy + (size_t)seg * P;
+  const uint64_t mask = signs.row[seg];
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = 0.f;
+  bool failed = false;
+  constexpr int kBatch = 8;
+  for (int a0 = 0; a0 < B; a0 += kBatch) {
+    uint4 w[kBatch][2];                          // 4 words = 8 halves per source segment
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+      if (a0 + i < B) {
+        const uint2* src = xr + (((size_t)(a0 + i) * P + tid * 8) >> 1);
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[i][0].x), "=r"(w[i][0].y), "=r"(w[i][0].z), "=r"(w[i][0].w) : "l"(src) : "memory");
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[i][1].x), "=r"(w[i][1].y), "=r"(w[i][1].z), "=r"(w[i][1].w) : "l"(src + 2) : "memory");
+      }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+      if (a0 + i < B) {
+        const uint2* src = xr + (((size_t)(a0 + i) * P + tid * 8) >> 1);
+        int spin = 0;
+        while ((w[i][0].y != epoch || w[i][0].w != epoch || w[i][1].y != epoch || w[i][1].w != epoch) && !failed) {
+          if (++spin > (1 << 22)) { failed = true; break; }
+          asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[i][0].x), "=r"(w[i][0].y), "=r"(w[i][0].z), "=r"(w[i][0].w) : "l"(src) : "memory");
+          asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[i][1].x), "=r"(w[i][1].y), "=r"(w[i][1].z), "=r"(w[i][1].w) : "l"(src + 2) : "memory");
+        }
+        const uint4 raw = make_uint4(w[i][0].x, w[i][0].z, w[i][1].x, w[i][1].z);
+        float t[8];
+        Elem<__half>::unpack8(raw, t);
+        const float sg = ((mask >> (a0 + i)) & 1ull) ? -1.f : 1.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = fmaf(sg, t[e], v[e]);
+      }
+  }
+  if (failed && status_word) atomicOr(status_word, UNIQL_STATUS_WAIT_TIMEOUT);
+  butterflies<8>(v);
+#pragma unroll
+  for (int s = 0; s < 5; ++s) {
+    if ((8 << s) < P) {
+      const bool upper = (lane >> s) & 1;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float o = __shfl_xor_sync(0xffffffffu, v[i], 1 << s);
+        v[i] = upper ? (o - v[i]) : (v[i] + o);
+      }
+    }
+  }
+  if (P > 256) {
+    float4* d = reinterpret_cast<float4*>(buf + tid * 8);
+    d[0] = make_float4(v[0], v[1], v[2], v[3]);
+    d[1] = make_float4(v[4], v[5], v[6], v[7]);
+    __syncthreads();
+    if (P == 512) strided_pass<2>(buf, P, 256, tid, blockDim.x);
+    else strided_pass<4>(buf, P, 256, tid, blockDim.x);
+    __syncthreads();
+    const float4* s4 = reinterpret_cast<const float4*>(buf + tid * 8);
+    const float4 a = s4[0], b = s4[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] *= scale;
+  Elem<__half>::store8(yr + tid * 8, v);
+}
+
+// Segment layout of the few-row kernels: dim = B segments of Ps points.  Returns false if the size does not fit them.
+static bool split_layout(int64_t dim, int base, int64_t* Ps_out, int64_t* B_out, HadSigns* signs) {
+  const int64_t P = dim / base;
+  if (P < 256) return false;
+  int64_t Ps = P < 512 ? P : 512;
+  int64_t Q = P / Ps;
+  if (base * Q > 64) { Ps = 1024; Q = P / Ps; }
+  const int64_t B = base * Q;
+  if (!(B <= 64 && Ps <= 1024 && Q >= 1)) return false;
+  int8_t h[1600];
+  if (base > 1) base_matrix(base, h);
+  for (int i = 0; i < 64; ++i) signs->row[i] = 0;
+  for (int s1 = 0; s1 < B; ++s1)
+    for (int s2 = 0; s2 < B; ++s2) {
+      const int a1 = (int)(s1 / Q), h1 = (int)(s1 % Q), a2 = (int)(s2 / Q), h2 = (int)(s2 % Q);
+      int neg = (base > 1 && h[a1 * base + a2] < 0) ? 1 : 0;
+      neg ^= __builtin_popcount((unsigned)(h1 & h2)) & 1;
+      if (neg) signs->row[s1] |= (1ull << s2);
+    }
+  *Ps_out = Ps;
+  *B_out = B;
+  return true;
+}
+
+int launch_hadamard_feat(const CommView& cv, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
+                         int* status_word, cudaStream_t stream) {
+  const int base = hadamard_base_of(dim);
+  if (base == 0 || dim > cv.feat_cap || rows < 1 || rows > 16) return UNIQL_ESHAPE;
+  HadSigns signs;
+  int64_t Ps = 0, B = 0;
+  if (!split_layout(dim, base, &Ps, &B, &signs)) return UNIQL_ESHAPE;
+  dim3 grid((unsigned)B, (unsigned)rows);
+  hadamard_split_feat_kernel<<<grid, (int)(Ps / 8), 0, stream>>>(cv.bufs[cv.rank], cv.gather_off, cv.gather_epoch_off,
+                                                               cv.feat_cap, (__half*)y, ldy, (int)Ps, (int)B, scale,
+                                                               signs, status_word);
+  return launch_status();
+}
+
 int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
                     int dtype, bool pdl_trigger, cudaStream_t stream) {
   const int base = hadamard_base_of(dim);

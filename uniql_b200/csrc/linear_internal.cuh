@@ -58,6 +58,10 @@ struct DecodeArgs {
   size_t prefetch_bytes[4];
 };
 
+// CTA-tiled decode kernel (w4a16_gemv.cu): single-GPU launches, activations already transformed.
+size_t gemv_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue);
+int launch_gemv_group(const DecodeArgs& a, const __half* A, int64_t lda, cudaStream_t stream);
+
 // m <= 16.  Scratch bytes the launch needs (tickets included).
 size_t decode_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t hadamard_dim,
                             int64_t k_offset);
@@ -81,6 +85,9 @@ int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D,
 int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
                     int dtype, bool pdl_trigger, cudaStream_t stream);
 int hadamard_base_of(int64_t dim);   // 40/28/20/12/1, or 0 if dim is not a supported size
+// fp16 rows (at most 16) read from this rank's feature area of a tensor-parallel layer (see CommView), transformed
+int launch_hadamard_feat(const CommView& cv, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
+                         int* status_word, cudaStream_t stream);
 // Sign rows of the base matrix: bit a' of row[a] set <=> H[a][a'] = -1 (all zero for base 1).
 void hadamard_base_signs(int base, unsigned long long* rows40);
 

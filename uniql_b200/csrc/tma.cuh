@@ -62,5 +62,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn encode_tiled_fn();
 // Packed weights as a 2-D uint32 tensor [KT rows][2N words]; one box = 128 words x 8 rows = one ring slot.
 int make_weight_map(CUtensorMap* map, const void* B, int64_t n, int64_t kt);
+// The same, kept per (address, n, kt): encoded maps are pure functions of those, so a launch does not re-encode.
+int cached_weight_map(CUtensorMap* out, const void* B, int64_t n, int64_t kt);
 
 }  // namespace uniql

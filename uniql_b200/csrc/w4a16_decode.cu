@@ -947,7 +947,7 @@ struct MapKeyHash {
     return std::hash<const void*>()(k.B) ^ (std::hash<int64_t>()(k.n) * 1000003u) ^ (std::hash<int64_t>()(k.kt) * 7919u);
   }
 };
-static int cached_weight_map(CUtensorMap* out, const void* B, int64_t n, int64_t kt) {
+int cached_weight_map(CUtensorMap* out, const void* B, int64_t n, int64_t kt) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   const MapKey key{B, n, kt};
@@ -1117,7 +1117,20 @@ size_t decode_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, i
   if (cached_plan(&pl, m, k, n, nproj, epilogue, hadamard_dim, k_offset) != UNIQL_OK) return UNIQL_SCRATCH_COUNTER_BYTES;
   size_t total = UNIQL_SCRATCH_COUNTER_BYTES + align256(pl.partial_bytes);
   if (hadamard_dim && !pl.fused_had) total += align256((size_t)m * hadamard_dim * 2);   // separate transform kernel
-  return total;
+  // whichever of the two decode kernels the launch ends up on
+  size_t tiled = gemv_scratch_bytes(m, k, n, nproj, epilogue);
+  if (hadamard_dim) tiled += align256((size_t)m * hadamard_dim * 2);
+  return total > tiled ? total : tiled;
+}
+
+// Which decode kernel runs a launch.  Both take every launch (grouped, SwiGLU, residual, the tensor-parallel
+// exchanges); the CTA-tiled kernel of w4a16_gemv.cu is the default because its reduction stays inside the CTA or the
+// cluster and a launch costs about half as much.  UNIQL_B200_DECODE_ENGINE=slot selects the slot-balanced kernel of
+// this file (tests, profiling), which also runs the Hadamard transform in its own prologue.
+static bool use_slot_engine(const DecodeArgs& a) {
+  (void)a;
+  const char* e = getenv("UNIQL_B200_DECODE_ENGINE");
+  return e && e[0] == 's';
 }
 
 template <int MT, int WARPS, int MINB, bool HAD, int RING>
@@ -1159,6 +1172,34 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   int64_t n[kMaxProj] = {0, 0, 0, 0};
   if (a.nproj < 1 || a.nproj > kMaxProj) return UNIQL_EINVAL;
   for (int i = 0; i < a.nproj; ++i) n[i] = a.proj[i].n;
+  if (!use_slot_engine(a)) {
+    // CTA-tiled kernel; an online Hadamard runs as its own kernel in front (rows rounded to fp16 in scratch) and the
+    // linear's weight stream overlaps it through the programmatic dependent launch
+    const size_t base = gemv_scratch_bytes(a.m, a.k, n, a.nproj, a.epilogue);
+    const size_t xh_bytes = a.hadamard_dim ? align256((size_t)a.m * a.hadamard_dim * 2) : 0;
+    if (!a.scratch || a.scratch_bytes < base + xh_bytes || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return UNIQL_ESCRATCH;
+    const __half* Ain = (const __half*)a.A;
+    int64_t lda = a.lda;
+    if (a.hadamard_dim) {
+      __half* xh = (__half*)((char*)a.scratch + base);
+      const float hscale = (float)(1.0 / sqrt((double)a.hadamard_dim));
+      int st;
+      if (a.comm && a.comm->gather_in) {
+        // tensor parallel: the full row sits in this rank's feature area; every rank transforms it and multiplies
+        // its own k slice of the result
+        if (a.k_offset % 128 || a.k_offset + a.k > a.hadamard_dim) return UNIQL_ESHAPE;
+        st = launch_hadamard_feat(*a.comm, xh, a.hadamard_dim, a.m, a.hadamard_dim, hscale, a.status_word, stream);
+        Ain = xh + a.k_offset;
+      } else {
+        if (a.k_offset != 0 || a.k != a.hadamard_dim) return UNIQL_ESHAPE;
+        st = launch_hadamard(a.A, a.lda, xh, a.hadamard_dim, a.m, a.hadamard_dim, hscale, UNIQL_F16, true, stream);
+        Ain = xh;
+      }
+      if (st != UNIQL_OK) return st;
+      lda = a.hadamard_dim;
+    }
+    return launch_gemv_group(a, Ain, lda, stream);
+  }
   DecodePlan pl;
   int st = cached_plan(&pl, a.m, a.k, n, a.nproj, a.epilogue, a.hadamard_dim, a.k_offset);
   if (st != UNIQL_OK) return st;
@@ -1356,6 +1397,7 @@ extern "C" int uniql_w4a16_linear_static(const void* A, int64_t lda, const void*
   if (m == 0) return UNIQL_OK;
   if (!A || !B || !s || !D) return UNIQL_EINVAL;
   if (!aligned16(A) || !aligned16(B) || !aligned16(s) || (reinterpret_cast<uintptr_t>(D) & 1u)) return UNIQL_EINVAL;
+  // the figure uniql_w4a16_scratch_bytes reports for the problem (what either decode kernel would need)
   const size_t need = decode_scratch_bytes(m, k, &n, 1, UNIQL_EPILOGUE_NONE, 0, 0);
   if (need > (size_t)UNIQL_STATIC_SCRATCH_BYTES) return UNIQL_ESTATIC;
   void* scratch = nullptr;

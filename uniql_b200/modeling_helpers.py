@@ -232,3 +232,81 @@ def slice_norm(weight, n_groups, num_heads, intermediate_size, load_intermediate
     head_dim = intermediate_size // num_heads
     idx = get_topk_head_indices(n_groups, num_heads, head_dim, load_intermediate_size // num_heads)
     return weight[idx.to(weight.device)].contiguous()
+
+
+# ----------------------------------------------------------------------------------------------- checkpoint walker
+def _put(loaded, key, names, values):
+    for name, value in zip(names, values):
+        if value is not None:
+            loaded[f"{key}.{name}"] = value
+
+
+def slice_quantized_weights(model, model_helper, loaded_model):
+    """Applies the slicers above to a loaded full-size state dict, layer by layer, so that it fits an elastic
+    (reduced-width) model -- the walker of modeling/modeling_helpers.py:235-358, same arguments and result.
+
+    `model_helper` names the quantised block classes (`mlp_w4a16_uniql_class_name`, `attn_w4a16_uniql_class_name`,
+    `mamba_w4a16_uniql_class_name`) and the state-dict prefixes (`get_mlp_key`, `get_attn_key`, `get_mamba_key`,
+    `get_layers`); the reduced sizes are read from the model's own modules.  `loaded_model` is modified in place and
+    returned; tensors stay on the device they are on (GPU tensors are sliced by the CUDA kernels)."""
+    cfg = model.config
+    wsw = ("weight", "scale", "workspace")
+    for layer_idx, layer in enumerate(model_helper.get_layers(model)):
+        for _, module in layer.named_children():
+            cls = module.__class__.__name__
+            if cls == model_helper.mlp_w4a16_uniql_class_name:
+                key = model_helper.get_mlp_key(layer_idx)
+                for name in ("up_proj", "gate_proj"):
+                    k = f"{key}.{name}"
+                    if k + ".weight" not in loaded_model:        # blocks without a gate projection
+                        continue
+                    _put(loaded_model, k, wsw, slice_w4a16_up_gate_proj(
+                        *(loaded_model[f"{k}.{n}"] for n in wsw), cfg.hidden_size, cfg.intermediate_size,
+                        module.intermediate_size, getattr(module, name).weight.shape))
+                k = f"{key}.down_proj"
+                _put(loaded_model, k, wsw, slice_w4a16_down_proj(
+                    *(loaded_model[f"{k}.{n}"] for n in wsw), cfg.hidden_size, cfg.intermediate_size,
+                    module.intermediate_size, module.down_proj.weight.shape))
+            elif cls == model_helper.attn_w4a16_uniql_class_name:
+                key = model_helper.get_attn_key(layer_idx)
+                head_dim = getattr(cfg, "head_dim", cfg.hidden_size // cfg.num_attention_heads)
+                for name, heads in (("q_proj", cfg.num_attention_heads), ("k_proj", cfg.num_key_value_heads)):
+                    k = f"{key}.{name}"
+                    w, b, s, ws = slice_w4a16_qk_proj(
+                        loaded_model[k + ".weight"], loaded_model.get(k + ".bias"), loaded_model[k + ".scale"],
+                        loaded_model[k + ".workspace"], cfg.hidden_size, heads, head_dim, module.head_dim,
+                        getattr(module, name).weight.shape)
+                    _put(loaded_model, k, ("weight", "bias", "scale", "workspace"), (w, b, s, ws))
+                k = f"{key}.v_proj"
+                _put(loaded_model, k, wsw, slice_w4a16_v_proj(
+                    *(loaded_model[f"{k}.{n}"] for n in wsw), cfg.hidden_size, cfg.num_key_value_heads, head_dim,
+                    module.head_dim, module.v_proj.weight.shape))
+                k = f"{key}.o_proj"
+                _put(loaded_model, k, wsw, slice_w4a16_o_proj(
+                    *(loaded_model[f"{k}.{n}"] for n in wsw), cfg.hidden_size, cfg.num_attention_heads, head_dim,
+                    module.head_dim, module.o_proj.weight.shape))
+                if f"{key}.indices" in loaded_model:
+                    loaded_model[f"{key}.indices"] = slice_indices(loaded_model[f"{key}.indices"], head_dim, module.head_dim)
+            elif cls == model_helper.mamba_w4a16_uniql_class_name:
+                key = model_helper.get_mamba_key(layer_idx)
+                full_inter = model_helper.get_mamba_full_intermediate_size
+                full_state = model_helper.get_mamba_full_ssm_state_size
+                k = f"{key}.in_proj"
+                _put(loaded_model, k, wsw, slice_w4a16_in_proj(
+                    *(loaded_model[f"{k}.{n}"] for n in wsw), hidden_size=cfg.hidden_size, n_groups=module.n_groups,
+                    num_heads=module.num_heads, intermediate_size=full_inter, ssm_state_size=full_state,
+                    load_intermediate_size=module.intermediate_size, load_ssm_state_size=module.ssm_state_size,
+                    load_shape=module.in_proj.weight.shape))
+                k = f"{key}.conv1d"
+                _put(loaded_model, k, ("weight", "bias"), slice_conv1d(
+                    loaded_model[k + ".weight"], loaded_model[k + ".bias"], module.n_groups, module.num_heads, full_inter,
+                    full_state, module.intermediate_size, module.ssm_state_size))
+                k = f"{key}.norm"
+                loaded_model[k + ".weight"] = slice_norm(loaded_model[k + ".weight"], module.n_groups, module.num_heads,
+                                                         full_inter, module.intermediate_size)
+                k = f"{key}.out_proj"
+                _put(loaded_model, k, wsw, slice_w4a16_out_proj(
+                    *(loaded_model[f"{k}.{n}"] for n in wsw), hidden_size=cfg.hidden_size, n_groups=module.n_groups,
+                    num_heads=module.num_heads, intermediate_size=full_inter,
+                    load_intermediate_size=module.intermediate_size, load_shape=module.out_proj.weight.shape))
+    return loaded_model
