@@ -89,10 +89,8 @@ def main():
     # the activated columns into every rank's feature area, then the down shard that reads the full row there,
     # transforms it (Hadamard in the prologue), multiplies its k slice and sums over the ranks in its epilogue ----
     from uniql_b200 import fused as fz
-    slot = os.environ.get("UNIQL_B200_DECODE_ENGINE", "").startswith("s")
-    # (the CTA-tiled kernel's gather path needs 256-point segments or longer; 3584 = 28 x 128 runs on the other kernel)
-    mlp_cases = [(1024, 3584, 1)] if slot else [(4096, 14336, 16)]
-    for hidden, inter, m in mlp_cases + [(4096, 14336, 1), (4096, 14336, 4), (4096, 8192, 2)]:
+    # (the gather path transforms in 256-point segments or longer: 14336 = 28 x 512, 8192 = 16 x 512)
+    for hidden, inter, m in [(4096, 14336, 16), (4096, 14336, 1), (4096, 14336, 4), (4096, 8192, 2)]:
         if (inter // 64) % world or (inter // 128) % world:
             continue
         gate = W4A16B16O16Linear.from_fp16(torch.nn.Linear(hidden, inter, bias=False).half()).to(dev)

@@ -205,7 +205,6 @@ struct DecodeParams {
   const unsigned char* pf_ptr[kMaxPrefetch];   // byte ranges to pull into L2 when this launch's own stream ends
   long long pf_lines[kMaxPrefetch];            // (the weights of the launches that follow), in 128-byte lines
   int npf;
-  CommView cv;
 };
 
 // ------------------------------------------------------------------------------------------------ device helpers
@@ -245,14 +244,6 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void st_word_sys(uint2* p, uint32_t data, uint32_t flag) {
-  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(flag) : "memory");
-}
-__device__ __forceinline__ uint2 ld_word_sys(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
 // A partial sum travels between warps as an 8-byte word {fp32 bits, tag}: one store, one load, and the tag says whether
@@ -342,9 +333,9 @@ __device__ __forceinline__ void flush_tile(uint2* lane_tile, float (&acc)[MT][4]
 }
 
 // Final values of two adjacent columns of one batch row -> fp16 (bias, optional SwiGLU partner, optional residual),
-// stored to D and, in a tensor-parallel column shard, into every rank's feature area.
+// stored to D.
 __device__ __forceinline__ void store_pair(const DecodeParams& p, const DecodeProj& pr, const DecodeProj& pr2, int m,
-                                           int n0, float2 v, float2 v2, bool swiglu, uint32_t gepoch) {
+                                           int n0, float2 v, float2 v2, bool swiglu) {
   if (n0 >= pr.n_out) return;
   const bool two = n0 + 1 < pr.n_out;
   if (pr.bias) {
@@ -375,20 +366,12 @@ __device__ __forceinline__ void store_pair(const DecodeParams& p, const DecodePr
     d[0] = h0;
     if (two) d[1] = h1;
   }
-  if (p.cv.gather_out) {
-    // only real columns travel (n_out is even here): the consumer's row is the concatenation of the ranks' real columns
-    const __half2 hv = __halves2half2(h0, two ? h1 : __float2half_rn(0.f));
-    const size_t word = ((size_t)(gepoch & 1u) * 16 + m) * (size_t)(p.cv.feat_cap >> 1) + (size_t)((p.cv.col_offset + n0) >> 1);
-    for (int r = 0; r < p.cv.world; ++r)
-      st_word_sys(reinterpret_cast<uint2*>(p.cv.bufs[r] + p.cv.gather_off) + word, *reinterpret_cast<const uint32_t*>(&hv),
-                  gepoch);
-  }
 }
 
 // Finishes one block (or one gate/up pair of blocks): the calling warp -- the one that streamed the block's last slot --
 // waits for the tiles of all the warps that worked on it (words tagged with this launch's tag, bounded poll), adds
 // them up in a fixed order and finishes the 64 columns, two per lane.  Consumed words are cleared to tag 0 for the
-// launches to come.  Returns false if a wait gave up.
+// launches to come.  Returns false if the wait gave up.
 __device__ __forceinline__ bool finish_block(const DecodeParams& p, int unit, int lane) {
   const bool swiglu = p.epilogue == UNIQL_EPILOGUE_SWIGLU;
   const size_t tile_elems = (size_t)p.M * 64;   // words per tile
@@ -410,11 +393,6 @@ __device__ __forceinline__ bool finish_block(const DecodeParams& p, int unit, in
                             chunk_hi(cc, p.G.kc, p.G.koff, p.G.NG));
     }
   const int total = p.G.nchunks * p.G.Pc;
-  uint32_t repoch = 0, gepoch = 0;
-  if (p.cv.reduce)
-    repoch = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_epoch_off + 4 * (size_t)unit) + 1;
-  if (p.cv.gather_out)
-    gepoch = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off + 4 * (size_t)unit) + 1;
   for (int m = 0; m < p.M; ++m) {
     float2 v[2];
 #pragma unroll
@@ -459,41 +437,7 @@ __device__ __forceinline__ bool finish_block(const DecodeParams& p, int unit, in
       }
     }
     const int n0 = lb * 64 + 2 * lane;
-    if (p.cv.reduce) {
-      // row-parallel shard: push this rank's fp16 partial of the two columns to every rank, then add up the
-      // words of all ranks that arrived in this GPU's own block (rank order, fp32: same bits everywhere)
-      const __half2 hv = __floats2half2_rn(v[0].x, v[0].y);
-      const size_t word = (size_t)unit * kFuseBlockWords + (size_t)m * 32 + lane;
-      const size_t per_rank = (size_t)p.cv.block_cap * kFuseBlockWords;
-      const size_t par = (size_t)(repoch & 1u) * p.cv.world;
-      for (int r = 0; r < p.cv.world; ++r)
-        st_word_sys(reinterpret_cast<uint2*>(p.cv.bufs[r] + p.cv.reduce_off) + (par + p.cv.rank) * per_rank + word,
-                    *reinterpret_cast<const uint32_t*>(&hv), repoch);
-      float2 sum = make_float2(0.f, 0.f);
-      for (int r = 0; r < p.cv.world; ++r) {
-        const uint2* src = reinterpret_cast<const uint2*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_off) + (par + r) * per_rank + word;
-        uint2 wv = ld_word_sys(src);
-        int spin = 0;
-        while (wv.y != repoch && ok) {
-          if (++spin > kSpinLimit) { ok = false; break; }
-          wv = ld_word_sys(src);
-        }
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv.x));
-        sum.x += f.x;
-        sum.y += f.y;
-      }
-      v[0] = sum;
-    }
-    store_pair(p, pr, pr2, m, n0, v[0], v[1], swiglu, gepoch);
-  }
-  if (p.cv.reduce || p.cv.gather_out) {
-    __syncwarp();
-    if (lane == 0) {
-      if (p.cv.reduce)
-        *reinterpret_cast<volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_epoch_off + 4 * (size_t)unit) = repoch;
-      if (p.cv.gather_out)
-        *reinterpret_cast<volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off + 4 * (size_t)unit) = gepoch;
-    }
+    store_pair(p, pr, pr2, m, n0, v[0], v[1], swiglu);
   }
   return ok;
 }
@@ -501,9 +445,7 @@ __device__ __forceinline__ bool finish_block(const DecodeParams& p, int unit, in
 // Hadamard prologue of a CTA: forms, in shared memory, the segments of  H a / sqrt(dim)  that the CTA's slots multiply
 // with (nseg consecutive segments from global segment seg0 + c_first, every batch row), rounded to fp16.
 // dim = Mdim x P with commuting factors: segment s of the result is the P-point Walsh-Hadamard transform of
-// sum_a' sign(s, a') a[a' P .. a' P + P).  FEAT: the row comes from this rank's feature area (epoch-tagged words written
-// by all ranks, bounded poll) instead of A.  Returns false if a poll gave up.
-template <bool FEAT>
+// sum_a' sign(s, a') a[a' P .. a' P + P).  Returns false if a wait gave up (none in this version).
 __device__ __noinline__ bool hadamard_prologue(const DecodeParams& p, uint8_t* area, uint32_t* s_mask, int c_first,
                                                int nseg, int nthreads) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -526,14 +468,6 @@ __device__ __noinline__ bool hadamard_prologue(const DecodeParams& p, uint8_t* a
     }
   }
   __syncthreads();
-  // epoch the feature words of this call carry: this rank's own column shard was produced by the launch before
-  uint32_t in_epoch = 0;
-  const uint2* feat = nullptr;
-  if (FEAT) {
-    in_epoch = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off);
-    feat = reinterpret_cast<const uint2*>(p.cv.bufs[p.cv.rank] + p.cv.gather_off) +
-           (size_t)(in_epoch & 1u) * 16 * (size_t)(p.cv.feat_cap >> 1);
-  }
   // z[seg][row][b] = sum_a' sign(seg, a') a[row][a' P + b]: a thread owns two adjacent b of one row and, when there
   // are threads to spare (one batch row), every `nsplit`-th source segment; the split sums meet in shared memory
   const int nitems = p.M * half_p;
@@ -548,28 +482,10 @@ __device__ __noinline__ bool hadamard_prologue(const DecodeParams& p, uint8_t* a
     constexpr int NB = 16;                   // source segments fetched per round trip
     for (int a0 = split; a0 < p.hMdim; a0 += NB * nsplit) {
       uint32_t hv[NB];
-      if (!FEAT) {
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.A + (size_t)row * p.lda) + cp;
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(p.A + (size_t)row * p.lda) + cp;
 #pragma unroll
-        for (int i = 0; i < NB; ++i)
-          if (a0 + i * nsplit < p.hMdim) hv[i] = __ldcg(src + (size_t)(a0 + i * nsplit) * half_p);
-      } else {
-        const uint2* src = feat + (size_t)row * (size_t)(p.cv.feat_cap >> 1) + cp;
-        uint2 wv[NB];
-#pragma unroll
-        for (int i = 0; i < NB; ++i)
-          if (a0 + i * nsplit < p.hMdim) wv[i] = ld_word_sys(src + (size_t)(a0 + i * nsplit) * half_p);
-#pragma unroll
-        for (int i = 0; i < NB; ++i)
-          if (a0 + i * nsplit < p.hMdim) {
-            int spin = 0;
-            while (wv[i].y != in_epoch && ok) {
-              if (++spin > kSpinLimit) { ok = false; break; }
-              wv[i] = ld_word_sys(src + (size_t)(a0 + i * nsplit) * half_p);
-            }
-            hv[i] = wv[i].x;
-          }
-      }
+      for (int i = 0; i < NB; ++i)
+        if (a0 + i * nsplit < p.hMdim) hv[i] = __ldcg(src + (size_t)(a0 + i * nsplit) * half_p);
 #pragma unroll
       for (int i = 0; i < NB; ++i)
         if (a0 + i * nsplit < p.hMdim) {
@@ -784,10 +700,7 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) w4a16_decode_kernel(const __
       const int c_last = slot_decode(p.G, cs1 - 1).c;
       int nseg = c_last - c_first + 1;
       if (nseg > kMaxSeg) nseg = kMaxSeg;                 // excluded by the host plan
-      bool ok;
-      if (p.cv.gather_in) ok = hadamard_prologue<true>(p, smem_raw + (xarea - smem_base), &s_mask[0][0], c_first, nseg, WARPS * 32);
-      else ok = hadamard_prologue<false>(p, smem_raw + (xarea - smem_base), &s_mask[0][0], c_first, nseg, WARPS * 32);
-      if (!ok) timed_out = true;
+      if (!hadamard_prologue(p, smem_raw + (xarea - smem_base), &s_mask[0][0], c_first, nseg, WARPS * 32)) timed_out = true;
     }
   }
   // one commit group per ring slot, empty ones included: the group of slot i is then always followed by exactly
@@ -1123,12 +1036,12 @@ size_t decode_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, i
   return total > tiled ? total : tiled;
 }
 
-// Which decode kernel runs a launch.  Both take every launch (grouped, SwiGLU, residual, the tensor-parallel
-// exchanges); the CTA-tiled kernel of w4a16_gemv.cu is the default because its reduction stays inside the CTA or the
-// cluster and a launch costs about half as much.  UNIQL_B200_DECODE_ENGINE=slot selects the slot-balanced kernel of
-// this file (tests, profiling), which also runs the Hadamard transform in its own prologue.
+// Which decode kernel runs a launch.  The CTA-tiled kernel of w4a16_gemv.cu is the default: its reduction stays inside
+// the CTA or the cluster and a launch costs about half as much; it also carries the tensor-parallel exchanges.
+// UNIQL_B200_DECODE_ENGINE=slot selects the slot-balanced kernel of this file for single-GPU launches (tests,
+// profiling); that kernel runs an online Hadamard transform in its own prologue.
 static bool use_slot_engine(const DecodeArgs& a) {
-  (void)a;
+  if (a.comm) return false;
   const char* e = getenv("UNIQL_B200_DECODE_ENGINE");
   return e && e[0] == 's';
 }
@@ -1203,8 +1116,7 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   DecodePlan pl;
   int st = cached_plan(&pl, a.m, a.k, n, a.nproj, a.epilogue, a.hadamard_dim, a.k_offset);
   if (st != UNIQL_OK) return st;
-  const CommView* cv = a.comm;
-  if (cv && cv->gather_in && !pl.fused_had) return UNIQL_ESHAPE;     // the feature area is read by the prologue only
+  if (a.comm) return UNIQL_EINVAL;       // launches that talk to other GPUs run on the CTA-tiled kernel
   const size_t part_off = UNIQL_SCRATCH_COUNTER_BYTES;
   const size_t xh_off = part_off + align256(pl.partial_bytes);
   const size_t need = xh_off + ((a.hadamard_dim && !pl.fused_had) ? align256((size_t)a.m * a.hadamard_dim * 2) : 0);
@@ -1262,13 +1174,6 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
       p.pf_lines[p.npf] = (long long)(a.prefetch_bytes[i] / 128);
       ++p.npf;
     }
-  if (cv) {
-    p.cv = *cv;
-    if (cv->reduce && pl.units > cv->block_cap) return UNIQL_ESHAPE;
-    if (cv->gather_out && (cv->col_offset % 64 || cv->col_offset + (int64_t)pl.units * 64 > cv->feat_cap)) return UNIQL_ESHAPE;
-    if (cv->gather_in && a.hadamard_dim > cv->feat_cap) return UNIQL_ESHAPE;
-    if (cv->reduce && a.epilogue != UNIQL_EPILOGUE_NONE) return UNIQL_EINVAL;
-  }
   if (pl.fused_had) {
     if (pl.variant == 0) return launch_variant<1, 16, 1, true, 3>(p, pl, stream);
     if (pl.variant == 3) return launch_variant<1, 8, 2, true, 2>(p, pl, stream);
