@@ -282,7 +282,8 @@ def _triple(mod):
 
 def make_step(stack, world, rank, group, mode="none", comm=None, taps=None):
     """Returns step(x) -> y running the projections of every layer: qkv -> o -> [gate, up, SwiGLU] -> Hadamard -> down
-    (no attention maths: the q shard stands in for the attention output).  Four launches per layer at decode sizes.
+    (no attention maths: the q shard stands in for the attention output).  Five launches per layer at decode sizes
+    (qkv, o, gate+up with SwiGLU, Hadamard, down).
     mode (world > 1): "fused" = cross-GPU sums and the feature gather inside the decode kernels, "push" = separate
     push all-reduce kernels, "nccl" = torch.distributed collectives.  taps: list that receives the two row-parallel
     outputs (o_proj, down_proj) of every layer."""
@@ -309,7 +310,7 @@ def make_step(stack, world, rank, group, mode="none", comm=None, taps=None):
             if world == 1:
                 y = mods["o"](att)
                 h = fz.gate_up_swiglu(mods["gate"], mods["up"], y)
-                x = mods["down"](h)                        # Hadamard in the kernel prologue
+                x = mods["down"](h)                        # Hadamard kernel + linear, chained by dependent launch
             elif mode == "fused" and m <= 16:
                 o, d = mods["o"], mods["down"]
                 y = comm.linear_all_reduce(att, o.weight, o.scale, None, o.out_features)
@@ -576,7 +577,10 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    launches_per_layer = 4 if (m <= 16 and (world == 1 or collective == "fused")) else None
+    # qkv, o, gate+up (SwiGLU in the epilogue), Hadamard, down: the cross-GPU sums and the feature gather ride in the
+    # linears' epilogues, the Hadamard kernel of a tensor-parallel layer reads the gathered row directly
+    # (larger batches: q, k, v, o, gate, up, Hadamard, down on the tensor-core kernels; SiLU * up is PyTorch's)
+    launches_per_layer = 5 if m <= 16 else 8
     parity = None
     with torch.cuda.stream(stream):
         # ---- tensor parallel: check the sharded result before timing anything ----
@@ -808,11 +812,11 @@ def run_ours(args):
             "pct_of_hbm_peak": {"of_measured_%.0f" % peak: nbytes / world / t_step / 1e9 / peak,
                                 "of_nominal_8000": nbytes / world / t_step / 1e9 / 8000.0},
             "roofline": {"bound": "hbm",
-                         "kernel": f"w4a16_decode_kernel, gate+up 2x{n_gate}x{HIDDEN} with SwiGLU epilogue, m={m}",
+                         "kernel": f"w4a16_gemv_kernel, gate+up 2x{n_gate}x{HIDDEN} with SwiGLU epilogue, m={m}",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "us_per_launch": pair_us, "bytes_per_launch": pair_bytes,
                          "traffic": NCU_TRAFFIC_GATE_UP_M1 if (world == 1 and m == 1) else None},
-            "single_projection": {"kernel": f"w4a16_decode_kernel, gate {n_gate}x{HIDDEN}, m={m}", "us_per_launch": gate_us,
+            "single_projection": {"kernel": f"w4a16_gemv_kernel, gate {n_gate}x{HIDDEN}, m={m}", "us_per_launch": gate_us,
                                   "gbs": linear_bytes(n_gate, HIDDEN, m) / (gate_us * 1e-6) / 1e9,
                                   "frac_of_hbm_peak": linear_bytes(n_gate, HIDDEN, m) / (gate_us * 1e-6) / 1e9 / peak},
             "step_percentiles": pct,

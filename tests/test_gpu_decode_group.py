@@ -16,8 +16,8 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(params=["tiled", "slot"], autouse=True)
 def engine(request, monkeypatch):
-    """Both decode kernels take every grouped launch: the CTA-tiled one (default on one GPU) and the slot-balanced one
-    (the kernel tensor-parallel launches use; UNIQL_B200_DECODE_ENGINE=slot selects it here)."""
+    """Both decode kernels take every grouped launch: the CTA-tiled one (the default, and the only one tensor-parallel
+    launches use) and the slot-balanced one (single GPU; UNIQL_B200_DECODE_ENGINE=slot selects it here)."""
     if request.param == "slot":
         monkeypatch.setenv("UNIQL_B200_DECODE_ENGINE", "slot")
     else:
