@@ -178,6 +178,16 @@ int uniql_w4a16_dequantize_rows(const void* packed, const void* scales, int64_t 
  * base in {12, 20, 28, 40}; `out` is a HOST pointer.  Returns UNIQL_ESHAPE for other orders. */
 int uniql_hadamard_base_matrix(int base, int8_t* out);
 
+/* Host call: replaces the order-`base` matrix (12, 20, 28 or 40) used by every transform launched afterwards in this
+ * process -- uniql_hadamard, the hadamard_dim argument of the linears, uniql_hadamard_base_matrix.  `h` is a HOST
+ * pointer to base*base entries of +1 / -1, row-major, y[a'] = sum_a h[a'*base + a] x[a] on the slow index of
+ * i = a * 2^j + b; it is checked for H H^T = base I (UNIQL_EINVAL otherwise).  NULL restores the built-in matrix.
+ * The reference takes these matrices from the third-party package fast-hadamard-transform
+ * (quantize/hadamard_helpers.py:18-36); a holder of that package's tables passes them here to get its results.
+ * Decode-size launches (<= 16 rows) keep their speed; transforms of many rows of a replaced order run on a plainer
+ * kernel. */
+int uniql_hadamard_set_base_matrix(int base, const int8_t* h);
+
 /*
  * One-shot push all-reduce (sum) of fp16 vectors across the GPUs of one node, for the row-parallel linears of a
  * tensor-parallel model at decode sizes.  No counterpart in the reference (it is single-GPU).  One process per GPU.

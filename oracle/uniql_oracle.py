@@ -319,8 +319,9 @@ def fwht(x: np.ndarray) -> np.ndarray:
     return y.reshape(x.shape)
 
 
-def hadamard_transform(x: np.ndarray, scale: float | None = None) -> np.ndarray:
-    """y = (H_base (x) H_{2^k}) x * scale along the last axis, float64 result.
+def hadamard_transform(x: np.ndarray, scale: float | None = None, base_h: np.ndarray | None = None) -> np.ndarray:
+    """y = (H_base (x) H_{2^k}) x * scale along the last axis, float64 result.  `base_h` replaces this build's
+    choice of base matrix (for a caller who holds the third-party package's tables).
 
     The index splits as i = a * 2^k + b with a the base-matrix index (slow) and
     b the Sylvester index (fast).  scale defaults to 1/sqrt(dim)
@@ -333,6 +334,7 @@ def hadamard_transform(x: np.ndarray, scale: float | None = None) -> np.ndarray:
         return fwht(x) * scale
     p = dim // base
     y = fwht(x.reshape(*x.shape[:-1], base, p))
-    hb = base_matrix(base).astype(np.float64)
+    hb = (base_matrix(base) if base_h is None else np.asarray(base_h)).astype(np.float64)
+    assert hb.shape == (base, base)
     y = np.einsum("ij,...jp->...ip", hb, y)
     return y.reshape(x.shape) * scale

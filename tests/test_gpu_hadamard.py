@@ -108,6 +108,31 @@ def test_fused_hadamard_linear(n, k, m):
     linear_tolerance_check(y, y2.astype(np.float32))
 
 
+@pytest.mark.parametrize("n,k,m", [(4096, 14336, 1024), (4096, 14336, 4096), (4096, 8192, 2048)])
+def test_fused_hadamard_linear_prefill_sampled_rows(n, k, m):
+    """down_proj / out_proj with their online transform at prefill sizes: full-size launch, 40 seeded rows against the
+    oracle (transform in float64, rounded to fp16, then the fp32 linear), the other rows through the column-sum
+    identity sum_rows(y) = (sum_rows(fp16(H x))) W."""
+    from uniql_b200 import ops
+    layer = quantized_layer(n + k + 3, n, k)
+    x = make_acts(m + 11, m, k)
+    packed, scales = torch.from_numpy(layer["packed"]).cuda(), torch.from_numpy(layer["scales"]).cuda()
+    y = ops.w4a16_linear(x.cuda(), packed, scales, None, n, hadamard_dim=k)
+    torch.cuda.synchronize()
+    y = y.cpu().numpy()
+    rng = np.random.default_rng(m + k)
+    rows = np.sort(rng.choice(m, size=40, replace=False))
+    rows[0], rows[-1] = 0, m - 1
+    xh = orc.hadamard_transform(x.double().numpy()[rows]).astype(np.float16)
+    linear_tolerance_check(y[rows], orc.linear_ref(xh, None, None, None, n, w_deq=layer["w_deq"]))
+    xh_all = ops.hadamard(x.cuda(), 1.0 / np.sqrt(k)).float().sum(0, keepdim=True).cpu().numpy()
+    col_ref = orc.linear_ref(xh_all, None, None, None, n, w_deq=layer["w_deq"])
+    col_sum = y.astype(np.float64).sum(0, keepdims=True)
+    tol = 2.0 ** -10 * np.abs(y).astype(np.float64).sum(0, keepdims=True) + 1e-3
+    assert (np.abs(col_sum - col_ref) <= tol).all()
+    assert ops.read_and_clear_status("cuda") == 0
+
+
 def test_had_linear_offline_rotation_matches_online():
     """HadLinear folds H into the weight; y = x W^T must equal (xH)(WH)^T."""
     from uniql_b200.quantize.quant_linear_layers import HadLinear
@@ -117,3 +142,46 @@ def test_had_linear_offline_rotation_matches_online():
     x = torch.randn(4, 512, device="cuda", dtype=torch.float16)
     y = had(ops.hadamard(x, 1.0 / np.sqrt(512)))
     assert torch.allclose(y.float(), (x.float() @ lin.weight.float().t()), atol=3e-2)
+
+
+@pytest.mark.parametrize("dim", [12 * 512, 20 * 256, 28 * 512, 40 * 256, 28 * 64, 12 * 8])
+def test_replaced_base_matrix_is_used_by_every_path(dim):
+    """uniql_hadamard_set_base_matrix: with another Hadamard matrix of the same order installed, the few-row kernel,
+    the many-row kernel, the fused linear (both decode kernels) and the exported matrix all follow it; results
+    against the oracle fed the same matrix.  The built-in matrix is restored afterwards."""
+    from uniql_b200 import ops
+    base = orc.had_factor(dim)
+    h0 = orc.base_matrix(base)
+    rng = np.random.default_rng(dim)
+    h1 = h0[rng.permutation(base)][:, rng.permutation(base)] * rng.choice([-1, 1], size=(base, 1)) * rng.choice([-1, 1], size=(1, base))
+    assert not np.array_equal(h0, h1)
+    try:
+        ops.hadamard_set_base_matrix(base, h1)
+        for rows, dtype in ((1, torch.float16), (5, torch.float32), (16, torch.float16), (70, torch.float32), (300, torch.bfloat16)):
+            x = torch.randn(rows, dim, generator=torch.Generator().manual_seed(rows)).to(dtype)
+            y = ops.hadamard(x.cuda(), dim ** -0.5)
+            want = orc.hadamard_transform(x.double().numpy(), base_h=h1)
+            tol = {torch.float32: 2e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dtype]
+            assert np.abs(y.double().cpu().numpy() - want).max() <= tol * max(1.0, np.abs(want).max())
+            wrong = orc.hadamard_transform(x.double().numpy())
+            assert np.abs(y.double().cpu().numpy() - wrong).max() > 0.05       # and it is not the built-in transform
+        if dim >= 1024:
+            import os
+            n, layer = 256, quantized_layer(dim, 256, dim)
+            packed, scales = torch.from_numpy(layer["packed"]).cuda(), torch.from_numpy(layer["scales"]).cuda()
+            for m in (1, 4, 16, 40):
+                x = make_acts(m, m, dim)
+                xh = orc.hadamard_transform(x.double().numpy(), base_h=h1).astype(np.float16)
+                want = orc.linear_ref(xh, None, None, None, n, w_deq=layer["w_deq"])
+                for engine in ("tiled", "slot"):
+                    os.environ["UNIQL_B200_DECODE_ENGINE"] = engine
+                    try:
+                        y = ops.w4a16_linear(x.cuda(), packed, scales, None, n, hadamard_dim=dim).cpu().numpy()
+                    finally:
+                        del os.environ["UNIQL_B200_DECODE_ENGINE"]
+                    linear_tolerance_check(y, want)
+    finally:
+        ops.hadamard_set_base_matrix(base, None)
+    x = torch.randn(3, dim, generator=torch.Generator().manual_seed(3))
+    y = ops.hadamard(x.cuda(), dim ** -0.5)
+    assert np.abs(y.double().cpu().numpy() - orc.hadamard_transform(x.double().numpy())).max() <= 2e-5 * 4

@@ -186,6 +186,24 @@ def test_baseline_shapes_prefill_sampled_rows(n, k, m):
     assert (np.abs(col_sum - col_ref) <= tol).all()
 
 
+@pytest.mark.parametrize("n,k", [(12160, 4096), (4096, 12160), (3584, 4096), (4096, 3584), (896, 4096)])
+def test_sliced_llama_shapes_at_2048_rows(n, k):
+    """The 85 % Llama-3.1-8B layers (intermediate 12160, head_dim 112) at the 2048-row prefill of that configuration:
+    sampled rows against the oracle, all rows through the column-sum identity."""
+    m = 2048
+    layer = quantized_layer(n + k + 85, n, k)
+    x = make_acts(m + 5, m, k)
+    y = _run(layer, x)
+    rng = np.random.default_rng(n * 3 + k)
+    rows = np.sort(rng.choice(m, size=48, replace=False))
+    rows[0], rows[-1] = 0, m - 1
+    linear_tolerance_check(y[rows], orc.linear_ref(x.numpy()[rows], None, None, None, n, w_deq=layer["w_deq"]))
+    col_ref = orc.linear_ref(x.float().sum(0, keepdim=True).numpy(), None, None, None, n, w_deq=layer["w_deq"])
+    col_sum = y.astype(np.float64).sum(0, keepdims=True)
+    tol = 2.0 ** -10 * np.abs(y).astype(np.float64).sum(0, keepdims=True) + 1e-3
+    assert (np.abs(col_sum - col_ref) <= tol).all()
+
+
 # ---------------------------------------------------------------------------------------------
 # batches of 17..128 rows: operand-swapped tcgen05 kernel, with a cluster split over k when there are few column tiles
 # ---------------------------------------------------------------------------------------------

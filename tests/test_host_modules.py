@@ -179,3 +179,33 @@ def test_library_base_matrix_equals_oracle(built_lib, base):
     got = np.frombuffer(buf, dtype=np.int8).reshape(base, base)
     assert np.array_equal(got, orc.base_matrix(base))
     assert lib().uniql_hadamard_base_matrix(16, buf) == -3
+
+
+def test_base_matrix_can_be_replaced_and_is_validated(built_lib):
+    """uniql_hadamard_set_base_matrix: a row/column-permuted, sign-flipped copy is still a Hadamard matrix and is
+    accepted; broken ones are refused and leave the current matrix in place; NULL restores the built-in one."""
+    from oracle import uniql_oracle as orc
+    from uniql_b200 import UniqlError, ops
+    for base in (12, 20, 28, 40):
+        h0 = orc.base_matrix(base)
+        rng = np.random.default_rng(base)
+        h1 = h0[rng.permutation(base)][:, rng.permutation(base)] * rng.choice([-1, 1], size=(base, 1)) * rng.choice([-1, 1], size=(1, base))
+        try:
+            ops.hadamard_set_base_matrix(base, h1)
+            assert np.array_equal(ops.hadamard_base_matrix(base).numpy(), h1)
+            bad = h1.copy()
+            bad[1, 2] = -bad[1, 2]
+            with pytest.raises(UniqlError):
+                ops.hadamard_set_base_matrix(base, bad)                       # rows no longer orthogonal
+            zero = h1.copy()
+            zero[0, 0] = 0
+            with pytest.raises(UniqlError):
+                ops.hadamard_set_base_matrix(base, zero)                      # entries must be +1 / -1
+            assert np.array_equal(ops.hadamard_base_matrix(base).numpy(), h1)  # refused calls change nothing
+        finally:
+            ops.hadamard_set_base_matrix(base, None)
+        assert np.array_equal(ops.hadamard_base_matrix(base).numpy(), h0)
+    with pytest.raises(UniqlError):
+        ops.hadamard_set_base_matrix(16, np.ones((16, 16)))
+    with pytest.raises(RuntimeError):
+        ops.hadamard_set_base_matrix(12, np.ones((11, 12)))

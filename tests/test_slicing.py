@@ -227,3 +227,67 @@ def test_checkpoint_walker_applies_every_slicer(gold):
     _same(sd["model.layers.0.self_attn.q_proj.bias"], gold["qk_bias"])
     assert "model.layers.0.self_attn.k_proj.bias" not in sd
     assert torch.equal(sd["model.layers.0.self_attn.indices"], mh.slice_indices(idx, HD, RHD))
+
+
+@pytest.mark.gpu
+def test_llama_8b_sized_layers_sliced_on_the_gpu_keep_their_weights():
+    """Llama-3.1-8B layers cut to the 85 % model (intermediate 14336 -> 12160, head_dim 128 -> 112), on the GPU.  At this
+    size the CPU re-pack takes minutes, so the check is a property that holds at any size: dequantising a sliced layer
+    gives, bit for bit, the kept rows and columns of the dequantised original (column slices keep codes and scales;
+    the row slice of o_proj re-quantises, so there the sliced layer is compared with a second quantisation of the kept
+    rows and its checksum with the checksum of the device-side quantiser run directly)."""
+    from uniql_b200 import ops
+    hidden, inter, red, nheads, nkv, hd, rhd = 4096, 14336, 12160, 32, 8, 128, 112
+    gen = torch.Generator(device="cuda").manual_seed(85)
+
+    def layer(n, k):
+        w = (torch.randn(n, k, generator=gen, device="cuda") * 0.02).half()
+        _, packed, scale = ops.w4a16_quantize(w, want_ref=False)
+        return packed, scale, torch.zeros(packed.shape[1] // 2 // 64 * 16, dtype=torch.int32, device="cuda")
+
+    def deq(packed, scale, n):
+        k = packed.shape[0] * 16
+        return ops.w4a16_dequantize_rows(packed, scale, torch.arange(k), n)          # fp16 [n, k]
+
+    def same(a, b):
+        return torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+    # gate / up: column prefix
+    p, s, ws = layer(inter, hidden)
+    p2, s2, ws2 = mh.slice_w4a16_up_gate_proj(p, s, ws, hidden, inter, red, p.shape)
+    assert p2.shape == (hidden // 16, 2 * red) and s2.shape == (hidden // 128, red) and ws2.numel() == red // 64 * 16
+    assert same(deq(p2, s2, red), deq(p, s, inter)[:red])
+    # down: row prefix
+    p, s, ws = layer(hidden, inter)
+    p2, s2, _ = mh.slice_w4a16_down_proj(p, s, ws, hidden, inter, red, p.shape)
+    assert p2.shape == (red // 16, 2 * hidden) and s2.shape == (red // 128, hidden)
+    assert same(deq(p2, s2, hidden), deq(p, s, hidden)[:, :red])
+    # q (32 heads) and k (8 heads): leading channels of both rotary halves of every head
+    for heads in (nheads, nkv):
+        p, s, ws = layer(heads * hd, hidden)
+        bias = torch.arange(heads * hd, device="cuda", dtype=torch.float16)
+        p2, b2, s2, ws2 = mh.slice_w4a16_qk_proj(p, bias, s, ws, hidden, heads, hd, rhd, p.shape)
+        idx = mh._rotary_half_indices(heads, hd, rhd).cuda()
+        n_keep = heads * rhd
+        n_pad = (n_keep + 255) // 256 * 256
+        assert p2.shape == (hidden // 16, 2 * n_pad) and ws2.numel() == n_pad // 64 * 16
+        assert same(deq(p2, s2, n_keep), deq(p, s, heads * hd)[idx]) and torch.equal(b2, bias[idx])
+        if n_pad > n_keep:                                       # padded columns carry zero scales
+            assert float(deq(p2, s2, n_pad)[n_keep:].abs().max()) == 0.0
+    # v: first 112 channels of every head
+    p, s, ws = layer(nkv * hd, hidden)
+    p2, s2, _ = mh.slice_w4a16_v_proj(p, s, ws, hidden, nkv, hd, rhd, p.shape)
+    idx = mh.get_topk_head_indices(1, nkv, hd, rhd).cuda()
+    assert same(deq(p2, s2, nkv * rhd), deq(p, s, nkv * hd)[idx])
+    # o: keep 112 of 128 input rows per head -> groups change -> dequantise, quantise again
+    p, s, ws = layer(hidden, nheads * hd)
+    p2, s2, _ = mh.slice_w4a16_o_proj(p, s, ws, hidden, nheads, hd, rhd, p.shape)
+    idx = mh.get_topk_head_indices(1, nheads, hd, rhd).cuda()
+    kept = deq(p, s, hidden)[:, idx].contiguous()                                    # fp16 [4096, 3584]
+    _, want_p, want_s = ops.w4a16_quantize(kept, want_ref=False)
+    assert p2.shape == (nheads * rhd // 16, 2 * hidden) and torch.equal(p2, want_p) and same(s2, want_s)
+    assert int(p2.long().sum()) == int(want_p.long().sum())
+    # re-quantising moves every weight by at most half a step of its new group scale
+    step = ops.w4a16_dequantize_rows(torch.full_like(p2, 0x99999999 - (1 << 32)), s2, torch.arange(nheads * rhd), hidden)
+    assert bool(((deq(p2, s2, hidden).float() - kept.float()).abs() <= 0.5 * step.float().abs() + 1e-6).all())
+    assert ops.read_and_clear_status("cuda") == 0

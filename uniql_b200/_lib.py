@@ -58,6 +58,7 @@ SYMBOLS = {
     "uniql_hadamard": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_float, _c.c_int, _c.c_void_p]),
     "uniql_hadamard_base_matrix": (_c.c_int, [_c.c_int, _c.c_void_p]),
+    "uniql_hadamard_set_base_matrix": (_c.c_int, [_c.c_int, _c.c_void_p]),
     "uniql_w4a16_gather_columns": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p,
         _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p]),

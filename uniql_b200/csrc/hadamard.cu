@@ -16,6 +16,7 @@
 #include "linear_internal.cuh"
 
 #include <stdlib.h>
+#include <mutex>
 #include <type_traits>
 #include <utility>
 
@@ -72,19 +73,64 @@ __host__ __device__ constexpr int c_base_entry(int base, int i, int j) {
   return (i >= 20 && j >= 20) ? -v : v;
 }
 
+// A caller may replace a base matrix at run time (uniql_hadamard_set_base_matrix): whoever holds the matrices of the
+// third-party package the reference links can make every transform of this library use them without a rebuild.  The
+// few-row kernels and the linear kernel's prologue take their signs as launch parameters and follow at full speed;
+// the many-row kernels have the built-in signs compiled in, so sizes of a replaced order go to hadamard_rt_kernel.
+static std::mutex g_base_mu;
+static bool g_base_custom[4] = {false, false, false, false};
+static int8_t g_base_h[4][1600];
+static int base_slot(int base) { return base == 12 ? 0 : base == 20 ? 1 : base == 28 ? 2 : base == 40 ? 3 : -1; }
+
+static bool base_is_custom(int base) {
+  const int s = base_slot(base);
+  if (s < 0) return false;
+  std::lock_guard<std::mutex> lk(g_base_mu);
+  return g_base_custom[s];
+}
+
 static int base_matrix(int base, int8_t* h) {
-  if (base != 12 && base != 20 && base != 28 && base != 40) return UNIQL_ESHAPE;
+  const int s = base_slot(base);
+  if (s < 0) return UNIQL_ESHAPE;
+  {
+    std::lock_guard<std::mutex> lk(g_base_mu);
+    if (g_base_custom[s]) {
+      for (int i = 0; i < base * base; ++i) h[i] = g_base_h[s][i];
+      return UNIQL_OK;
+    }
+  }
   for (int i = 0; i < base; ++i)
     for (int j = 0; j < base; ++j) h[i * base + j] = (int8_t)c_base_entry(base, i, j);
   return UNIQL_OK;
 }
 
+static int set_base_matrix(int base, const int8_t* h) {
+  const int s = base_slot(base);
+  if (s < 0) return UNIQL_ESHAPE;
+  if (h) {
+    for (int i = 0; i < base * base; ++i)
+      if (h[i] != 1 && h[i] != -1) return UNIQL_EINVAL;
+    for (int i = 0; i < base; ++i)
+      for (int j = 0; j < base; ++j) {
+        int dot = 0;
+        for (int t = 0; t < base; ++t) dot += h[i * base + t] * h[j * base + t];
+        if (dot != (i == j ? base : 0)) return UNIQL_EINVAL;      // rows must be orthogonal: H H^T = base I
+      }
+  }
+  std::lock_guard<std::mutex> lk(g_base_mu);
+  g_base_custom[s] = h != nullptr;
+  if (h)
+    for (int i = 0; i < base * base; ++i) g_base_h[s][i] = h[i];
+  return UNIQL_OK;
+}
+
 void hadamard_base_signs(int base, unsigned long long* rows40) {
   for (int i = 0; i < 40; ++i) rows40[i] = 0ull;
-  if (base != 12 && base != 20 && base != 28 && base != 40) return;
+  int8_t h[1600];
+  if (base_matrix(base, h) != UNIQL_OK) return;
   for (int i = 0; i < base; ++i)
     for (int j = 0; j < base; ++j)
-      if (c_base_entry(base, i, j) < 0) rows40[i] |= (1ull << j);
+      if (h[i * base + j] < 0) rows40[i] |= (1ull << j);
 }
 
 static bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
@@ -437,6 +483,56 @@ __global__ void __launch_bounds__(256) hadamard_rows32_kernel(const T* __restric
   else base_pass<T, 40, true>(buf, yr, P, scale, tid, nthreads);
 }
 
+// Many rows with a base matrix given at run time: one CTA per row, the row as fp32 in shared memory, radix-2 passes
+// over the power-of-two part, then per column b the base x base signed sums with the signs read from the launch
+// parameters.  Plain and a few times slower than the kernels with compiled-in signs; it exists so that a replaced
+// base matrix is honoured at every size.
+template <typename T>
+__global__ void __launch_bounds__(256) hadamard_rt_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y,
+                                                          int64_t ldy, int dim, int P, int base, float scale,
+                                                          const HadSigns signs, int pdl_trigger) {
+  extern __shared__ __align__(16) float rt_buf[];
+  if (pdl_trigger) pdl_launch_dependents();
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const T* xr = x + (int64_t)blockIdx.x * ldx;
+  T* yr = y + (int64_t)blockIdx.x * ldy;
+  for (int c = tid; c < dim / 8; c += nt) {
+    float t[8];
+    Elem<T>::load8(xr + (size_t)c * 8, t);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) rt_buf[c * 8 + e] = t[e];
+  }
+  __syncthreads();
+  for (int h = 1; h < P; h <<= 1) {
+    for (int idx = tid; idx < dim / 2; idx += nt) {
+      const int i = (idx / h) * 2 * h + (idx % h);
+      const float a = rt_buf[i], b = rt_buf[i + h];
+      rt_buf[i] = a + b;
+      rt_buf[i + h] = a - b;
+    }
+    __syncthreads();
+  }
+  for (int b = tid; b < P; b += nt) {
+    float v[40];
+#pragma unroll
+    for (int a = 0; a < 40; ++a) v[a] = a < base ? rt_buf[(size_t)a * P + b] : 0.f;
+    for (int ap = 0; ap < base; ++ap) {
+      const uint64_t mask = signs.row[ap];
+      float acc = 0.f;
+#pragma unroll
+      for (int a = 0; a < 40; ++a) acc += ((mask >> a) & 1ull) ? -v[a] : v[a];
+      rt_buf[(size_t)ap * P + b] = acc * scale;      // column b belongs to this thread alone
+    }
+  }
+  __syncthreads();
+  for (int c = tid; c < dim / 8; c += nt) {
+    float t[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) t[e] = rt_buf[c * 8 + e];
+    Elem<T>::store8(yr + (size_t)c * 8, t);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict__ x, int64_t ldx,
                                                              T* __restrict__ y, int64_t ldy, int P, int B,
@@ -670,6 +766,35 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
     }
   }
 
+  // ---- a base matrix replaced at run time: the kernels below have the built-in signs compiled in ----
+  if (base > 1 && base_is_custom(base)) {
+    for (int i = 0; i < base; ++i)
+      for (int j = 0; j < base; ++j)
+        if (h[i * base + j] < 0) signs.row[i] |= (1ull << j);
+    const size_t smem = (size_t)dim * sizeof(float);
+#define UNIQL_HAD_RT_LAUNCH(T)                                                                                \
+  do {                                                                                                        \
+    static thread_local bool attr_done[64] = {};   /* function attributes are per device */                   \
+    if (!attr_done[cur_dev]) {                                                                                \
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(hadamard_rt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                          40960 * (int)sizeof(float)));                                       \
+      attr_done[cur_dev] = true;                                                                              \
+    }                                                                                                         \
+    for (int64_t r0 = 0; r0 < rows; r0 += (int64_t)1 << 30) {                                                 \
+      const int64_t nr = rows - r0 < ((int64_t)1 << 30) ? rows - r0 : ((int64_t)1 << 30);                     \
+      hadamard_rt_kernel<T><<<(unsigned)nr, 256, smem, stream>>>((const T*)x + r0 * ldx, ldx, (T*)y + r0 * ldy, ldy, \
+                                                                 (int)dim, (int)P, base, scale, signs,        \
+                                                                 pdl_trigger ? 1 : 0);                        \
+    }                                                                                                         \
+  } while (0)
+    if (dtype == UNIQL_F16) UNIQL_HAD_RT_LAUNCH(__half);
+    else if (dtype == UNIQL_BF16) UNIQL_HAD_RT_LAUNCH(__nv_bfloat16);
+    else if (dtype == UNIQL_F32) UNIQL_HAD_RT_LAUNCH(float);
+    else return UNIQL_EDTYPE;
+#undef UNIQL_HAD_RT_LAUNCH
+    return launch_status();
+  }
+
   // ---- many rows, P >= 32 and more stages than fit the register + shuffle pass: 32 elements per thread ----
   if (P >= 32 && !(base == 1 && P <= 256)) {
     int threads = (int)((dim / 32 + 31) / 32 * 32);
@@ -751,6 +876,8 @@ extern "C" int uniql_hadamard(const void* x, void* y, int64_t rows, int64_t dim,
   if (!x || !y || !aligned16(x) || !aligned16(y)) return UNIQL_EINVAL;
   return launch_hadamard(x, dim, y, dim, rows, dim, scale, dtype, false, (cudaStream_t)stream);
 }
+
+extern "C" int uniql_hadamard_set_base_matrix(int base, const int8_t* h) { return uniql::set_base_matrix(base, h); }
 
 extern "C" int uniql_hadamard_base_matrix(int base, int8_t* out) {
   if (!out) return UNIQL_EINVAL;

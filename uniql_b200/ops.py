@@ -269,6 +269,30 @@ def hadamard(x: torch.Tensor, scale: float) -> torch.Tensor:
     return y
 
 
+def hadamard_base_matrix(base: int) -> torch.Tensor:
+    """The int8 [base, base] matrix of +1 / -1 the library applies for orders 12, 20, 28 and 40 right now."""
+    import ctypes
+    buf = (ctypes.c_int8 * (base * base))()
+    check(lib().uniql_hadamard_base_matrix(int(base), buf), "uniql_hadamard_base_matrix")
+    return torch.tensor(list(buf), dtype=torch.int8).reshape(base, base)
+
+
+def hadamard_set_base_matrix(base: int, matrix=None) -> None:
+    """Replace the order-`base` Hadamard matrix (12, 20, 28, 40) for every transform launched afterwards in this
+    process; `matrix` is a [base, base] array of +1 / -1 with orthogonal rows, None restores the built-in one.  The
+    reference's transforms come from the third-party fast_hadamard_transform package (quantize/hadamard_helpers.py:18-36):
+    passing that package's tables here makes this library reproduce them."""
+    import ctypes
+    if matrix is None:
+        check(lib().uniql_hadamard_set_base_matrix(int(base), None), "uniql_hadamard_set_base_matrix")
+        return
+    m = torch.as_tensor(matrix).to(torch.int8).contiguous().cpu()
+    if tuple(m.shape) != (base, base):
+        raise RuntimeError(f"matrix must be [{base}, {base}]")
+    buf = (ctypes.c_int8 * (base * base))(*m.reshape(-1).tolist())
+    check(lib().uniql_hadamard_set_base_matrix(int(base), buf), "uniql_hadamard_set_base_matrix")
+
+
 def w4a16_quantize(weight: torch.Tensor, group_scale: torch.Tensor | None = None, n_pad: int | None = None,
                    want_ref: bool = True):
     """Quantise and pack an nn.Linear weight [out, in] (fp16, CUDA) on the GPU.
