@@ -26,8 +26,8 @@ SHAPES = {"qkv": (QKV, HIDDEN), "o": (HIDDEN, HIDDEN), "gate": (INTER, HIDDEN), 
           "down": (HIDDEN, INTER)}
 FALLBACK_HBM_GBS = 6650.0        # HBM copy bandwidth of a B200 (GB/s), used only if MEASURED_PEAKS.json is absent
 # DRAM bytes read + written by one fused gate+up launch (two 14336x4096 projections, m = 1) as counted by the
-# profiler (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture of this kernel exists
-NCU_TRAFFIC_GATE_UP_M1 = None
+# profiler (dram__bytes_read.sum + dram__bytes_write.sum = 60,643,072 + 201,472) in one capture of that launch
+NCU_TRAFFIC_GATE_UP_M1 = 60844544
 
 
 def linear_bytes(n, k, m):

@@ -55,6 +55,35 @@ def test_many_rows_row_kernel(rows, dim):
     assert np.allclose((y.astype(np.float64) ** 2).sum(1), (x.astype(np.float64) ** 2).sum(1), rtol=1e-4)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("dim", [2048, 4096, 8192, 16384, 1536, 3072, 6144, 3584, 7168, 14336, 5120, 10240, 20480])
+def test_many_rows_16bit_tensor_core_kernel(dim, dtype):
+    """16-bit rows with 128 <= dim / base <= 512 (power-of-two sizes count 16 or 32 as their base) apply the base matrix
+    with mma.sync on the raw inputs; every (m-tile count, segment length) variant is covered.  Oracle on sampled rows,
+    first row == last row, and the in-place call gives the same bits."""
+    from uniql_b200 import ops
+    from uniql_b200._lib import check, lib
+    rows = 333
+    x = make_acts(dim + 1, rows, dim).to(dtype)
+    x[-1] = x[0]
+    xd = x.cuda()
+    y = ops.hadamard(xd, dim ** -0.5)
+    torch.cuda.synchronize()
+    pick = [0, 1, 2, 100, 331, 332]
+    want = orc.hadamard_transform(x[pick].double().numpy())
+    eps = 2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7
+    got = y[pick].double().cpu().numpy()
+    assert np.abs(got - want).max() <= eps * np.abs(want).max() + 1e-6
+    # away from the largest values the error stays at fp32 accumulation + one rounding of the result
+    assert (np.abs(got - want) <= eps * np.abs(want) + 2e-5 * np.abs(want).max()).all()
+    assert torch.equal(y[0], y[-1])
+    code = lib().uniql_hadamard(xd.data_ptr(), xd.data_ptr(), rows, dim, float(dim ** -0.5),
+                                0 if dtype == torch.float16 else 1, torch.cuda.current_stream().cuda_stream)
+    check(code, "uniql_hadamard")
+    torch.cuda.synchronize()
+    assert torch.equal(xd, y)
+
+
 def test_many_rows_in_place_fp16():
     from uniql_b200._lib import check, lib
     rows, dim = 3000, 2048

@@ -533,6 +533,186 @@ __global__ void __launch_bounds__(256) hadamard_rt_kernel(const T* __restrict__ 
   }
 }
 
+// Many rows of a 16-bit type, 128 <= P <= 512: the base matrix runs on the tensor cores.  The two factors of
+// (H_base (x) H_P) commute, so the base matrix is applied FIRST, to the raw inputs: Z[a', b] = sum_a H[a'][a] X[a, b] is
+// a matrix product with a +1/-1 operand -- exact products, fp32 sums -- and costs one mma.sync per 16 x 8 outputs instead
+// of `base` adds per output (28 x 28 signed sums per column were three quarters of the row kernel's instructions).
+// Power-of-two sizes use H_16 or H_32 in Sylvester order as their "base".  One CTA per row:
+//   1. cp.async the row into shared memory as [a][b] (row stride P + 8 elements, so ldmatrix is conflict free);
+//   2. warp (m-tile, 128-column unit): ldmatrix.trans gives the [k = a][n = b] operand, H sits in registers as the
+//      16-row operand (signs from the launch parameters: a matrix replaced at run time costs nothing), 16 n-tiles ->
+//      64 fp32 accumulators per thread; butterflies over the b bits a thread holds (0 and 3..6) in registers;
+//   3. fp32 tile to shared memory (it reuses the raw row's space), second pass: a thread takes 8 consecutive b for every
+//      128-column unit, runs bits 1, 2 and 7.., scales, converts and stores 16 bytes, coalesced.
+template <typename T> struct MmaOp;
+template <> struct MmaOp<__half> {
+  static constexpr unsigned kOne = 0x3C00u, kMinusOne = 0xBC00u;
+  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+template <> struct MmaOp<__nv_bfloat16> {
+  static constexpr unsigned kOne = 0x3F80u, kMinusOne = 0xBF80u;
+  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+
+__device__ __forceinline__ uint32_t had_smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void had_cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(had_smem_addr(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+template <typename T, int MT, int LOGP>
+__global__ void __launch_bounds__(MT * (1 << (LOGP - 7)) * 32, MT <= 2 ? 3 : 2)
+    hadamard_mma_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy, int base, float scale,
+                        const HadSigns signs, int pdl_trigger) {
+  constexpr int KT = MT;
+  constexpr int P = 1 << LOGP;
+  constexpr int NU = P / 128;
+  constexpr int NTHREADS = MT * NU * 32;
+  constexpr int RS = P + 8;     // raw row stride, 16-bit elements
+  constexpr int FS = P + 8;     // fp32 row stride, words (= 8 mod 32: the float2 stores of a half-warp hit 32 banks)
+  extern __shared__ __align__(16) unsigned char had_smem[];
+  T* raw = reinterpret_cast<T*>(had_smem);
+  float* fb = reinterpret_cast<float*>(had_smem);
+  if (pdl_trigger) pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const T* xr = x + (int64_t)blockIdx.x * ldx;
+  T* yr = y + (int64_t)blockIdx.x * ldy;
+
+  for (int ch = tid; ch < base * (P / 8); ch += NTHREADS) {
+    const int a = ch >> (LOGP - 3), cb = ch & (P / 8 - 1);
+    had_cp_async16(raw + a * RS + cb * 8, xr + (size_t)a * P + cb * 8);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  // H as the 16-row operand (rows a', k = a), zero outside base x base
+  const int mt = warp % MT, u = warp / MT;
+  uint32_t afrag[KT][4];
+#pragma unroll
+  for (int kt = 0; kt < KT; ++kt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = 16 * mt + g + (j & 1) * 8;
+      const int k = 16 * kt + 2 * c + (j >> 1) * 8;
+      uint32_t w = 0;
+      if (r < base) {
+        const uint64_t m = signs.row[r];
+        if (k < base) w |= ((m >> k) & 1ull) ? MmaOp<T>::kMinusOne : MmaOp<T>::kOne;
+        if (k + 1 < base) w |= (((m >> (k + 1)) & 1ull) ? MmaOp<T>::kMinusOne : MmaOp<T>::kOne) << 16;
+      }
+      afrag[kt][j] = w;
+    }
+  // ldmatrix row of this lane: k = lane (and 32 + lane % 16 for a third k-tile); rows past `base` read row 0, whose
+  // products meet the zero columns of H
+  int k0 = KT == 1 ? (lane & 15) : lane;
+  if (k0 >= base) k0 = 0;
+  int k1 = 32 + (lane & 15);
+  if (k1 >= base) k1 = 0;
+  const uint32_t row0 = had_smem_addr(raw + k0 * RS + 128 * u);
+  const uint32_t row1 = had_smem_addr(raw + k1 * RS + 128 * u);
+
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+
+  float acc[16][4];
+#pragma unroll
+  for (int t = 0; t < 16; ++t) {
+    acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+    uint32_t b[6];
+    if constexpr (KT == 1) {
+      asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                   : "=r"(b[0]), "=r"(b[1]) : "r"(row0 + t * 16));
+    } else {
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(row0 + t * 16));
+      if constexpr (KT == 3)
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                     : "=r"(b[4]), "=r"(b[5]) : "r"(row1 + t * 16));
+    }
+#pragma unroll
+    for (int kt = 0; kt < KT; ++kt) MmaOp<T>::mma(acc[t], afrag[kt], b[2 * kt], b[2 * kt + 1]);
+  }
+  // b = 128 u + 8 t + 2 c + e: bit 0 is the accumulator pair, bits 3..6 the n-tile index
+#pragma unroll
+  for (int t = 0; t < 16; ++t) {
+    const float a0 = acc[t][0], a1 = acc[t][1], a2 = acc[t][2], a3 = acc[t][3];
+    acc[t][0] = a0 + a1; acc[t][1] = a0 - a1; acc[t][2] = a2 + a3; acc[t][3] = a2 - a3;
+  }
+#pragma unroll
+  for (int s = 1; s < 16; s <<= 1)
+#pragma unroll
+    for (int t = 0; t < 16; ++t)
+      if (!(t & s)) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = acc[t][j], hi = acc[t | s][j];
+          acc[t][j] = lo + hi;
+          acc[t | s][j] = lo - hi;
+        }
+      }
+  __syncthreads();                       // every warp has read its part of the raw row: the space becomes the fp32 tile
+  {
+    const int ra = 16 * mt + g;
+    float* fa = fb + ra * FS + 128 * u + 2 * c;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      if (ra < base) *reinterpret_cast<float2*>(fa + 8 * t) = make_float2(acc[t][0], acc[t][1]);
+      if (ra + 8 < base) *reinterpret_cast<float2*>(fa + 8 * FS + 8 * t) = make_float2(acc[t][2], acc[t][3]);
+    }
+  }
+  __syncthreads();
+  for (int task = tid; task < base * 16; task += NTHREADS) {
+    const int ap = task >> 4, q = task & 15;
+    const float* src = fb + ap * FS + 8 * q;
+    float v[NU][8];
+    const int flip = (q >> 2) & 1;       // lanes q and q + 4 share banks: they take the two 16-byte halves in turn
+#pragma unroll
+    for (int h = 0; h < NU; ++h) {
+      const float4 p0 = *reinterpret_cast<const float4*>(src + 128 * h + 4 * flip);
+      const float4 p1 = *reinterpret_cast<const float4*>(src + 128 * h + 4 * (flip ^ 1));
+      const float4 lo = flip ? p1 : p0, hi = flip ? p0 : p1;
+      v[h][0] = lo.x; v[h][1] = lo.y; v[h][2] = lo.z; v[h][3] = lo.w;
+      v[h][4] = hi.x; v[h][5] = hi.y; v[h][6] = hi.z; v[h][7] = hi.w;
+    }
+#pragma unroll
+    for (int h = 0; h < NU; ++h)
+#pragma unroll
+      for (int s = 2; s < 8; s <<= 1)
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (!(e & s)) {
+            const float lo = v[h][e], hi = v[h][e | s];
+            v[h][e] = lo + hi;
+            v[h][e | s] = lo - hi;
+          }
+#pragma unroll
+    for (int s = 1; s < NU; s <<= 1)
+#pragma unroll
+      for (int h = 0; h < NU; ++h)
+        if (!(h & s)) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float lo = v[h][e], hi = v[h | s][e];
+            v[h][e] = lo + hi;
+            v[h | s][e] = lo - hi;
+          }
+        }
+#pragma unroll
+    for (int h = 0; h < NU; ++h) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[h][e] *= scale;
+      Elem<T>::store8(yr + (size_t)ap * P + 128 * h + 8 * q, v[h]);
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict__ x, int64_t ldx,
                                                              T* __restrict__ y, int64_t ldy, int P, int B,
@@ -763,6 +943,62 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
         hadamard_split_kernel<float><<<grid, threads, 0, stream>>>((const float*)x, ldx, (float*)y, ldy, (int)Ps, (int)B, scale, signs, pdl_trigger ? 1 : 0);
       else return UNIQL_EDTYPE;
       return launch_status();
+    }
+  }
+
+  // ---- many rows of a 16-bit type, 128 <= P <= 512: base matrix on the tensor cores ----
+  if (dtype != UNIQL_F32) {
+    int mbase = base;
+    int64_t mP = P;
+    if (base == 1) {                       // power of two: H_16 or H_32 (Sylvester) takes the base matrix's place
+      mbase = dim >= 16384 ? 32 : 16;
+      mP = dim / mbase;
+    }
+    if (mP == 128 || mP == 256 || mP == 512) {
+      HadSigns ms;
+      for (int i = 0; i < 64; ++i) ms.row[i] = 0;
+      for (int i = 0; i < mbase; ++i)
+        for (int j = 0; j < mbase; ++j) {
+          const bool neg = base == 1 ? (__builtin_popcount((unsigned)(i & j)) & 1) : (h[i * base + j] < 0);
+          if (neg) ms.row[i] |= (1ull << j);
+        }
+      const int MTv = (mbase + 15) / 16, logp = mP == 128 ? 7 : mP == 256 ? 8 : 9;
+      const size_t smem = (size_t)mbase * (size_t)(mP + 8) * sizeof(float);
+      const int threads = MTv * (int)(mP / 128) * 32;
+#define UNIQL_HAD_MMA_CASE(T, MT_, LP_)                                                                       \
+  do {                                                                                                        \
+    static thread_local bool attr_done[64] = {};   /* function attributes are per device */                   \
+    if (!attr_done[cur_dev]) {                                                                                \
+      UNIQL_CUDA_TRY(cudaFuncSetAttribute(hadamard_mma_kernel<T, MT_, LP_>,                                   \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
+                                          (int)(16 * MT_ * ((1 << LP_) + 8) * sizeof(float))));               \
+      attr_done[cur_dev] = true;                                                                              \
+    }                                                                                                         \
+    for (int64_t r0 = 0; r0 < rows; r0 += (int64_t)1 << 30) {                                                 \
+      const int64_t nr = rows - r0 < ((int64_t)1 << 30) ? rows - r0 : ((int64_t)1 << 30);                     \
+      hadamard_mma_kernel<T, MT_, LP_><<<(unsigned)nr, threads, smem, stream>>>(                              \
+          (const T*)x + r0 * ldx, ldx, (T*)y + r0 * ldy, ldy, mbase, scale, ms, pdl_trigger ? 1 : 0);         \
+    }                                                                                                         \
+    return launch_status();                                                                                   \
+  } while (0)
+#define UNIQL_HAD_MMA_LOGP(T, MT_)                                                                            \
+  do {                                                                                                        \
+    if (logp == 7) UNIQL_HAD_MMA_CASE(T, MT_, 7);                                                             \
+    else if (logp == 8) UNIQL_HAD_MMA_CASE(T, MT_, 8);                                                        \
+    else UNIQL_HAD_MMA_CASE(T, MT_, 9);                                                                       \
+  } while (0)
+#define UNIQL_HAD_MMA_MT(T)                                                                                   \
+  do {                                                                                                        \
+    if (MTv == 1) UNIQL_HAD_MMA_LOGP(T, 1);                                                                   \
+    else if (MTv == 2) UNIQL_HAD_MMA_LOGP(T, 2);                                                              \
+    else UNIQL_HAD_MMA_LOGP(T, 3);                                                                            \
+  } while (0)
+      if (dtype == UNIQL_F16) UNIQL_HAD_MMA_MT(__half);
+      else if (dtype == UNIQL_BF16) UNIQL_HAD_MMA_MT(__nv_bfloat16);
+      else return UNIQL_EDTYPE;
+#undef UNIQL_HAD_MMA_MT
+#undef UNIQL_HAD_MMA_LOGP
+#undef UNIQL_HAD_MMA_CASE
     }
   }
 
