@@ -764,9 +764,10 @@ def run_ours(args):
         if world == 1 and not os.environ.get("UNIQL_BENCH_NO_AUX"):
             aux = aux_kernels(device, stream, peak)
             torch.cuda.empty_cache()
-            qwen = qwen_decode_leg(device, stream, peak)
-            torch.cuda.empty_cache()
-            mamba = mamba_decode_leg(device, stream, peak)
+            if not os.environ.get("UNIQL_BENCH_NO_LEGS"):       # profiling runs of the aux kernels skip the model legs
+                qwen = qwen_decode_leg(device, stream, peak)
+                torch.cuda.empty_cache()
+                mamba = mamba_decode_leg(device, stream, peak)
 
     def rank_max(v):
         if world == 1:

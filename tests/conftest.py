@@ -25,4 +25,6 @@ def built_lib():
     from uniql_b200 import _build
     if not os.path.exists(_build.LIB_PATH):
         _build.build()
+    if not os.path.exists(_build.EXT_PATH):
+        _build.build_torch_ext()
     return _build.LIB_PATH

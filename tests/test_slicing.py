@@ -255,8 +255,10 @@ def test_llama_8b_sized_layers_sliced_on_the_gpu_keep_their_weights():
     # gate / up: column prefix
     p, s, ws = layer(inter, hidden)
     p2, s2, ws2 = mh.slice_w4a16_up_gate_proj(p, s, ws, hidden, inter, red, p.shape)
-    assert p2.shape == (hidden // 16, 2 * red) and s2.shape == (hidden // 128, red) and ws2.numel() == red // 64 * 16
+    width = (red + 255) // 256 * 256                            # stored widths are multiples of 256
+    assert p2.shape == (hidden // 16, 2 * width) and s2.shape == (hidden // 128, width) and ws2.numel() == width // 64 * 16
     assert same(deq(p2, s2, red), deq(p, s, inter)[:red])
+    assert float(deq(p2, s2, width)[red:].abs().max()) == 0.0   # columns between 12160 and 12288: zero scales
     # down: row prefix
     p, s, ws = layer(hidden, inter)
     p2, s2, _ = mh.slice_w4a16_down_proj(p, s, ws, hidden, inter, red, p.shape)

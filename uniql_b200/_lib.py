@@ -93,6 +93,37 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+_ext = None
+_ext_tried = False
+
+
+def torch_ext():
+    """The torch binding of the same library (uniql_b200/_torch_ext.so, built from csrc/torch_binding.cpp), or None.
+
+    The modules' forward goes through it when it is there: the C++ binding does in a few microseconds what the ctypes
+    path below does in tens.  Both end in the same C-ABI calls of libuniql_b200.so.  UNIQL_B200_TORCH_EXT=0 keeps
+    everything on ctypes; a missing or unloadable binding does the same with a warning (it is built by
+    `python -m uniql_b200._build`)."""
+    global _ext, _ext_tried
+    if _ext_tried:
+        return _ext
+    _ext_tried = True
+    if os.environ.get("UNIQL_B200_TORCH_EXT", "1") == "0":
+        return None
+    try:
+        lib()
+        import torch  # noqa: F401  (libtorch must be loaded before the binding)
+        from . import _torch_ext as ext
+        if ext.abi_version() != lib().uniql_abi_version():
+            raise RuntimeError("torch binding and library disagree on the ABI version")
+        _ext = ext
+    except Exception as e:  # noqa: BLE001
+        import warnings
+        warnings.warn(f"uniql_b200: torch binding not loaded ({e}); module calls go through ctypes")
+        _ext = None
+    return _ext
+
+
 class UniqlError(RuntimeError):
     def __init__(self, code: int, where: str):
         msg = lib().uniql_strerror(code).decode()

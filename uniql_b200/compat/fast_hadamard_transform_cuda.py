@@ -13,6 +13,9 @@ def _checked(base):
             ok = dim % base == 0 and p > 0 and (p & (p - 1)) == 0
         if not ok:
             raise RuntimeError(f"dim {dim} is not {'a power of two' if base == 1 else f'{base} times a power of two'}")
+        ext = ops.torch_ext()
+        if ext is not None:
+            return ext.hadamard(x, float(scale))
         return ops.hadamard(x, scale)
     return fn
 

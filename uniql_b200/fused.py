@@ -21,6 +21,10 @@ def _layer(mod):
     return (mod.weight, mod.scale, mod.bias, mod.out_features)
 
 
+def _rows(x):
+    return x.numel() // x.shape[-1] if x.shape[-1] else 0
+
+
 def _flat(x, mod):
     x2 = x.reshape(-1, x.shape[-1])
     if mod.pad_in:
@@ -31,6 +35,11 @@ def _flat(x, mod):
 @torch.no_grad()
 def gate_up_swiglu(gate_proj, up_proj, x):
     """silu(gate_proj(x)) * up_proj(x) for two W4A16B16O16Linear modules of the same shape."""
+    ext = ops.torch_ext()
+    if ext is not None and _rows(x) <= DECODE_ROWS:
+        return ext.linear_group(x, [gate_proj.weight, up_proj.weight], [gate_proj.scale, up_proj.scale],
+                                [gate_proj.bias, up_proj.bias], [gate_proj.out_features, up_proj.out_features], 1, None,
+                                gate_proj.pad_in, False)[0]
     x2 = _flat(x, gate_proj)
     if x2.shape[0] <= DECODE_ROWS:
         (h,) = ops.w4a16_linear_group(x2, [_layer(gate_proj), _layer(up_proj)], epilogue="swiglu")
@@ -42,8 +51,12 @@ def gate_up_swiglu(gate_proj, up_proj, x):
 @torch.no_grad()
 def qkv_proj(q_proj, k_proj, v_proj, x):
     """(q_proj(x), k_proj(x), v_proj(x)) for three W4A16B16O16Linear modules with the same in_features."""
-    x2 = _flat(x, q_proj)
     mods = (q_proj, k_proj, v_proj)
+    ext = ops.torch_ext()
+    if ext is not None and _rows(x) <= DECODE_ROWS:
+        return tuple(ext.linear_group(x, [m.weight for m in mods], [m.scale for m in mods], [m.bias for m in mods],
+                                      [m.out_features for m in mods], 0, None, q_proj.pad_in, False))
+    x2 = _flat(x, q_proj)
     if x2.shape[0] <= DECODE_ROWS:
         outs = ops.w4a16_linear_group(x2, [_layer(m) for m in mods])
     else:
@@ -55,6 +68,11 @@ def qkv_proj(q_proj, k_proj, v_proj, x):
 def linear_residual(proj, x, residual):
     """residual + proj(x) (o_proj / down_proj / out_proj with the block's skip connection); when `proj` is a
     W4A16B16O16HadLinear its Hadamard transform of x is part of the same call."""
+    ext = ops.torch_ext()
+    if ext is not None and _rows(x) <= DECODE_ROWS:
+        return ext.linear_group(x, [proj.weight], [proj.scale], [proj.bias], [proj.out_features], 0, residual,
+                                proj.pad_in, bool(getattr(proj, "hadamard_dim", 0)))[0].view(
+                                    *residual.shape[:-1], proj.out_features)
     x2 = _flat(x, proj)
     r2 = residual.reshape(-1, residual.shape[-1])
     had = proj.size_k if getattr(proj, "hadamard_dim", 0) else 0

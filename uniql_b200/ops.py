@@ -9,7 +9,7 @@ import torch
 
 import ctypes
 
-from ._lib import Prefetch, Proj, check, lib
+from ._lib import Prefetch, Proj, check, lib, torch_ext
 
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
 
@@ -25,7 +25,9 @@ def status_word(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     t = _status.get(idx)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        ext = torch_ext()
+        # one word per device, shared with the torch binding when that is loaded
+        t = ext.status_tensor(idx) if ext is not None else torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _status[idx] = t
     return t
 

@@ -84,6 +84,10 @@ class W4A16B16O16Linear(torch.nn.Module):
 
     @torch.no_grad()
     def forward(self, x):
+        ext = ops.torch_ext()
+        if ext is not None:
+            return ext.linear(x, self.weight, self.scale, self.bias, self.out_features, self.pad_in,
+                              bool(self.hadamard_dim))
         x_shape = x.shape
         x2 = x.reshape(-1, x_shape[-1])
         if self.pad_in != 0:
