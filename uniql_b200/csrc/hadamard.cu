@@ -16,6 +16,8 @@
 #include "linear_internal.cuh"
 
 #include <stdlib.h>
+#include <string.h>
+
 #include <mutex>
 #include <type_traits>
 #include <utility>
@@ -80,6 +82,21 @@ __host__ __device__ constexpr int c_base_entry(int base, int i, int j) {
 static std::mutex g_base_mu;
 static bool g_base_custom[4] = {false, false, false, false};
 static int8_t g_base_h[4][1600];
+static unsigned g_base_generation = 0;       // bumped by every replacement; host-side sign caches compare it
+
+struct BuiltinBases {
+  int8_t h[4][1600];
+  BuiltinBases() {
+    const int orders[4] = {12, 20, 28, 40};
+    for (int s = 0; s < 4; ++s)
+      for (int i = 0; i < orders[s]; ++i)
+        for (int j = 0; j < orders[s]; ++j) h[s][i * orders[s] + j] = (int8_t)c_base_entry(orders[s], i, j);
+  }
+};
+static const BuiltinBases& builtin_bases() {
+  static const BuiltinBases b;
+  return b;
+}
 static int base_slot(int base) { return base == 12 ? 0 : base == 20 ? 1 : base == 28 ? 2 : base == 40 ? 3 : -1; }
 
 static bool base_is_custom(int base) {
@@ -99,8 +116,7 @@ static int base_matrix(int base, int8_t* h) {
       return UNIQL_OK;
     }
   }
-  for (int i = 0; i < base; ++i)
-    for (int j = 0; j < base; ++j) h[i * base + j] = (int8_t)c_base_entry(base, i, j);
+  memcpy(h, builtin_bases().h[s], (size_t)base * base);
   return UNIQL_OK;
 }
 
@@ -121,6 +137,7 @@ static int set_base_matrix(int base, const int8_t* h) {
   g_base_custom[s] = h != nullptr;
   if (h)
     for (int i = 0; i < base * base; ++i) g_base_h[s][i] = h[i];
+  ++g_base_generation;
   return UNIQL_OK;
 }
 
@@ -867,6 +884,7 @@ __global__ void __launch_bounds__(128) hadamard_split_feat_kernel(const unsigned
 }
 
 // Segment layout of the few-row kernels: dim = B segments of Ps points.  Returns false if the size does not fit them.
+// The sign words of the last few sizes are remembered (a decode loop asks for the same one on every step).
 static bool split_layout(int64_t dim, int base, int64_t* Ps_out, int64_t* B_out, HadSigns* signs) {
   const int64_t P = dim / base;
   if (P < 256) return false;
@@ -875,6 +893,22 @@ static bool split_layout(int64_t dim, int base, int64_t* Ps_out, int64_t* B_out,
   if (base * Q > 64) { Ps = 1024; Q = P / Ps; }
   const int64_t B = base * Q;
   if (!(B <= 64 && Ps <= 1024 && Q >= 1)) return false;
+  *Ps_out = Ps;
+  *B_out = B;
+  struct Entry { int64_t dim; unsigned gen; HadSigns signs; };
+  static std::mutex mu;
+  static Entry cache[8];
+  static int used = 0, next = 0;
+  unsigned gen;
+  {
+    std::lock_guard<std::mutex> lk(g_base_mu);
+    gen = g_base_generation;
+  }
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (int i = 0; i < used; ++i)
+      if (cache[i].dim == dim && cache[i].gen == gen) { *signs = cache[i].signs; return true; }
+  }
   int8_t h[1600];
   if (base > 1) base_matrix(base, h);
   for (int i = 0; i < 64; ++i) signs->row[i] = 0;
@@ -885,8 +919,10 @@ static bool split_layout(int64_t dim, int base, int64_t* Ps_out, int64_t* B_out,
       neg ^= __builtin_popcount((unsigned)(h1 & h2)) & 1;
       if (neg) signs->row[s1] |= (1ull << s2);
     }
-  *Ps_out = Ps;
-  *B_out = B;
+  std::lock_guard<std::mutex> lk(mu);
+  cache[next] = {dim, gen, *signs};
+  next = (next + 1) % 8;
+  if (used < 8) ++used;
   return true;
 }
 
@@ -915,24 +951,11 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
   cudaGetDevice(&cur_dev);
   if (cur_dev < 0 || cur_dev >= 64) cur_dev = 0;
   HadSigns signs;
-  for (int i = 0; i < 64; ++i) signs.row[i] = 0;
-  int8_t h[1600];
-  if (base > 1) base_matrix(base, h);
 
   // ---- few rows: one CTA per (segment, row) ----
   if (rows <= 16 && P >= 256 && !(x == y)) {
-    int64_t Ps = P < 512 ? P : 512;
-    int64_t Q = P / Ps;
-    if (base * Q > 64) { Ps = 1024; Q = P / Ps; }
-    const int64_t B = base * Q;
-    if (B <= 64 && Ps <= 1024 && Q >= 1) {
-      for (int s1 = 0; s1 < B; ++s1)
-        for (int s2 = 0; s2 < B; ++s2) {
-          const int a1 = (int)(s1 / Q), h1 = (int)(s1 % Q), a2 = (int)(s2 / Q), h2 = (int)(s2 % Q);
-          int neg = (base > 1 && h[a1 * base + a2] < 0) ? 1 : 0;
-          neg ^= __builtin_popcount((unsigned)(h1 & h2)) & 1;
-          if (neg) signs.row[s1] |= (1ull << s2);
-        }
+    int64_t Ps = 0, B = 0;
+    if (split_layout(dim, base, &Ps, &B, &signs)) {
       dim3 grid((unsigned)B, (unsigned)rows);
       const int threads = (int)(Ps / 8);
       if (dtype == UNIQL_F16)
@@ -945,6 +968,9 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
       return launch_status();
     }
   }
+  for (int i = 0; i < 64; ++i) signs.row[i] = 0;
+  int8_t h[1600];
+  if (base > 1) base_matrix(base, h);
 
   // ---- many rows of a 16-bit type, 128 <= P <= 512: base matrix on the tensor cores ----
   if (dtype != UNIQL_F32) {

@@ -48,6 +48,26 @@ at::Tensor scratch_for(int device, cudaStream_t stream, size_t need) {
   return slot;
 }
 
+// Scratch requirement of the last few shapes (a decode loop repeats a handful of them).
+struct NeedKey {
+  int64_t v[8];
+  bool operator==(const NeedKey& o) const {
+    for (int i = 0; i < 8; ++i)
+      if (v[i] != o.v[i]) return false;
+    return true;
+  }
+};
+template <typename F>
+size_t cached_need(const NeedKey& key, F&& compute) {
+  static thread_local std::vector<std::pair<NeedKey, size_t>> cache;
+  for (const auto& e : cache)
+    if (e.first == key) return e.second;
+  const size_t need = compute();
+  if (cache.size() >= 64) cache.clear();
+  cache.emplace_back(key, need);
+  return need;
+}
+
 void check_code(int code, const char* what) {
   if (code == UNIQL_OK) return;
   if (code == UNIQL_ECUDA)
@@ -104,7 +124,7 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& weight, const at::Tenso
   if (m == 0) return out;
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
   const int64_t had = hadamard ? k : 0;
-  const size_t need = uniql_w4a16_scratch_bytes(m, n, k, had);
+  const size_t need = cached_need(NeedKey{{0, m, n, k, had, 0, 0, 0}}, [&] { return uniql_w4a16_scratch_bytes(m, n, k, had); });
   at::Tensor scratch = scratch_for(dev, stream, need);
   at::Tensor status = status_tensor(dev);
   const void* bias_ptr = (bias.has_value() && bias->defined()) ? bias->data_ptr() : nullptr;
@@ -168,7 +188,9 @@ std::vector<at::Tensor> linear_group(const at::Tensor& x, const std::vector<at::
   }
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
   const int64_t had = hadamard ? k : 0;
-  const size_t need = uniql_w4a16_group_scratch_bytes(m, k, ns, np, (int)epilogue, had);
+  const size_t need = cached_need(
+      NeedKey{{1 + epilogue + 2 * (had != 0), m, k, ns[0], np > 1 ? ns[1] : 0, np > 2 ? ns[2] : 0, np > 3 ? ns[3] : 0, np}},
+      [&] { return uniql_w4a16_group_scratch_bytes(m, k, ns, np, (int)epilogue, had); });
   at::Tensor scratch = scratch_for(dev, stream, need);
   at::Tensor status = status_tensor(dev);
   const int code = uniql_w4a16_linear_group(x2.data_ptr(), m > 1 ? x2.stride(0) : k, m, k, proj, np, (int)epilogue, res_ptr,

@@ -36,6 +36,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
+#include <vector>
+
 namespace uniql {
 
 constexpr int kGemvThreads = 256;
@@ -667,12 +670,44 @@ struct GemvPlan {
 
 // n: width of the launch's virtual column space (all projections side by side).  pair: the blocks alternate gate / up,
 // so a CTA must hold an even number of them.
+// The tuning overrides are read from the environment once per process (a getenv per launch is a scan of the whole
+// environment block).
+struct GemvEnv {
+  int slots, wn, s, r, cluster;
+};
+static const GemvEnv& gemv_env() {
+  static const GemvEnv e = {env_int("UNIQL_B200_GEMV_SLOTS", 0), env_int("UNIQL_B200_GEMV_WN", 0),
+                            env_int("UNIQL_B200_GEMV_S", 0), env_int("UNIQL_B200_GEMV_R", 0),
+                            env_int("UNIQL_B200_CLUSTER", 1)};
+  return e;
+}
+
+static GemvPlan make_gemv_plan(int64_t m, int64_t n, int64_t k, bool pair);
+
+// Plans are a pure function of (m, n, k, pair): the last few are remembered so that an eager decode loop does not run
+// the cost model on every launch.
 static GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k, bool pair) {
+  struct Entry { int64_t m, n, k; bool pair; GemvPlan plan; };
+  static std::mutex mu;
+  static std::vector<Entry> cache;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (const Entry& e : cache)
+      if (e.m == m && e.n == n && e.k == k && e.pair == pair) return e.plan;
+  }
+  const GemvPlan plan = make_gemv_plan(m, n, k, pair);
+  std::lock_guard<std::mutex> lk(mu);
+  if (cache.size() >= 256) cache.clear();
+  cache.push_back({m, n, k, pair, plan});
+  return plan;
+}
+
+static GemvPlan make_gemv_plan(int64_t m, int64_t n, int64_t k, bool pair) {
   GemvPlan best{};
   const int MT = m <= 8 ? 1 : 2;
   const int nblk = (int)(n / 64), KT = (int)(k / 16), NG = KT / 8;
   const int ctas_per_sm = MT == 1 ? kCtasMt1 : 2;
-  const int slots = device_info().sm_count * env_int("UNIQL_B200_GEMV_SLOTS", ctas_per_sm);
+  const int slots = device_info().sm_count * (gemv_env().slots > 0 ? gemv_env().slots : ctas_per_sm);
   double best_cost = 1e30;
   for (int WN = 8; WN >= (pair ? 2 : 1); WN >>= 1) {
     const int WK = kGemvWarps / WN;
@@ -696,7 +731,7 @@ static GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k, bool pair) {
       }
     }
   }
-  const int ov_wn = env_int("UNIQL_B200_GEMV_WN", 0), ov_s = env_int("UNIQL_B200_GEMV_S", 0);
+  const int ov_wn = gemv_env().wn, ov_s = gemv_env().s;
   if ((ov_wn == 1 && !pair) || ov_wn == 2 || ov_wn == 4 || ov_wn == 8) { best.WN = ov_wn; best.WK = kGemvWarps / ov_wn; }
   if (ov_s >= 1) best.S = ov_s;
   if (best.S > KT) best.S = KT;
@@ -710,7 +745,7 @@ static GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k, bool pair) {
   const int r_max = MT == 1 ? 2 : 3;
   if (R > r_max) R = r_max;
   if (R < 1) R = 1;
-  const int ov_r = env_int("UNIQL_B200_GEMV_R", 0);
+  const int ov_r = gemv_env().r;
   if (ov_r >= 1 && ov_r <= 4) R = ov_r;
   const size_t ring_bytes = (size_t)kGemvWarps * R * kSlotBytes;
   const size_t left = budget > ring_bytes ? budget - ring_bytes : 0;
@@ -727,8 +762,7 @@ static GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k, bool pair) {
   const size_t red_bytes = (size_t)kGemvWarps * 8 * MT * kRedStride * 4;
   best.smem = ring_bytes + xs_bytes > red_bytes ? ring_bytes + xs_bytes : red_bytes;
   // cluster mode (2 <= S <= 8): the CTA's reduced tile lives behind the warp reduction buffer
-  static const int cluster_on = env_int("UNIQL_B200_CLUSTER", 1);
-  best.cluster = (cluster_on && best.S >= 2 && best.S <= 8) ? 1 : 0;
+  best.cluster = (gemv_env().cluster && best.S >= 2 && best.S <= 8) ? 1 : 0;
   best.ctile_off = (int)((red_bytes + 1023) / 1024 * 1024);
   if (best.cluster) {
     const size_t need = (size_t)best.ctile_off + (size_t)(m < 16 ? m : 16) * best.WN * 64 * 4;

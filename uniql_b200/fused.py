@@ -32,7 +32,6 @@ def _flat(x, mod):
     return x2
 
 
-@torch.no_grad()
 def gate_up_swiglu(gate_proj, up_proj, x):
     """silu(gate_proj(x)) * up_proj(x) for two W4A16B16O16Linear modules of the same shape."""
     ext = ops.torch_ext()
@@ -48,7 +47,6 @@ def gate_up_swiglu(gate_proj, up_proj, x):
     return h.view(*x.shape[:-1], gate_proj.out_features)
 
 
-@torch.no_grad()
 def qkv_proj(q_proj, k_proj, v_proj, x):
     """(q_proj(x), k_proj(x), v_proj(x)) for three W4A16B16O16Linear modules with the same in_features."""
     mods = (q_proj, k_proj, v_proj)
@@ -64,7 +62,6 @@ def qkv_proj(q_proj, k_proj, v_proj, x):
     return tuple(o.view(*x.shape[:-1], m.out_features) for o, m in zip(outs, mods))
 
 
-@torch.no_grad()
 def linear_residual(proj, x, residual):
     """residual + proj(x) (o_proj / down_proj / out_proj with the block's skip connection); when `proj` is a
     W4A16B16O16HadLinear its Hadamard transform of x is part of the same call."""

@@ -82,12 +82,15 @@ class W4A16B16O16Linear(torch.nn.Module):
             qlinear.bias = nn.Parameter(originalLayer.bias.data.clone().to(torch.float16), requires_grad=False)
         return qlinear
 
-    @torch.no_grad()
     def forward(self, x):
         ext = ops.torch_ext()
-        if ext is not None:
+        if ext is not None:       # the binding records nothing for autograd: no no_grad context needed around it
             return ext.linear(x, self.weight, self.scale, self.bias, self.out_features, self.pad_in,
                               bool(self.hadamard_dim))
+        return self._forward_ctypes(x)
+
+    @torch.no_grad()
+    def _forward_ctypes(self, x):
         x_shape = x.shape
         x2 = x.reshape(-1, x_shape[-1])
         if self.pad_in != 0:

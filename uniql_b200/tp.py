@@ -212,8 +212,10 @@ class PushAllReduce:
 
     def down_gather_reduce(self, m: int, down, hadamard_dim: int, k_offset: int, residual=None):
         """Row-parallel down/out projection of the row gathered by the preceding gate_up_gather: every rank
-        transforms the full row (Hadamard of hadamard_dim points) in the kernel prologue, multiplies its own k slice
-        (from feature k_offset on) and the partial results are summed over the ranks in the epilogue.  One launch."""
+        transforms the full row (Hadamard of hadamard_dim points, a few-row kernel that reads the words straight from
+        this rank's feature area and waits, bounded, for those that have not arrived), multiplies its own k slice
+        (from feature k_offset on) and the partial results are summed over the ranks in the linear's epilogue.  The two
+        launches are chained by programmatic dependent launch; no collective call, no host step in between."""
         from . import ops
         return ops.w4a16_linear_group(None, [down], residual=residual, hadamard_dim=hadamard_dim, comm=self._comm,
                                       tp_flags=ops.TP_GATHER_IN | ops.TP_REDUCE, k_offset=k_offset, m=m)[0]
