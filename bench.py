@@ -689,7 +689,7 @@ def run_ours(args):
         # ---- the same stack at decode batches 16 and 64 (extra keys; the headline stays batch `m`) ----
         batch_curve = {}
         for bm in (16, 64):
-            if bm == m:
+            if bm == m or os.environ.get("UNIQL_BENCH_NO_LEGS"):     # profiling runs of the aux kernels skip these too
                 continue
             xb = (torch.randn(bm, HIDDEN, generator=gen, device=device) * 0.05).to(torch.float16)
             bmode = collective if (bm <= 16 or collective != "fused") else "push"
