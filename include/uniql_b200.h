@@ -68,7 +68,9 @@ int uniql_last_cuda_error(void);
  *   hadamard_dim  0, or k: apply y = H_k * x / sqrt(k) to every row of A first
  *              (quantize/quant_hadamard_layers.py:16-18 placed in front of the linear);
  *              the transformed rows are rounded to fp16 exactly as the separate module would.
- *              For m <= 4 the transform runs inside the linear kernel, otherwise as a kernel in front of it.
+ *              The transform runs as a few-row kernel in front of the linear, which starts as its programmatic
+ *              dependent (its weight stream overlaps the transform); the slot-balanced decode kernel
+ *              (UNIQL_B200_DECODE_ENGINE=slot) runs it inside its own prologue for m <= 4.
  *   scratch    device buffer of at least uniql_w4a16_scratch_bytes(m, n, k, hadamard_dim) bytes,
  *              256-byte aligned.  Its first UNIQL_SCRATCH_COUNTER_BYTES bytes must be zero before the
  *              first call and are left zero by every call; do not share one scratch buffer between
@@ -235,8 +237,8 @@ int uniql_w4a16_linear_allreduce(void* comm, const void* A, int64_t lda, const v
  *   - the residual add after o_proj / down_proj: `residual` (fp16 [m, n_out], row stride ldr, may alias D) is added to
  *     the rounded result (single projection or SwiGLU pair);
  *   - the Hadamard module in front of down_proj / out_proj (quantize/quant_hadamard_layers.py:16-18): hadamard_dim = k
- *     transforms every activation row first (rounded to fp16 as the module would); for m <= 4 the transform runs in the
- *     kernel's own prologue, no separate launch and no round trip through memory.
+ *     transforms every activation row first (rounded to fp16 as the module would): a few-row kernel in front whose
+ *     launch the linear's weight stream overlaps (in the slot-balanced kernel's own prologue for m <= 4).
  * Each projection is described by plain pointers and sizes (see uniql_w4a16_linear for B, s, bias, D, n, n_out).
  * scratch: at least uniql_w4a16_group_scratch_bytes(...) bytes, 256-byte aligned, first UNIQL_SCRATCH_COUNTER_BYTES
  * zero before the first call (every call leaves them zero).  The weights and scales must not be written by the kernel

@@ -103,8 +103,8 @@ def test_residual_add_in_the_epilogue(n, k, m):
                                    (4096, 8192, 3), (1024, 3584, 2), (256, 4096, 1), (512, 1536, 4), (128, 20480, 1),
                                    (256, 5120, 2), (4096, 14336, 8), (4096, 8192, 16)])
 def test_hadamard_in_the_prologue(n, k, m):
-    """hadamard_dim = k: rows are transformed (fp32 arithmetic, rounded to fp16 as the separate module does) and
-    multiplied in one launch for m <= 4, by a transform kernel in front for larger batches."""
+    """hadamard_dim = k: rows are transformed (fp32 arithmetic, rounded to fp16 as the separate module does) by a
+    transform kernel chained in front of the linear; the slot-balanced kernel does it in its own prologue for m <= 4."""
     from uniql_b200 import ops
     layer = quantized_layer(n + k + m, n, k)
     x = make_acts(m + 2, m, k)

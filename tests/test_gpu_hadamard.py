@@ -129,7 +129,7 @@ def test_fused_hadamard_linear(n, k, m):
     xh = orc.hadamard_transform(x.double().numpy()).astype(np.float16)
     want = orc.linear_ref(xh, None, None, None, n, w_deq=layer["w_deq"])
     linear_tolerance_check(y, want)
-    # and it agrees with the two-step module composition (for m <= 4 the transform runs inside the linear kernel with
+    # and it agrees with the two-step module composition (the slot-balanced kernel transforms inside the linear with
     # its fp32 sums in another order, so a transformed value may round to the neighbouring fp16 now and then)
     xh_gpu = ops.hadamard(x.cuda(), 1.0 / np.sqrt(k))
     y2 = ops.w4a16_linear(xh_gpu, torch.from_numpy(layer["packed"]).cuda(), torch.from_numpy(layer["scales"]).cuda(),

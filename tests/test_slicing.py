@@ -289,7 +289,8 @@ def test_llama_8b_sized_layers_sliced_on_the_gpu_keep_their_weights():
     _, want_p, want_s = ops.w4a16_quantize(kept, want_ref=False)
     assert p2.shape == (nheads * rhd // 16, 2 * hidden) and torch.equal(p2, want_p) and same(s2, want_s)
     assert int(p2.long().sum()) == int(want_p.long().sum())
-    # re-quantising moves every weight by at most half a step of its new group scale
+    # re-quantising moves every weight by at most half a step of its new group scale (plus the fp16 roundings of the
+    # scale and of w / scale: the group maximum sits at 7.5 steps and is clamped to 7)
     step = ops.w4a16_dequantize_rows(torch.full_like(p2, 0x99999999 - (1 << 32)), s2, torch.arange(nheads * rhd), hidden)
-    assert bool(((deq(p2, s2, hidden).float() - kept.float()).abs() <= 0.5 * step.float().abs() + 1e-6).all())
+    assert bool(((deq(p2, s2, hidden).float() - kept.float()).abs() <= 0.52 * step.float().abs() + 1e-5).all())
     assert ops.read_and_clear_status("cuda") == 0

@@ -87,7 +87,7 @@ def main():
             check(torch.allclose(y_f.float(), y_full.float(), rtol=2e-2, atol=2e-2 * float(y_full.float().abs().max())), f"fused vs unsharded m={m} k={k} call {call}")
     # ---- the decode MLP of a tensor-parallel layer in two launches: gate/up shard with SwiGLU whose epilogue stores
     # the activated columns into every rank's feature area, then the down shard that reads the full row there,
-    # transforms it (Hadamard in the prologue), multiplies its k slice and sums over the ranks in its epilogue ----
+    # transforms it (Hadamard kernel reading the feature area), multiplies its k slice and sums over the ranks in its epilogue ----
     from uniql_b200 import fused as fz
     # (the gather path transforms in 256-point segments or longer: 14336 = 28 x 512, 8192 = 16 x 512)
     for hidden, inter, m in [(4096, 14336, 16), (4096, 14336, 1), (4096, 14336, 4), (4096, 8192, 2)]:
