@@ -1093,7 +1093,9 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     if (!a.scratch || a.scratch_bytes < base + xh_bytes || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return UNIQL_ESCRATCH;
     const __half* Ain = (const __half*)a.A;
     int64_t lda = a.lda;
-    if (a.hadamard_dim) {
+    // few rows, segments of 256 / 512 points, one GPU: the linear transforms its k-range in its own prologue
+    const bool fuse = a.hadamard_dim && gemv_fuses_hadamard(a);
+    if (a.hadamard_dim && !fuse) {
       __half* xh = (__half*)((char*)a.scratch + base);
       const float hscale = (float)(1.0 / sqrt((double)a.hadamard_dim));
       int st;
@@ -1111,7 +1113,7 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
       if (st != UNIQL_OK) return st;
       lda = a.hadamard_dim;
     }
-    return launch_gemv_group(a, Ain, lda, stream);
+    return launch_gemv_group(a, Ain, lda, fuse, stream);
   }
   DecodePlan pl;
   int st = cached_plan(&pl, a.m, a.k, n, a.nproj, a.epilogue, a.hadamard_dim, a.k_offset);
