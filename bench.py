@@ -282,8 +282,8 @@ def _triple(mod):
 
 def make_step(stack, world, rank, group, mode="none", comm=None, taps=None):
     """Returns step(x) -> y running the projections of every layer: qkv -> o -> [gate, up, SwiGLU] -> Hadamard -> down
-    (no attention maths: the q shard stands in for the attention output).  Four launches per layer at decode sizes on
-    one GPU (qkv, o, gate+up with SwiGLU, down with the Hadamard in its prologue), five in a tensor-parallel layer.
+    (no attention maths: the q shard stands in for the attention output).  Five launches per layer at decode sizes
+    (qkv, o, gate+up with SwiGLU, Hadamard, down).
     mode (world > 1): "fused" = cross-GPU sums and the feature gather inside the decode kernels, "push" = separate
     push all-reduce kernels, "nccl" = torch.distributed collectives.  taps: list that receives the two row-parallel
     outputs (o_proj, down_proj) of every layer."""
@@ -310,7 +310,7 @@ def make_step(stack, world, rank, group, mode="none", comm=None, taps=None):
             if world == 1:
                 y = mods["o"](att)
                 h = fz.gate_up_swiglu(mods["gate"], mods["up"], y)
-                x = mods["down"](h)                        # Hadamard in the linear's prologue (separate kernel above 8 rows)
+                x = mods["down"](h)                        # Hadamard kernel + linear, chained by dependent launch
             elif mode == "fused" and m <= 16:
                 o, d = mods["o"], mods["down"]
                 y = comm.linear_all_reduce(att, o.weight, o.scale, None, o.out_features)
@@ -577,11 +577,10 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # qkv, o, gate+up (SwiGLU in the epilogue), down with the Hadamard transform in its prologue (up to 8 rows on one
-    # GPU; a separate few-row kernel otherwise: 9..16 rows, and tensor-parallel layers, where it reads the gathered row);
-    # the cross-GPU sums and the feature gather ride in the linears' epilogues
+    # qkv, o, gate+up (SwiGLU in the epilogue), Hadamard, down: the cross-GPU sums and the feature gather ride in the
+    # linears' epilogues, the Hadamard kernel of a tensor-parallel layer reads the gathered row directly
     # (larger batches: q, k, v, o, gate, up, Hadamard, down on the tensor-core kernels; SiLU * up is PyTorch's)
-    launches_per_layer = (4 if (m <= 8 and world == 1) else 5) if m <= 16 else 8
+    launches_per_layer = 5 if m <= 16 else 8
     parity = None
     with torch.cuda.stream(stream):
         # ---- tensor parallel: check the sharded result before timing anything ----

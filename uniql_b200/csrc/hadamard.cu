@@ -950,14 +950,6 @@ static bool split_layout(int64_t dim, int base, int64_t* Ps_out, int64_t* B_out,
   return true;
 }
 
-bool hadamard_split_signs(int64_t dim, int64_t* P, int64_t* B, unsigned long long* rows64) {
-  const int base = hadamard_base_of(dim);
-  HadSigns signs;
-  if (base == 0 || !split_layout(dim, base, P, B, &signs)) return false;
-  for (int i = 0; i < 64; ++i) rows64[i] = signs.row[i];
-  return true;
-}
-
 int launch_hadamard_feat(const CommView& cv, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
                          int* status_word, cudaStream_t stream) {
   const int base = hadamard_base_of(dim);

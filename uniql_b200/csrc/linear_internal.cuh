@@ -58,11 +58,9 @@ struct DecodeArgs {
   size_t prefetch_bytes[4];
 };
 
-// CTA-tiled decode kernel (w4a16_gemv.cu).  A: the activations the kernel reads -- already transformed, or, with
-// fused_hadamard, the raw rows whose transform (a.hadamard_dim points) the kernel runs in its own prologue.
+// CTA-tiled decode kernel (w4a16_gemv.cu): single-GPU launches, activations already transformed.
 size_t gemv_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue);
-bool gemv_fuses_hadamard(const DecodeArgs& a);
-int launch_gemv_group(const DecodeArgs& a, const __half* A, int64_t lda, bool fused_hadamard, cudaStream_t stream);
+int launch_gemv_group(const DecodeArgs& a, const __half* A, int64_t lda, cudaStream_t stream);
 
 // m <= 16.  Scratch bytes the launch needs (tickets included).
 size_t decode_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t hadamard_dim,
@@ -90,9 +88,6 @@ int hadamard_base_of(int64_t dim);   // 40/28/20/12/1, or 0 if dim is not a supp
 // fp16 rows (at most 16) read from this rank's feature area of a tensor-parallel layer (see CommView), transformed
 int launch_hadamard_feat(const CommView& cv, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
                          int* status_word, cudaStream_t stream);
-// Few-row factorisation (M (x) H_P) of the transform of `dim` points: P points per segment, B segments, bit a of
-// rows64[s] set <=> M[s][a] = -1.  False if the size does not fit it.
-bool hadamard_split_signs(int64_t dim, int64_t* P, int64_t* B, unsigned long long* rows64);
 // Sign rows of the base matrix: bit a' of row[a] set <=> H[a][a'] = -1 (all zero for base 1).
 void hadamard_base_signs(int base, unsigned long long* rows40);
 

@@ -1093,9 +1093,7 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     if (!a.scratch || a.scratch_bytes < base + xh_bytes || (reinterpret_cast<uintptr_t>(a.scratch) & 255u)) return UNIQL_ESCRATCH;
     const __half* Ain = (const __half*)a.A;
     int64_t lda = a.lda;
-    // few rows, segments of 256 / 512 points, one GPU: the linear transforms its k-range in its own prologue
-    const bool fuse = a.hadamard_dim && gemv_fuses_hadamard(a);
-    if (a.hadamard_dim && !fuse) {
+    if (a.hadamard_dim) {
       __half* xh = (__half*)((char*)a.scratch + base);
       const float hscale = (float)(1.0 / sqrt((double)a.hadamard_dim));
       int st;
@@ -1113,7 +1111,7 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
       if (st != UNIQL_OK) return st;
       lda = a.hadamard_dim;
     }
-    return launch_gemv_group(a, Ain, lda, fuse, stream);
+    return launch_gemv_group(a, Ain, lda, stream);
   }
   DecodePlan pl;
   int st = cached_plan(&pl, a.m, a.k, n, a.nproj, a.epilogue, a.hadamard_dim, a.k_offset);

@@ -33,7 +33,6 @@
 #include "tma.cuh"
 
 #include <cuda.h>
-#include <math.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -81,13 +80,6 @@ struct GemvParams {
   long long pf_lines[4];
   int npf;
   CommView cv;          // tensor parallelism: cross-GPU sum of a row-parallel shard / feature gather of a column shard
-  // online Hadamard transform of the activation rows in this kernel's prologue (had != 0): A holds the untransformed
-  // rows; the transform is (M (x) H_P) with P = 1 << hlogP points per segment and hB segments, M given by its signs
-  int had, hlogP, hB;
-  int had_off;          // byte offset in dynamic shared memory of [transformed rows | exchange buffer]
-  int had_stride;       // halves per transformed row held by a CTA (segments its k-range touches)
-  float hscale;
-  unsigned long long hsign[64];   // bit a of hsign[s] set <=> M[s][a] = -1
 };
 
 constexpr int kGemvSpinLimit = 1 << 22;   // polls of a word another GPU has to write before giving up
@@ -217,94 +209,6 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_addr, uint32_t rank
   return v;
 }
 
-// The online Hadamard transform in the linear's own prologue (up to 8 rows): the CTA computes, into shared memory, the
-// transformed activations of the segments its k-range touches, so that no separate transform launch sits in the decode
-// chain.  The transform factorises as (M (x) H_P) with commuting factors: segment s of the result is
-// H_P (sum_a M[s][a] x_a), x_a the a-th run of P inputs.  P / 8 threads work on one (row, segment) pair -- 8 contiguous
-// elements each: signed sums of the hB input segments (independent 16-byte loads), three butterfly stages in registers,
-// up to five across lanes, and for P = 512 one more across the pair's two warps through shared memory.  Every CTA of a
-// column group repeats the work of its k-range (a few microseconds of one CTA, all of them in parallel).
-__device__ __noinline__ void gemv_hadamard_prologue(const GemvParams& p, __half* xh, float* hbuf, int seg0, int nseg,
-                                                    int m_rows) {
-  const int tid = threadIdx.x, lane = tid & 31;
-  const int P = 1 << p.hlogP;
-  const int lt = p.hlogP - 3;                        // log2(threads per pair)
-  const int worker = tid >> lt, wt = tid & ((1 << lt) - 1);
-  const int nworkers = kGemvThreads >> lt;
-  const int npairs = m_rows * nseg;
-  for (int q0 = 0; q0 < npairs; q0 += nworkers) {    // same trip count for every thread: the barriers below are safe
-    const int q = q0 + worker;
-    const bool on = q < npairs;
-    const int row = on ? q / nseg : 0, seg = on ? seg0 + q % nseg : 0;
-    float v[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = 0.f;
-    if (on) {
-      const unsigned long long mask = p.hsign[seg];
-      const __half* xr = p.A + (size_t)row * p.lda + wt * 8;
-      constexpr int kBatch = 14;
-      for (int a0 = 0; a0 < p.hB; a0 += kBatch) {
-        uint4 raw[kBatch];
-#pragma unroll
-        for (int i = 0; i < kBatch; ++i)
-          if (a0 + i < p.hB) raw[i] = ld_nc16(xr + ((size_t)(a0 + i) << p.hlogP));
-#pragma unroll
-        for (int i = 0; i < kBatch; ++i)
-          if (a0 + i < p.hB) {
-            const __half2* h2 = reinterpret_cast<const __half2*>(&raw[i]);
-            const float sg = ((mask >> (a0 + i)) & 1ull) ? -1.f : 1.f;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __half22float2(h2[e]);
-              v[2 * e] = fmaf(sg, f.x, v[2 * e]);
-              v[2 * e + 1] = fmaf(sg, f.y, v[2 * e + 1]);
-            }
-          }
-      }
-    }
-#pragma unroll
-    for (int s = 1; s < 8; s <<= 1)
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (!(i & s)) {
-          const float lo = v[i], hi = v[i | s];
-          v[i] = lo + hi;
-          v[i | s] = lo - hi;
-        }
-#pragma unroll
-    for (int s = 0; s < 5; ++s)
-      if ((8 << s) < P) {
-        const bool upper = (lane >> s) & 1;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float o = __shfl_xor_sync(0xffffffffu, v[i], 1 << s);
-          v[i] = upper ? (o - v[i]) : (v[i] + o);
-        }
-      }
-    if (P == 512) {
-      // elements e and e ^ 256 sit in the pair's two warps, same lane: one exchange through shared memory
-      float* mine = hbuf + (size_t)worker * 512 + wt * 8;
-      *reinterpret_cast<float4*>(mine) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(mine + 4) = make_float4(v[4], v[5], v[6], v[7]);
-      asm volatile("bar.sync %0, 64;" ::"r"(10 + worker) : "memory");
-      const float* other = hbuf + (size_t)worker * 512 + ((wt * 8) ^ 256);
-      const float4 o0 = *reinterpret_cast<const float4*>(other), o1 = *reinterpret_cast<const float4*>(other + 4);
-      const float o[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
-      const bool upper = wt >= 32;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = upper ? (o[i] - v[i]) : (v[i] + o[i]);
-      asm volatile("bar.sync %0, 64;" ::"r"(10 + worker) : "memory");      // the buffer is free for the next pair
-    }
-    if (on) {
-      uint4 out;
-      __half2* h2 = reinterpret_cast<__half2*>(&out);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) h2[e] = __floats2half2_rn(v[2 * e] * p.hscale, v[2 * e + 1] * p.hscale);
-      *reinterpret_cast<uint4*>(xh + (size_t)row * p.had_stride + ((size_t)(seg - seg0) << p.hlogP) + wt * 8) = out;
-    }
-  }
-}
-
 template <int MT>
 __global__ void __launch_bounds__(kGemvThreads, MT == 1 ? kCtasMt1 : 2)
 w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
@@ -375,22 +279,9 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
     }
   }
 
-  const int m_staged = p.xs_rows - 1;                 // real rows staged by this kernel (M, at most 8*MT)
-  // online Hadamard: transformed rows of the segments this CTA's k-range touches, in shared memory
-  const __half* xh_s = nullptr;
-  int xh_k0 = 0;                                      // first k value held in xh_s
-  if (p.had) {
-    const int gA = cta_k0 >> 3, gB = (cta_k1 + 7) >> 3;
-    const int seg0 = (gA * 128) >> p.hlogP, seg1 = (gB * 128 + (1 << p.hlogP) - 1) >> p.hlogP;
-    __half* xh = reinterpret_cast<__half*>(smem_raw + p.had_off);
-    float* hbuf = reinterpret_cast<float*>(smem_raw + p.had_off + (size_t)m_staged * p.had_stride * 2);
-    gemv_hadamard_prologue(p, xh, hbuf, seg0, seg1 - seg0, m_staged);
-    __syncthreads();
-    xh_s = xh;
-    xh_k0 = seg0 << p.hlogP;
-  }
   const int row_threads = p.WN * 32;
   const int row_tid = wn * 32 + lane;
+  const int m_staged = p.xs_rows - 1;                 // real rows staged by this kernel (M, at most 8*MT)
   // the extra row is read by MMA lanes whose batch row does not exist: clear it once
   for (int v = row_tid; v < p.xs_stride / 8; v += row_threads)
     *reinterpret_cast<uint4*>(xs + (size_t)m_staged * p.xs_stride + v * 8) = make_uint4(0, 0, 0, 0);
@@ -431,16 +322,9 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
             lo[i] = make_uint4(0, 0, 0, 0);
             hi[i] = make_uint4(0, 0, 0, 0);
             if (vin && r0 + i < m_staged) {
-              if (xh_s) {
-                const uint4* s16 = reinterpret_cast<const uint4*>(xh_s + (size_t)(r0 + i) * p.had_stride +
-                                                                  (gi * 128 - xh_k0) + v * 16);
-                lo[i] = s16[0];
-                hi[i] = s16[1];
-              } else {
-                const __half* s16 = src + (size_t)(r0 + i) * p.lda + v * 16;
-                lo[i] = ld_nc16(s16);
-                hi[i] = ld_nc16(s16 + 8);
-              }
+              const __half* s16 = src + (size_t)(r0 + i) * p.lda + v * 16;
+              lo[i] = ld_nc16(s16);
+              hi[i] = ld_nc16(s16 + 8);
             }
           }
 #pragma unroll
@@ -782,8 +666,6 @@ struct GemvPlan {
   int cluster, ctile_off;
   size_t smem;
   size_t partial_bytes;
-  // Hadamard prologue (hlogP != 0): whether it fits, where its buffers sit and how many halves a transformed row holds
-  int had_ok, had_off, had_stride;
 };
 
 // n: width of the launch's virtual column space (all projections side by side).  pair: the blocks alternate gate / up,
@@ -800,27 +682,27 @@ static const GemvEnv& gemv_env() {
   return e;
 }
 
-static GemvPlan make_gemv_plan(int64_t m, int64_t n, int64_t k, bool pair, int hlogP);
+static GemvPlan make_gemv_plan(int64_t m, int64_t n, int64_t k, bool pair);
 
-// Plans are a pure function of (m, n, k, pair, hlogP): the last few are remembered so that an eager decode loop does
-// not run the cost model on every launch.  hlogP != 0 asks for room for the Hadamard prologue (segments of 2^hlogP).
-static GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k, bool pair, int hlogP = 0) {
-  struct Entry { int64_t m, n, k; bool pair; int hlogP; GemvPlan plan; };
+// Plans are a pure function of (m, n, k, pair): the last few are remembered so that an eager decode loop does not run
+// the cost model on every launch.
+static GemvPlan plan_gemv(int64_t m, int64_t n, int64_t k, bool pair) {
+  struct Entry { int64_t m, n, k; bool pair; GemvPlan plan; };
   static std::mutex mu;
   static std::vector<Entry> cache;
   {
     std::lock_guard<std::mutex> lk(mu);
     for (const Entry& e : cache)
-      if (e.m == m && e.n == n && e.k == k && e.pair == pair && e.hlogP == hlogP) return e.plan;
+      if (e.m == m && e.n == n && e.k == k && e.pair == pair) return e.plan;
   }
-  const GemvPlan plan = make_gemv_plan(m, n, k, pair, hlogP);
+  const GemvPlan plan = make_gemv_plan(m, n, k, pair);
   std::lock_guard<std::mutex> lk(mu);
   if (cache.size() >= 256) cache.clear();
-  cache.push_back({m, n, k, pair, hlogP, plan});
+  cache.push_back({m, n, k, pair, plan});
   return plan;
 }
 
-static GemvPlan make_gemv_plan(int64_t m, int64_t n, int64_t k, bool pair, int hlogP) {
+static GemvPlan make_gemv_plan(int64_t m, int64_t n, int64_t k, bool pair) {
   GemvPlan best{};
   const int MT = m <= 8 ? 1 : 2;
   const int nblk = (int)(n / 64), KT = (int)(k / 16), NG = KT / 8;
@@ -856,28 +738,7 @@ static GemvPlan make_gemv_plan(int64_t m, int64_t n, int64_t k, bool pair, int h
   // Shared memory per CTA: rings = 8 warps x R slots x 4 KB, then the staged activations
   // = WK warp rows x (rows + 1) x (GCH*128 + pad) halves.  Budget: 3 CTAs per SM for m <= 8, else 2.
   const int rows = (int)(m < 8 * MT ? m : 8 * MT) + 1;
-  size_t budget = (MT == 1 && kCtasMt1 == 3 ? 74 : 110) * 1024;
-  // Hadamard prologue: transformed rows of the segments the widest CTA k-range touches + 8 KB exchange buffer
-  size_t had_bytes = 0;
-  best.had_ok = 0;
-  if (hlogP && m <= 8) {
-    const int P = 1 << hlogP;
-    int max_nseg = 0;
-    for (int y = 0; y < best.S; ++y) {
-      const int k0 = (int)((int64_t)KT * y / best.S), k1 = (int)((int64_t)KT * (y + 1) / best.S);
-      const int gA = k0 >> 3, gB = (k1 + 7) >> 3;
-      const int nseg = ((gB * 128 + P - 1) >> hlogP) - ((gA * 128) >> hlogP);
-      if (nseg > max_nseg) max_nseg = nseg;
-    }
-    best.had_stride = max_nseg * P;
-    had_bytes = (size_t)m * best.had_stride * 2 + 4 * 512 * 4;
-    if (had_bytes <= 26 * 1024) {
-      best.had_ok = 1;
-      budget -= had_bytes;
-    } else {
-      had_bytes = 0;
-    }
-  }
+  const size_t budget = (MT == 1 && kCtasMt1 == 3 ? 74 : 110) * 1024;
   const size_t xs_min = (size_t)best.WK * rows * (128 + kXsPad) * 2 + (size_t)best.WK * 8 * 64;
   int R = (int)((budget - xs_min) / (kGemvWarps * kSlotBytes));
   // two slots per warp measured faster than three for m <= 8 (39.1 vs 41.6 us per Llama-3.1-8B layer)
@@ -899,9 +760,7 @@ static GemvPlan make_gemv_plan(int64_t m, int64_t n, int64_t k, bool pair, int h
   best.xs_rows = rows;
   const size_t xs_bytes = (size_t)best.WK * rows * (gch * 128 + kXsPad) * 2 + (size_t)best.WK * gch * 64;
   const size_t red_bytes = (size_t)kGemvWarps * 8 * MT * kRedStride * 4;
-  best.had_off = (int)((ring_bytes + xs_bytes + 127) / 128 * 128);
-  const size_t main_bytes = best.had_ok ? (size_t)best.had_off + had_bytes : ring_bytes + xs_bytes;
-  best.smem = main_bytes > red_bytes ? main_bytes : red_bytes;
+  best.smem = ring_bytes + xs_bytes > red_bytes ? ring_bytes + xs_bytes : red_bytes;
   // cluster mode (2 <= S <= 8): the CTA's reduced tile lives behind the warp reduction buffer
   best.cluster = (gemv_env().cluster && best.S >= 2 && best.S <= 8) ? 1 : 0;
   best.ctile_off = (int)((red_bytes + 1023) / 1024 * 1024);
@@ -925,25 +784,8 @@ size_t gemv_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int
   return UNIQL_SCRATCH_COUNTER_BYTES + (plan.partial_bytes + 255) / 256 * 256;
 }
 
-// Whether the transform of this launch can run in the kernel's own prologue: whole-row transform on one GPU, up to 8
-// rows, segments of 256 or 512 points, and room for the transformed rows beside the rings (UNIQL_B200_FUSED_HADAMARD=0
-// keeps the separate transform kernel).
-bool gemv_fuses_hadamard(const DecodeArgs& a) {
-  static const int fuse_on = env_int("UNIQL_B200_FUSED_HADAMARD", 1);
-  if (!fuse_on || !a.hadamard_dim || a.hadamard_dim != a.k || a.k_offset != 0 || a.m > 8) return false;
-  if (a.comm && a.comm->gather_in) return false;
-  int64_t P = 0, B = 0;
-  unsigned long long rows[64];
-  if (!hadamard_split_signs(a.hadamard_dim, &P, &B, rows) || (P != 256 && P != 512)) return false;
-  int64_t widths[kMaxProj] = {0, 0, 0, 0};
-  for (int i = 0; i < a.nproj && i < kMaxProj; ++i) widths[i] = a.proj[i].n;
-  const GemvPlan plan = plan_gemv(a.m, virtual_width(widths, a.nproj), a.k, a.epilogue == UNIQL_EPILOGUE_SWIGLU,
-                                  P == 512 ? 9 : 8);
-  return plan.had_ok != 0;
-}
-
-// A: the activations the kernel multiplies with -- transformed already, or raw with fused_hadamard.
-int launch_gemv_group(const DecodeArgs& a, const __half* A, int64_t lda, bool fused_hadamard, cudaStream_t stream) {
+// A: the activations the kernel multiplies with (already transformed if the layer has an online Hadamard).
+int launch_gemv_group(const DecodeArgs& a, const __half* A, int64_t lda, cudaStream_t stream) {
   if (a.nproj < 1 || a.nproj > kMaxProj || a.m < 1 || a.m > 16 || a.k % 128) return UNIQL_ESHAPE;
   const bool pair = a.epilogue == UNIQL_EPILOGUE_SWIGLU;
   if (pair && (a.nproj != 2 || a.proj[0].n != a.proj[1].n)) return UNIQL_EINVAL;
@@ -953,21 +795,9 @@ int launch_gemv_group(const DecodeArgs& a, const __half* A, int64_t lda, bool fu
     widths[i] = a.proj[i].n;
   }
   const int64_t nv = virtual_width(widths, a.nproj);
+  const GemvPlan plan = plan_gemv(a.m, nv, a.k, pair);
   GemvParams p;
   memset(&p, 0, sizeof(p));
-  int hlogP = 0;
-  if (fused_hadamard) {
-    int64_t P = 0, B = 0;
-    if (!hadamard_split_signs(a.hadamard_dim, &P, &B, p.hsign) || (P != 256 && P != 512)) return UNIQL_ESHAPE;
-    hlogP = P == 512 ? 9 : 8;
-    p.had = 1; p.hlogP = hlogP; p.hB = (int)B;
-    p.hscale = (float)(1.0 / sqrt((double)a.hadamard_dim));
-  }
-  const GemvPlan plan = plan_gemv(a.m, nv, a.k, pair, hlogP);
-  if (fused_hadamard) {
-    if (!plan.had_ok) return UNIQL_ESHAPE;
-    p.had_off = plan.had_off; p.had_stride = plan.had_stride;
-  }
   int vb = 0;
   for (int i = 0; i < a.nproj; ++i) {
     const DecodeProjArgs& q = a.proj[i];
