@@ -735,12 +735,10 @@ __global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict
                                                              T* __restrict__ y, int64_t ldy, int P, int B,
                                                              float scale, const HadSigns signs, int pdl_trigger) {
   __shared__ __align__(16) float buf[1024];
-  if (pdl_trigger) {
-    // part of a decode chain: launched as a programmatic dependent of the kernel that writes x, so it is resident and
-    // past its set-up when that kernel ends; its own dependent (the linear) starts its weight stream right away
-    pdl_launch_dependents();
-    pdl_wait();
-  }
+  // In a decode chain the linear behind this kernel starts its weight stream right away.  The kernel itself is a plain
+  // stream-ordered launch: started as a programmatic dependent of its producer it gained 0.5 us per Llama layer and
+  // lost 1 us per Mamba layer (its early-resident successor competes with the producer's own stream).
+  if (pdl_trigger) pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31;
   const int seg = blockIdx.x;
   const T* xr = x + (int64_t)blockIdx.y * ldx;
@@ -819,7 +817,6 @@ __global__ void __launch_bounds__(128) hadamard_split_feat_kernel(const unsigned
                                                                   const HadSigns signs, int* status_word) {
   __shared__ __align__(16) float buf[1024];
   pdl_launch_dependents();                       // the linear behind this kernel only prefetches until it waits on us
-  pdl_wait();                                    // this rank's producer launch has ended: its epoch counter is current
   const int tid = threadIdx.x, lane = tid & 31;
   const int seg = blockIdx.x, row = blockIdx.y;
   const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(area + epoch_off);
@@ -889,24 +886,6 @@ __global__ void __launch_bounds__(128) hadamard_split_feat_kernel(const unsigned
   Elem<__half>::store8(yr + tid * 8, v);
 }
 
-// Launch of a few-row kernel inside a decode chain: with the programmatic-serialisation attribute the kernel may start
-// while its producer still runs (it waits with griddepcontrol.wait before it reads), so its launch latency is hidden.
-template <typename... KArgs, typename... Args>
-static int launch_chained(void (*kern)(KArgs...), dim3 grid, int threads, cudaStream_t stream, bool chained, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3((unsigned)threads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = chained ? 1 : 0;
-  UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, KArgs(args)...));
-  return UNIQL_OK;
-}
-
 // Segment layout of the few-row kernels: dim = B segments of Ps points.  Returns false if the size does not fit them.
 // The sign words of the last few sizes are remembered (a decode loop asks for the same one on every step).
 static bool split_layout(int64_t dim, int base, int64_t* Ps_out, int64_t* B_out, HadSigns* signs) {
@@ -958,10 +937,10 @@ int launch_hadamard_feat(const CommView& cv, void* y, int64_t ldy, int64_t rows,
   int64_t Ps = 0, B = 0;
   if (!split_layout(dim, base, &Ps, &B, &signs)) return UNIQL_ESHAPE;
   dim3 grid((unsigned)B, (unsigned)rows);
-  static const bool pdl_on = [] { const char* e = getenv("UNIQL_B200_PDL"); return !(e && *e && atoi(e) == 0); }();
-  return launch_chained(hadamard_split_feat_kernel, grid, (int)(Ps / 8), stream, pdl_on,
-                        (const unsigned char*)cv.bufs[cv.rank], cv.gather_off, cv.gather_epoch_off, cv.feat_cap, (__half*)y,
-                        ldy, (int)Ps, (int)B, scale, signs, status_word);
+  hadamard_split_feat_kernel<<<grid, (int)(Ps / 8), 0, stream>>>(cv.bufs[cv.rank], cv.gather_off, cv.gather_epoch_off,
+                                                               cv.feat_cap, (__half*)y, ldy, (int)Ps, (int)B, scale,
+                                                               signs, status_word);
+  return launch_status();
 }
 
 int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,
@@ -982,19 +961,15 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
     if (split_layout(dim, base, &Ps, &B, &signs)) {
       dim3 grid((unsigned)B, (unsigned)rows);
       const int threads = (int)(Ps / 8);
-      static const bool pdl_on = [] { const char* e = getenv("UNIQL_B200_PDL"); return !(e && *e && atoi(e) == 0); }();
-      const bool chained = pdl_trigger && pdl_on;
       const int trig = pdl_trigger ? 1 : 0;
       if (dtype == UNIQL_F16)
-        return launch_chained(hadamard_split_kernel<__half>, grid, threads, stream, chained, (const __half*)x, ldx,
-                              (__half*)y, ldy, (int)Ps, (int)B, scale, signs, trig);
-      if (dtype == UNIQL_BF16)
-        return launch_chained(hadamard_split_kernel<__nv_bfloat16>, grid, threads, stream, chained,
-                              (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)y, ldy, (int)Ps, (int)B, scale, signs, trig);
-      if (dtype == UNIQL_F32)
-        return launch_chained(hadamard_split_kernel<float>, grid, threads, stream, chained, (const float*)x, ldx,
-                              (float*)y, ldy, (int)Ps, (int)B, scale, signs, trig);
-      return UNIQL_EDTYPE;
+        hadamard_split_kernel<__half><<<grid, threads, 0, stream>>>((const __half*)x, ldx, (__half*)y, ldy, (int)Ps, (int)B, scale, signs, trig);
+      else if (dtype == UNIQL_BF16)
+        hadamard_split_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)y, ldy, (int)Ps, (int)B, scale, signs, trig);
+      else if (dtype == UNIQL_F32)
+        hadamard_split_kernel<float><<<grid, threads, 0, stream>>>((const float*)x, ldx, (float*)y, ldy, (int)Ps, (int)B, scale, signs, trig);
+      else return UNIQL_EDTYPE;
+      return launch_status();
     }
   }
   for (int i = 0; i < 64; ++i) signs.row[i] = 0;
