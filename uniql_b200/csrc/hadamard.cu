@@ -585,31 +585,25 @@ __device__ __forceinline__ void had_cp_async16(void* smem_dst, const void* gmem_
 }
 
 template <typename T, int MT, int LOGP>
-__global__ void __launch_bounds__(MT * (1 << (LOGP - 7)) * 32, MT <= 2 ? 3 : 2)
-    hadamard_mma_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy, int base, float scale,
-                        const HadSigns signs, int pdl_trigger) {
+__global__ void __launch_bounds__(MT * (1 << (LOGP - 7)) * 32, (MT == 3 && LOGP == 9) ? 1 : 2)
+    hadamard_mma_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy, int64_t rows, int base,
+                        float scale, const HadSigns signs, int pdl_trigger) {
   constexpr int KT = MT;
   constexpr int P = 1 << LOGP;
   constexpr int NU = P / 128;
   constexpr int NTHREADS = MT * NU * 32;
-  constexpr int RS = P + 8;     // raw row stride, 16-bit elements
-  constexpr int FS = P + 8;     // fp32 row stride, words (= 8 mod 32: the float2 stores of a half-warp hit 32 banks)
+  constexpr int RS = P + 8;     // row stride of the raw row (16-bit elements) and of the fp32 tile (words); 8 mod 32
+  // Shared memory: three regions of base * RS * 2 bytes.  The raw row of iteration i sits in region c = 2 i mod 3; its
+  // fp32 tile (twice the size) takes regions c and c + 1 -- rows a' < base / 2 in the first, the rest in the second;
+  // the next row is fetched into region c + 2 while this one is worked on.
   extern __shared__ __align__(16) unsigned char had_smem[];
-  T* raw = reinterpret_cast<T*>(had_smem);
-  float* fb = reinterpret_cast<float*>(had_smem);
+  const int region_bytes = base * RS * 2;
+  const int half_rows = base >> 1;
   if (pdl_trigger) pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const T* xr = x + (int64_t)blockIdx.x * ldx;
-  T* yr = y + (int64_t)blockIdx.x * ldy;
 
-  for (int ch = tid; ch < base * (P / 8); ch += NTHREADS) {
-    const int a = ch >> (LOGP - 3), cb = ch & (P / 8 - 1);
-    had_cp_async16(raw + a * RS + cb * 8, xr + (size_t)a * P + cb * 8);
-  }
-  asm volatile("cp.async.commit_group;" ::: "memory");
-
-  // H as the 16-row operand (rows a', k = a), zero outside base x base
+  // H as the 16-row operand (rows a', k = a), zero outside base x base: built once per CTA
   const int mt = warp % MT, u = warp / MT;
   uint32_t afrag[KT][4];
 #pragma unroll
@@ -632,102 +626,129 @@ __global__ void __launch_bounds__(MT * (1 << (LOGP - 7)) * 32, MT <= 2 ? 3 : 2)
   if (k0 >= base) k0 = 0;
   int k1 = 32 + (lane & 15);
   if (k1 >= base) k1 = 0;
-  const uint32_t row0 = had_smem_addr(raw + k0 * RS + 128 * u);
-  const uint32_t row1 = had_smem_addr(raw + k1 * RS + 128 * u);
+  const uint32_t smem0 = had_smem_addr(had_smem);
+  const uint32_t off0 = (uint32_t)(k0 * RS + 128 * u) * 2, off1 = (uint32_t)(k1 * RS + 128 * u) * 2;
 
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  __syncthreads();
-
-  float acc[16][4];
-#pragma unroll
-  for (int t = 0; t < 16; ++t) {
-    acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-    uint32_t b[6];
-    if constexpr (KT == 1) {
-      asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
-                   : "=r"(b[0]), "=r"(b[1]) : "r"(row0 + t * 16));
-    } else {
-      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(row0 + t * 16));
-      if constexpr (KT == 3)
-        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
-                     : "=r"(b[4]), "=r"(b[5]) : "r"(row1 + t * 16));
+  auto fetch = [&](int64_t row, int region) {
+    const T* xr = x + row * ldx;
+    T* dst = reinterpret_cast<T*>(had_smem + (size_t)region * region_bytes);
+    for (int ch = tid; ch < base * (P / 8); ch += NTHREADS) {
+      const int a = ch >> (LOGP - 3), cb = ch & (P / 8 - 1);
+      had_cp_async16(dst + a * RS + cb * 8, xr + (size_t)a * P + cb * 8);
     }
-#pragma unroll
-    for (int kt = 0; kt < KT; ++kt) MmaOp<T>::mma(acc[t], afrag[kt], b[2 * kt], b[2 * kt + 1]);
-  }
-  // b = 128 u + 8 t + 2 c + e: bit 0 is the accumulator pair, bits 3..6 the n-tile index
-#pragma unroll
-  for (int t = 0; t < 16; ++t) {
-    const float a0 = acc[t][0], a1 = acc[t][1], a2 = acc[t][2], a3 = acc[t][3];
-    acc[t][0] = a0 + a1; acc[t][1] = a0 - a1; acc[t][2] = a2 + a3; acc[t][3] = a2 - a3;
-  }
-#pragma unroll
-  for (int s = 1; s < 16; s <<= 1)
-#pragma unroll
-    for (int t = 0; t < 16; ++t)
-      if (!(t & s)) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float lo = acc[t][j], hi = acc[t | s][j];
-          acc[t][j] = lo + hi;
-          acc[t | s][j] = lo - hi;
-        }
-      }
-  __syncthreads();                       // every warp has read its part of the raw row: the space becomes the fp32 tile
-  {
-    const int ra = 16 * mt + g;
-    float* fa = fb + ra * FS + 128 * u + 2 * c;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  int64_t row = blockIdx.x;
+  int reg = 0;                                   // region of the current row
+  if (row < rows) fetch(row, 0);
+  for (; row < rows; row += gridDim.x) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                             // this row has landed; the previous row's second pass is over
+    const int reg1 = reg + 1 >= 3 ? reg - 2 : reg + 1, reg2 = reg + 2 >= 3 ? reg - 1 : reg + 2;
+    if (row + gridDim.x < rows) fetch(row + gridDim.x, reg2);
+    const uint32_t raw_base = smem0 + (uint32_t)reg * region_bytes;
+
+    float acc[16][4];
 #pragma unroll
     for (int t = 0; t < 16; ++t) {
-      if (ra < base) *reinterpret_cast<float2*>(fa + 8 * t) = make_float2(acc[t][0], acc[t][1]);
-      if (ra + 8 < base) *reinterpret_cast<float2*>(fa + 8 * FS + 8 * t) = make_float2(acc[t][2], acc[t][3]);
+      acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+      uint32_t b[6];
+      if constexpr (KT == 1) {
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                     : "=r"(b[0]), "=r"(b[1]) : "r"(raw_base + off0 + t * 16));
+      } else {
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(raw_base + off0 + t * 16));
+        if constexpr (KT == 3)
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                       : "=r"(b[4]), "=r"(b[5]) : "r"(raw_base + off1 + t * 16));
+      }
+#pragma unroll
+      for (int kt = 0; kt < KT; ++kt) MmaOp<T>::mma(acc[t], afrag[kt], b[2 * kt], b[2 * kt + 1]);
     }
-  }
-  __syncthreads();
-  for (int task = tid; task < base * 16; task += NTHREADS) {
-    const int ap = task >> 4, q = task & 15;
-    const float* src = fb + ap * FS + 8 * q;
-    float v[NU][8];
-    const int flip = (q >> 2) & 1;       // lanes q and q + 4 share banks: they take the two 16-byte halves in turn
+    // b = 128 u + 8 t + 2 c + e: bit 0 is the accumulator pair, bits 3..6 the n-tile index
 #pragma unroll
-    for (int h = 0; h < NU; ++h) {
-      const float4 p0 = *reinterpret_cast<const float4*>(src + 128 * h + 4 * flip);
-      const float4 p1 = *reinterpret_cast<const float4*>(src + 128 * h + 4 * (flip ^ 1));
-      const float4 lo = flip ? p1 : p0, hi = flip ? p0 : p1;
-      v[h][0] = lo.x; v[h][1] = lo.y; v[h][2] = lo.z; v[h][3] = lo.w;
-      v[h][4] = hi.x; v[h][5] = hi.y; v[h][6] = hi.z; v[h][7] = hi.w;
+    for (int t = 0; t < 16; ++t) {
+      const float a0 = acc[t][0], a1 = acc[t][1], a2 = acc[t][2], a3 = acc[t][3];
+      acc[t][0] = a0 + a1; acc[t][1] = a0 - a1; acc[t][2] = a2 + a3; acc[t][3] = a2 - a3;
     }
 #pragma unroll
-    for (int h = 0; h < NU; ++h)
+    for (int s = 1; s < 16; s <<= 1)
 #pragma unroll
-      for (int s = 2; s < 8; s <<= 1)
+      for (int t = 0; t < 16; ++t)
+        if (!(t & s)) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          if (!(e & s)) {
-            const float lo = v[h][e], hi = v[h][e | s];
-            v[h][e] = lo + hi;
-            v[h][e | s] = lo - hi;
-          }
-#pragma unroll
-    for (int s = 1; s < NU; s <<= 1)
-#pragma unroll
-      for (int h = 0; h < NU; ++h)
-        if (!(h & s)) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float lo = v[h][e], hi = v[h | s][e];
-            v[h][e] = lo + hi;
-            v[h | s][e] = lo - hi;
+          for (int j = 0; j < 4; ++j) {
+            const float lo = acc[t][j], hi = acc[t | s][j];
+            acc[t][j] = lo + hi;
+            acc[t | s][j] = lo - hi;
           }
         }
+    __syncthreads();                     // every warp has read its part of the raw row: the space becomes the fp32 tile
+    // fp32 tile: row a' in region reg (a' < base / 2) or reg1; inside a row the two 16-byte halves of every odd
+    // 32-float block are swapped, so that the second pass reads 16-byte vectors without bank conflicts
+    float* f_lo = reinterpret_cast<float*>(had_smem + (size_t)reg * region_bytes);
+    float* f_hi = reinterpret_cast<float*>(had_smem + (size_t)reg1 * region_bytes) - (size_t)half_rows * RS;
+    {
+      const int ra = 16 * mt + g, rb = ra + 8;
+      float* fa = (ra < half_rows ? f_lo : f_hi) + ra * RS + 128 * u;
+      float* fb2 = (rb < half_rows ? f_lo : f_hi) + rb * RS + 128 * u;
+      const int c_plain = 2 * c, c_swap = (2 * c) ^ 4;      // column inside the 8-float tile, halves swapped or not
 #pragma unroll
-    for (int h = 0; h < NU; ++h) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[h][e] *= scale;
-      Elem<T>::store8(yr + (size_t)ap * P + 128 * h + 8 * q, v[h]);
+      for (int t = 0; t < 16; ++t) {
+        const int col = 8 * t + ((t & 4) ? c_swap : c_plain);   // bit 5 of the column index set <=> t & 4
+        if (ra < base) *reinterpret_cast<float2*>(fa + col) = make_float2(acc[t][0], acc[t][1]);
+        if (rb < base) *reinterpret_cast<float2*>(fb2 + col) = make_float2(acc[t][2], acc[t][3]);
+      }
     }
+    __syncthreads();
+    T* yr = y + row * ldy;
+    for (int task = tid; task < base * 16; task += NTHREADS) {
+      const int ap = task >> 4, q = task & 15;
+      const int flip = (q >> 2) & 1;
+      const float* src = (ap < half_rows ? f_lo : f_hi) + ap * RS + 8 * q;
+      float v[NU][8];
+#pragma unroll
+      for (int h = 0; h < NU; ++h) {
+        const float4 lo = *reinterpret_cast<const float4*>(src + 128 * h + 4 * flip);
+        const float4 hi = *reinterpret_cast<const float4*>(src + 128 * h + 4 * (flip ^ 1));
+        v[h][0] = lo.x; v[h][1] = lo.y; v[h][2] = lo.z; v[h][3] = lo.w;
+        v[h][4] = hi.x; v[h][5] = hi.y; v[h][6] = hi.z; v[h][7] = hi.w;
+      }
+#pragma unroll
+      for (int h = 0; h < NU; ++h)
+#pragma unroll
+        for (int s = 2; s < 8; s <<= 1)
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (!(e & s)) {
+              const float lo = v[h][e], hi = v[h][e | s];
+              v[h][e] = lo + hi;
+              v[h][e | s] = lo - hi;
+            }
+#pragma unroll
+      for (int s = 1; s < NU; s <<= 1)
+#pragma unroll
+        for (int h = 0; h < NU; ++h)
+          if (!(h & s)) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float lo = v[h][e], hi = v[h | s][e];
+              v[h][e] = lo + hi;
+              v[h | s][e] = lo - hi;
+            }
+          }
+#pragma unroll
+      for (int h = 0; h < NU; ++h) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[h][e] *= scale;
+        Elem<T>::store8(yr + (size_t)ap * P + 128 * h + 8 * q, v[h]);
+      }
+    }
+    reg = reg2;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 template <typename T>
@@ -993,22 +1014,24 @@ int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t ro
           if (neg) ms.row[i] |= (1ull << j);
         }
       const int MTv = (mbase + 15) / 16, logp = mP == 128 ? 7 : mP == 256 ? 8 : 9;
-      const size_t smem = (size_t)mbase * (size_t)(mP + 8) * sizeof(float);
+      const size_t smem = (size_t)3 * mbase * (size_t)(mP + 8) * 2;      // three raw-row regions
       const int threads = MTv * (int)(mP / 128) * 32;
 #define UNIQL_HAD_MMA_CASE(T, MT_, LP_)                                                                       \
   do {                                                                                                        \
-    static thread_local bool attr_done[64] = {};   /* function attributes are per device */                   \
-    if (!attr_done[cur_dev]) {                                                                                \
+    static thread_local int ctas_per_sm[64] = {};  /* function attributes and occupancy are per device */     \
+    if (!ctas_per_sm[cur_dev]) {                                                                              \
       UNIQL_CUDA_TRY(cudaFuncSetAttribute(hadamard_mma_kernel<T, MT_, LP_>,                                   \
                                           cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
-                                          (int)(16 * MT_ * ((1 << LP_) + 8) * sizeof(float))));               \
-      attr_done[cur_dev] = true;                                                                              \
+                                          (int)(3 * 16 * MT_ * ((1 << LP_) + 8) * 2)));                       \
+      int occ = 0;                                                                                            \
+      UNIQL_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(                                           \
+          &occ, hadamard_mma_kernel<T, MT_, LP_>, threads, (size_t)(3 * 16 * MT_ * ((1 << LP_) + 8) * 2)));   \
+      ctas_per_sm[cur_dev] = occ < 1 ? 1 : (occ > 4 ? 4 : occ);                                               \
     }                                                                                                         \
-    for (int64_t r0 = 0; r0 < rows; r0 += (int64_t)1 << 30) {                                                 \
-      const int64_t nr = rows - r0 < ((int64_t)1 << 30) ? rows - r0 : ((int64_t)1 << 30);                     \
-      hadamard_mma_kernel<T, MT_, LP_><<<(unsigned)nr, threads, smem, stream>>>(                              \
-          (const T*)x + r0 * ldx, ldx, (T*)y + r0 * ldy, ldy, mbase, scale, ms, pdl_trigger ? 1 : 0);         \
-    }                                                                                                         \
+    const int64_t max_ctas = (int64_t)ctas_per_sm[cur_dev] * device_info().sm_count;                          \
+    const unsigned grid = (unsigned)(rows < max_ctas ? rows : max_ctas);                                      \
+    hadamard_mma_kernel<T, MT_, LP_><<<grid, threads, smem, stream>>>((const T*)x, ldx, (T*)y, ldy, rows, mbase, \
+                                                                      scale, ms, pdl_trigger ? 1 : 0);        \
     return launch_status();                                                                                   \
   } while (0)
 #define UNIQL_HAD_MMA_LOGP(T, MT_)                                                                            \
