@@ -620,6 +620,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
   // instruction descriptor: D fp32, A/B fp16, both K-major, M = 128 (weight columns), N = Mb (batch rows)
   const uint32_t idesc = (1u << 4) | ((uint32_t)(p.Mb >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
+  pdl_launch_dependents();                       // the next kernel in the stream may start its own set-up and weights
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&xmap) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
@@ -666,6 +667,10 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
   } else if (warp == 2) {
     // ------------------------------------------------------------------ activation producer (re-reads, L2 hits)
     if (lane == 0) {
+      // Programmatic dependent launch: everything up to here (barriers, tensor memory, the first weight tiles, the
+      // dequantise warps' scale loads) ran while the producer of the activations was still finishing; the activation
+      // tiles are the only thing that has to wait for it.  Results are stored after MMAs that consumed those tiles.
+      pdl_wait();
       int kb = 0;
       for (int it = 0; it < total_it; ++it) {
         const int s = it % STAGES;
@@ -992,23 +997,29 @@ static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda
     while (split > 1 && forced <= 0 && max_active_clusters(split, smem_bytes(Mb)) < p.ntiles) --split;
   }
   p.split = split;
-  if (split == 1) {
-    const int grid = p.ntiles < sms ? p.ntiles : sms;
-    w4a16_gemm_tc_swap_kernel<<<grid, THREADS, smem_bytes(Mb), stream>>>(p, xmap, wmap);
-    return launch_status();
-  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(p.ntiles * split));
+  cfg.gridDim = split == 1 ? dim3((unsigned)(p.ntiles < sms ? p.ntiles : sms)) : dim3((unsigned)(p.ntiles * split));
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = (size_t)smem_bytes(Mb);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)split;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int nattr = 0;
+  // may start behind its predecessor; the kernel waits (griddepcontrol.wait) before it reads the activations
+  static const bool pdl_on = [] { const char* e = getenv("UNIQL_B200_PDL"); return !(e && *e && atoi(e) == 0); }();
+  if (pdl_on) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  if (split > 1) {
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = (unsigned)split;
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = nattr;
   UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a16_gemm_tc_swap_kernel, p, xmap, wmap));
   return launch_status();
 }
