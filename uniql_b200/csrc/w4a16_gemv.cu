@@ -193,10 +193,6 @@ __device__ __forceinline__ void gemv_group_partial(const uint8_t* slot_ptr, floa
       for (int r = 0; r < 4; ++r) accg[t][j][r] -= corr[t][r];
 }
 
-__device__ __forceinline__ void gemv_cp_async16(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
-}
-
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -314,52 +310,50 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
       const int blocks_per_row = (min(gi + p.GCH, g1) - gi) * 8;   // 16-value blocks per row
       const __half* src = p.A + (size_t)gi * 128;
-      // Pass 1: every 16-value block of every row goes from global memory to its place in the staged row as two
-      // asynchronous 16-byte copies -- all rows in flight at once, nothing held in registers (with register staging a
-      // batch of 8 rows took four dependent round trips to L2 per chunk).
-      for (int v0 = 0; v0 < blocks_per_row; v0 += row_threads) {
-        const int v = v0 + row_tid;
-        if (v < blocks_per_row)
-          for (int r = 0; r < m_staged; ++r) {
-            const __half* s16 = src + (size_t)r * p.lda + v * 16;
-            __half* d16 = xs + (size_t)r * p.xs_stride + v * 16;
-            gemv_cp_async16(d16, s16);
-            gemv_cp_async16(d16 + 8, s16 + 8);
-          }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-      // Pass 2: the lane that copied a block puts it into fragment order in place and adds up its offset term.
-      // Every lane takes part in the shuffles: warp-uniform trip counts, out-of-range blocks contribute zero.
+      // every lane takes part in the shuffles below: warp-uniform trip count, out-of-range blocks contribute zero
+      // (rows are loaded two at a time into registers; staging all rows at once through asynchronous copies was
+      // measured and changed nothing at 8 rows while costing 1 % at one row)
       for (int v0 = 0; v0 < blocks_per_row; v0 += row_threads) {
         const int v = v0 + row_tid;
         const bool vin = v < blocks_per_row;
-        for (int r = 0; r < m_staged; ++r) {
-          uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
-          if (vin) {
-            uint4* d = reinterpret_cast<uint4*>(xs + (size_t)r * p.xs_stride + v * 16);
-            lo = d[0];
-            hi = d[1];
-            d[0] = make_uint4(lo.x, hi.x, lo.y, hi.y);
-            d[1] = make_uint4(lo.z, hi.z, lo.w, hi.w);
-          }
-          if (MT != 1) continue;   // two batch tiles: the offset term comes from an MMA instead (gemv_group_partial)
-          // offset term of this 16-value block: 1032 * (sum of k % 16 < 8) + 72 * (sum of k % 16 >= 8)
-          const __half2* hl = reinterpret_cast<const __half2*>(&lo);
-          const __half2* hh = reinterpret_cast<const __half2*>(&hi);
-          float sl = 0.f, sh = 0.f;
+        constexpr int RB = MT == 1 ? 2 : 4;   // rows loaded together (independent requests in flight)
+        for (int r0 = 0; r0 < m_staged; r0 += RB) {
+          uint4 lo[RB], hi[RB];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 fl = __half22float2(hl[e]), fh = __half22float2(hh[e]);
-            sl += fl.x + fl.y;
-            sh += fh.x + fh.y;
+          for (int i = 0; i < RB; ++i) {
+            lo[i] = make_uint4(0, 0, 0, 0);
+            hi[i] = make_uint4(0, 0, 0, 0);
+            if (vin && r0 + i < m_staged) {
+              const __half* s16 = src + (size_t)(r0 + i) * p.lda + v * 16;
+              lo[i] = ld_nc16(s16);
+              hi[i] = ld_nc16(s16 + 8);
+            }
           }
-          float part = 1032.f * sl + 72.f * sh;
-          // the 8 blocks of a group sit in 8 consecutive lanes: fixed-order butterfly sum
-          part += __shfl_xor_sync(0xffffffffu, part, 1);
-          part += __shfl_xor_sync(0xffffffffu, part, 2);
-          part += __shfl_xor_sync(0xffffffffu, part, 4);
-          if (vin && (lane & 7) == 0) ncorr[(v >> 3) * 16 + r] = -part;
+#pragma unroll
+          for (int i = 0; i < RB; ++i) {
+            if (vin && r0 + i < m_staged) {
+              uint4* d = reinterpret_cast<uint4*>(xs + (size_t)(r0 + i) * p.xs_stride + v * 16);
+              d[0] = make_uint4(lo[i].x, hi[i].x, lo[i].y, hi[i].y);
+              d[1] = make_uint4(lo[i].z, hi[i].z, lo[i].w, hi[i].w);
+            }
+            if (MT != 1) continue;   // two batch tiles: the offset term comes from an MMA instead (gemv_group_partial)
+            // offset term of this 16-value block: 1032 * (sum of k % 16 < 8) + 72 * (sum of k % 16 >= 8)
+            const __half2* hl = reinterpret_cast<const __half2*>(&lo[i]);
+            const __half2* hh = reinterpret_cast<const __half2*>(&hi[i]);
+            float sl = 0.f, sh = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 fl = __half22float2(hl[e]), fh = __half22float2(hh[e]);
+              sl += fl.x + fl.y;
+              sh += fh.x + fh.y;
+            }
+            float part = 1032.f * sl + 72.f * sh;
+            // the 8 blocks of a group sit in 8 consecutive lanes: fixed-order butterfly sum
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            part += __shfl_xor_sync(0xffffffffu, part, 4);
+            if (vin && (lane & 7) == 0 && r0 + i < m_staged) ncorr[(v >> 3) * 16 + r0 + i] = -part;
+          }
         }
       }
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
