@@ -71,6 +71,8 @@ struct GemvParams {
   int WN, WK, log_wn, S_split, GCH, R;
   int xs_stride;        // halves per staged activation row (GCH*128 + kXsPad)
   int xs_rows;          // staged rows per warp row: min(M, 8*MT) + 1 (the extra row stays zero)
+  int stage_corr;       // 1: the offset term of every staged group is summed while staging (M <= 4: cheaper than the
+                        // extra MMA per packed row); 0: it comes from that MMA (the sums grow with the row count)
   float* partials;      // [S_split][M][Nv]
   int* counters;        // [gridDim.x], zero on entry, zero on exit
   int* status_word;
@@ -310,6 +312,34 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
       asm volatile("bar.sync %0, %1;" ::"r"(wk + 1), "r"(row_threads));
       const int blocks_per_row = (min(gi + p.GCH, g1) - gi) * 8;   // 16-value blocks per row
       const __half* src = p.A + (size_t)gi * 128;
+      if (!(MT == 1 && p.stage_corr)) {
+        // no offset sums to form: the (row, block) pairs are dealt out flat over the lanes, FL loads in flight each
+        constexpr int FL = MT == 1 ? 4 : 2;
+        const int nitems = blocks_per_row * m_staged;
+        for (int i0 = 0; i0 < nitems; i0 += FL * row_threads) {
+          uint4 lo[FL], hi[FL];
+          int dst[FL];
+#pragma unroll
+          for (int i = 0; i < FL; ++i) {
+            const int item = i0 + i * row_threads + row_tid;
+            dst[i] = -1;
+            if (item < nitems) {
+              const int r = item / blocks_per_row, v = item - r * blocks_per_row;
+              const __half* s16 = src + (size_t)r * p.lda + v * 16;
+              lo[i] = ld_nc16(s16);
+              hi[i] = ld_nc16(s16 + 8);
+              dst[i] = r * p.xs_stride + v * 16;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < FL; ++i)
+            if (dst[i] >= 0) {
+              uint4* d = reinterpret_cast<uint4*>(xs + dst[i]);
+              d[0] = make_uint4(lo[i].x, hi[i].x, lo[i].y, hi[i].y);
+              d[1] = make_uint4(lo[i].z, hi[i].z, lo[i].w, hi[i].w);
+            }
+        }
+      } else
       // every lane takes part in the shuffles below: warp-uniform trip count, out-of-range blocks contribute zero
       // (rows are loaded two at a time into registers; staging all rows at once through asynchronous copies was
       // measured and changed nothing at 8 rows while costing 1 % at one row)
@@ -336,7 +366,7 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
               d[0] = make_uint4(lo[i].x, hi[i].x, lo[i].y, hi[i].y);
               d[1] = make_uint4(lo[i].z, hi[i].z, lo[i].w, hi[i].w);
             }
-            if (MT != 1) continue;   // two batch tiles: the offset term comes from an MMA instead (gemv_group_partial)
+            if (MT != 1) continue;   // (not reached with two batch tiles: see the branch above)
             // offset term of this 16-value block: 1032 * (sum of k % 16 < 8) + 72 * (sum of k % 16 >= 8)
             const __half2* hl = reinterpret_cast<const __half2*>(&lo[i]);
             const __half2* hh = reinterpret_cast<const __half2*>(&hi[i]);
@@ -368,7 +398,7 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
       const uint8_t* xg = xl + chunk_pos * 256;
       // m <= 8: the offset term was computed while staging; m > 8: staging 16 rows is already the longer part of
       // the prologue, so the offset term rides on the tensor pipe there
-      if (MT == 1 && 8 * gi >= w0 && 8 * gi + 8 <= w1)
+      if (MT == 1 && p.stage_corr && 8 * gi >= w0 && 8 * gi + 8 <= w1)
         gemv_group_full<MT>(slot_addr, accg, xg, x_tile_stride, ncorr + chunk_pos * 16 + 2 * c);
       else
         gemv_group_partial<MT>(slot_addr, accg, xg, x_tile_stride, 8 * gi, w0, w1);
@@ -675,12 +705,12 @@ struct GemvPlan {
 // The tuning overrides are read from the environment once per process (a getenv per launch is a scan of the whole
 // environment block).
 struct GemvEnv {
-  int slots, wn, s, r, cluster;
+  int slots, wn, s, r, cluster, stage_corr_rows;
 };
 static const GemvEnv& gemv_env() {
   static const GemvEnv e = {env_int("UNIQL_B200_GEMV_SLOTS", 0), env_int("UNIQL_B200_GEMV_WN", 0),
                             env_int("UNIQL_B200_GEMV_S", 0), env_int("UNIQL_B200_GEMV_R", 0),
-                            env_int("UNIQL_B200_CLUSTER", 1)};
+                            env_int("UNIQL_B200_CLUSTER", 1), env_int("UNIQL_B200_GEMV_STAGE_CORR_ROWS", 4)};
   return e;
 }
 
@@ -819,6 +849,7 @@ int launch_gemv_group(const DecodeArgs& a, const __half* A, int64_t lda, cudaStr
   p.log_wn = plan.WN == 1 ? 0 : plan.WN == 2 ? 1 : plan.WN == 4 ? 2 : 3;
   p.xs_stride = plan.GCH * 128 + kXsPad;
   p.R = plan.R; p.xs_rows = plan.xs_rows; p.status_word = a.status_word;
+  p.stage_corr = a.m <= gemv_env().stage_corr_rows ? 1 : 0;
   p.cluster = plan.cluster; p.ctile_off = plan.ctile_off;
   const size_t part_bytes = (plan.partial_bytes + 255) / 256 * 256;
   if (!a.scratch || (reinterpret_cast<uintptr_t>(a.scratch) & 255u) ||
