@@ -169,12 +169,35 @@ class PushAllReduce:
         from . import ops
         self._status = ops.status_word(self.device)
 
+    @classmethod
+    def single_rank(cls, max_elems: int = 16 * 16384, device=None):
+        """A communicator of world size 1 that needs no process group: the exchanges of the tensor-parallel launches
+        (epoch-tagged words, parities, feature area) then run against this GPU's own block.  For tests and for code
+        that is written against the tensor-parallel calls but runs on one GPU."""
+        import ctypes
+
+        from ._lib import check, lib
+        self = cls.__new__(cls)
+        self.group, self.rank, self.world, self.max_elems = None, 0, 1, max_elems
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._lib = lib()
+        self._comm = ctypes.c_void_p()
+        nbytes = self._lib.uniql_comm_handle_bytes()
+        handle = ctypes.create_string_buffer(nbytes)
+        with torch.cuda.device(self.device):
+            check(self._lib.uniql_comm_create(0, 1, max_elems, ctypes.byref(self._comm), handle), "uniql_comm_create")
+            check(self._lib.uniql_comm_connect(self._comm, handle), "uniql_comm_connect")
+        from . import ops
+        self._status = ops.status_word(self.device)
+        return self
+
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         """In-place sum over the group; returns t."""
         n = t.numel()
         if (t.dtype != torch.float16 or not t.is_contiguous() or n % 8 != 0 or n > self.max_elems
                 or t.data_ptr() % 16 != 0):
-            dist.all_reduce(t, group=self.group)
+            if self.world > 1:
+                dist.all_reduce(t, group=self.group)
             return t
         from ._lib import check
         code = self._lib.uniql_allreduce_push(self._comm, t.data_ptr(), t.data_ptr(), n, self._status.data_ptr(),
