@@ -41,7 +41,7 @@ def test_push_all_reduce_of_one_rank_is_a_copy(comm):
 @pytest.mark.parametrize("m", [1, 3, 8, 16])
 def test_row_parallel_linear_with_the_sum_in_its_epilogue(comm, m):
     """UNIQL_TP_REDUCE: shapes alternate on one communicator (every 64-column block keeps its own epoch); bias and
-    residual are added after the sum; equal bits to the plain launch."""
+    residual are added after the sum; the plain launch's values up to the fp16 rounding of the exchanged partial."""
     from uniql_b200 import ops
     shapes = [(4096, 4096, False), (4096, 14336, True), (1024, 512, False), (4096, 4096, False), (3584, 18944, True)]
     layers = [(quantized_layer(n + k + m, n, k, bias=b), n, k) for n, k, b in shapes]
@@ -53,7 +53,9 @@ def test_row_parallel_linear_with_the_sum_in_its_epilogue(comm, m):
             got = comm.linear_all_reduce(x, p, s, b, n, residual=res)
             (want,) = ops.w4a16_linear_group(x, [(p, s, b, n)], residual=res)
             torch.cuda.synchronize()
-            assert torch.equal(got, want)
+            # the partial crosses the exchange as fp16 before bias and residual are added: one more rounding than the
+            # plain launch, never more than a couple of fp16 steps of the result
+            assert torch.allclose(got.float(), want.float(), rtol=2e-3, atol=2e-3 * float(want.float().abs().max()))
             linear_tolerance_check((got.float() - res.float()).cpu().numpy(),
                                    orc.linear_ref(x.cpu().numpy(), None, None, layer["bias"], n, w_deq=layer["w_deq"]))
     assert ops.read_and_clear_status("cuda") == 0
