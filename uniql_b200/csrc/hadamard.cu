@@ -830,8 +830,8 @@ __global__ void __launch_bounds__(128) hadamard_split_kernel(const T* __restrict
 // The few-row kernel again, for a tensor-parallel layer: the fp16 rows are read from this rank's feature area, where
 // the column shards of all ranks arrive as 8-byte words {2 halves, epoch} (stored there by the epilogue of the
 // column-parallel launch before this one).  A word whose epoch is not this call's yet is read again (bounded; a wait
-// that gives up raises UNIQL_STATUS_WAIT_TIMEOUT).  The epoch of the call is this rank's own counter of block 0, which
-// its own producer launch has already advanced.
+// that gives up raises UNIQL_STATUS_WAIT_TIMEOUT).  The epoch of the call is this rank's gather counter + 1; this
+// kernel advances the counter when it ends, so launches of any width may share a communicator.
 __global__ void __launch_bounds__(128) hadamard_split_feat_kernel(const unsigned char* area, size_t gather_off,
                                                                   size_t epoch_off, int64_t feat_cap, __half* __restrict__ y,
                                                                   int64_t ldy, int P, int B, float scale,
@@ -840,7 +840,8 @@ __global__ void __launch_bounds__(128) hadamard_split_feat_kernel(const unsigned
   pdl_launch_dependents();                       // the linear behind this kernel only prefetches until it waits on us
   const int tid = threadIdx.x, lane = tid & 31;
   const int seg = blockIdx.x, row = blockIdx.y;
-  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(area + epoch_off);
+  // the words of this call carry (this rank's gather counter + 1): the producer launches of all ranks tagged them so
+  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(area + epoch_off) + 1;
   const uint2* xr = reinterpret_cast<const uint2*>(area + gather_off) +
                     ((size_t)(epoch & 1u) * 16 + row) * (size_t)(feat_cap >> 1);
   __half* yr = y + (int64_t)row * ldy + (size_t)seg * P;
@@ -905,6 +906,17 @@ __global__ void __launch_bounds__(128) hadamard_split_feat_kernel(const unsigned
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] *= scale;
   Elem<__half>::store8(yr + tid * 8, v);
+  // The last CTA of the launch to get here (ticket, no waiting) advances the gather counter: every CTA has read it and
+  // every word of this call has been consumed; the next producer launch is ordered behind this kernel.
+  __syncthreads();
+  if (tid == 0) {
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(const_cast<unsigned char*>(area) + epoch_off + 4);
+    const unsigned int total = gridDim.x * gridDim.y;
+    if (atomicAdd(ticket, 1u) == total - 1) {
+      *ticket = 0;
+      *reinterpret_cast<volatile uint32_t*>(const_cast<unsigned char*>(area) + epoch_off) = epoch;
+    }
+  }
 }
 
 // Segment layout of the few-row kernels: dim = B segments of Ps points.  Returns false if the size does not fit them.

@@ -23,8 +23,8 @@ struct CommView {
   size_t reduce_epoch_off;    // per-block epoch counters (u32) of the reduce area
   int64_t block_cap;          // 64-column blocks a reduce slot has room for
   size_t gather_off;          // byte offset of the feature area: [2 parities][16 rows][feat_cap / 2] words
-  size_t gather_epoch_off;    // per-block epoch counters (u32) of this rank's own column shard; counter 0 also tells
-                              // the consumer which epoch the words of the current call carry
+  size_t gather_epoch_off;    // u32 gather counter of this rank (words of a call carry counter + 1; the consumer of the
+                              // gathered row advances it) followed by the consumer's u32 ticket
   int64_t feat_cap;           // features (columns) a row of the feature area has room for
   int64_t col_offset;         // gather_out: global index of this launch's column 0
 };

@@ -276,8 +276,10 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
       const size_t unit = (size_t)(p.swiglu ? vb >> 1 : vb);
       if (p.cv.reduce)
         s_repoch[tid] = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_epoch_off + 4 * unit) + 1;
+      // feature gather: one epoch per launch (this rank's gather counter + 1); the counter itself is advanced by the
+      // consumer of the gathered row (hadamard_split_feat_kernel), which runs between two producer launches
       if (p.cv.gather_out)
-        s_gepoch[tid] = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off + 4 * unit) + 1;
+        s_gepoch[tid] = *reinterpret_cast<const volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off) + 1;
     }
   }
 
@@ -598,14 +600,11 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
   };
   // once every item of the CTA's blocks is finished, their epoch counters advance (one thread per block)
   auto advance_epochs = [&]() {
-    if ((p.cv.reduce || p.cv.gather_out) && tid < p.WN) {
+    if (p.cv.reduce && tid < p.WN) {
       const int vb = blockIdx.x * p.WN + tid;
       if (vb < p.nblk) {
         const size_t unit = (size_t)(p.swiglu ? vb >> 1 : vb);
-        if (p.cv.reduce)
-          *reinterpret_cast<volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_epoch_off + 4 * unit) = s_repoch[tid];
-        if (p.cv.gather_out)
-          *reinterpret_cast<volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.gather_epoch_off + 4 * unit) = s_gepoch[tid];
+        *reinterpret_cast<volatile uint32_t*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_epoch_off + 4 * unit) = s_repoch[tid];
       }
     }
   };
