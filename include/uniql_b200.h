@@ -228,8 +228,11 @@ int uniql_w4a16_linear_allreduce(void* comm, const void* A, int64_t lda, const v
                                  void* stream);
 
 /*
- * Grouped decode launch (m <= 16): up to UNIQL_MAX_PROJ projections that read the same activations run as ONE kernel,
- * with the elementwise work the reference's blocks do around them folded into its epilogue / prologue.  Replaces
+ * Grouped launch: up to UNIQL_MAX_PROJ projections that read the same activations run as ONE kernel.  For m <= 16 that
+ * is the decode kernel with every option below; for 17 <= m <= 128 it is the operand-swapped tensor-core kernel with
+ * plain outputs only (epilogue NONE, no residual, no hadamard_dim; every n >= 128) -- q/k/v or gate and up of a block
+ * at small batches cost one launch instead of two or three.  Larger m returns UNIQL_ESHAPE.  At decode sizes the
+ * elementwise work the reference's blocks do around the projections is folded into the launch.  It replaces
  *   - gate_proj, up_proj and act_fn(gate) * up as three launches (modeling/llama/llama_qblocks.py:48-51):
  *     two projections + UNIQL_EPILOGUE_SWIGLU -> proj[0].D = silu(x W_gate + b_gate) * (x W_up + b_up), with the same
  *     fp16 roundings as the separate modules (proj[1].D is not written); both projections must have the same n, n_out;

@@ -166,7 +166,36 @@ def test_group_argument_errors():
         ops.w4a16_linear_group(x, [_dev(a), _dev(b)], epilogue="swiglu")
     with pytest.raises(UniqlError):                      # the residual belongs to a single output
         ops.w4a16_linear_group(x, [_dev(a), _dev(b)], residual=torch.zeros(2, 128, dtype=torch.float16, device="cuda"))
-    with pytest.raises(UniqlError):                      # decode-only entry point
-        ops.w4a16_linear_group(make_acts(1, 17, 256).cuda(), [_dev(a)])
+    with pytest.raises(UniqlError):                      # above 16 rows: plain outputs only ...
+        ops.w4a16_linear_group(make_acts(1, 17, 256).cuda(), [_dev(a)], residual=torch.zeros(17, 128, dtype=torch.float16, device="cuda"))
+    with pytest.raises(UniqlError):                      # ... and at most 128 rows
+        ops.w4a16_linear_group(make_acts(1, 129, 256).cuda(), [_dev(a)])
     with pytest.raises(RuntimeError):
         ops.w4a16_linear_group(x, [_dev(a)], epilogue="gelu")
+
+
+@pytest.mark.parametrize("shapes,k,m", [([(4096, False), (1024, False), (1024, False)], 4096, 64),
+                                        ([(3584, True), (512, True), (512, True)], 3584, 17),
+                                        ([(14336, False), (14336, False)], 4096, 64),
+                                        ([(18944, False), (18944, False)], 3584, 128),
+                                        ([(256, True), (192, False)], 256, 33),
+                                        ([(128, False), (128, True), (320, False), (192, False)], 384, 100)])
+def test_mid_batch_group_runs_on_the_tensor_core_kernel(shapes, k, m):
+    """17..128 rows: the projections of a grouped call share one launch of the operand-swapped tcgen05 kernel (one tile
+    list over all of them, cluster split along k when there are few tiles); every output agrees with the single launch."""
+    from uniql_b200 import ops
+    layers = [quantized_layer(19 * i + n + k, n, k, bias=b) for i, (n, b) in enumerate(shapes)]
+    x = make_acts(m + 5, m, k)
+    outs = ops.w4a16_linear_group(x.cuda(), [_dev(l) for l in layers])
+    torch.cuda.synchronize()
+    assert len(outs) == len(layers)
+    for layer, y in zip(layers, outs):
+        assert y.shape == (m, layer["n"])
+        single = ops.w4a16_linear(x.cuda(), *_dev(layer)[:3], layer["n"])
+        # same kernel; the split over k (and with it the order of the fp32 sums) depends on the launch's tile count
+        linear_tolerance_check(y.cpu().numpy(), single.float().cpu().numpy())
+        assert float((y.float() - single.float()).abs().max()) <= 2e-3 * float(single.float().abs().max()) + 1e-3
+    if layers[0]["n"] <= 4096:
+        for layer, y in zip(layers, outs):
+            linear_tolerance_check(y.cpu().numpy(), _ref(layer, x.numpy()))
+    assert ops.read_and_clear_status("cuda") == 0

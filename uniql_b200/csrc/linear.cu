@@ -62,7 +62,26 @@ static int group_launch(const CommView* cv, int64_t k_offset, const void* A, int
                         int64_t hadamard_dim, const uniql_prefetch* next, int nnext, void* scratch,
                         size_t scratch_bytes, int* status_word, cudaStream_t stream) {
   if (!proj || nproj < 1 || nproj > UNIQL_MAX_PROJ || m < 0 || k <= 0) return UNIQL_EINVAL;
-  if (m > 16 || k % 128 != 0) return UNIQL_ESHAPE;
+  if (k % 128 != 0) return UNIQL_ESHAPE;
+  if (m > 16) {
+    // 17..128 rows: the projections share one launch of the operand-swapped tensor-core kernel (plain outputs only:
+    // the elementwise epilogues, the transform and the tensor-parallel exchanges belong to the decode kernel)
+    if (m > 128 || cv || epilogue != UNIQL_EPILOGUE_NONE || residual || hadamard_dim) return UNIQL_ESHAPE;
+    if (lda < k || lda % 8 != 0 || !A || !aligned16(A)) return UNIQL_EINVAL;
+    LinearArgs la[UNIQL_MAX_PROJ];
+    void* ds[UNIQL_MAX_PROJ];
+    int64_t widths[UNIQL_MAX_PROJ];
+    for (int i = 0; i < nproj; ++i) {
+      const int st = check_proj(proj[i], k);
+      if (st != UNIQL_OK) return st;
+      la[i].B = proj[i].B; la[i].s = proj[i].s; la[i].bias = proj[i].bias; la[i].ldd = proj[i].ldd;
+      la[i].n = proj[i].n; la[i].n_out = proj[i].n_out; la[i].k = k; la[i].status_word = status_word;
+      ds[i] = proj[i].D;
+      widths[i] = proj[i].n;
+    }
+    if (!gemm_tc_group_supported(m, k, widths, nproj)) return UNIQL_ESHAPE;
+    return launch_gemm_tc_group(la, ds, nproj, (const __half*)A, lda, m, stream);
+  }
   if (epilogue != UNIQL_EPILOGUE_NONE && epilogue != UNIQL_EPILOGUE_SWIGLU) return UNIQL_EINVAL;
   if (epilogue == UNIQL_EPILOGUE_SWIGLU && (nproj != 2 || proj[0].n != proj[1].n || proj[0].n_out != proj[1].n_out))
     return UNIQL_EINVAL;

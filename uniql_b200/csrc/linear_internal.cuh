@@ -80,6 +80,11 @@ struct LinearArgs {
 bool gemm_tc_supported(int64_t m, int64_t n, int64_t k);
 size_t gemm_tc_scratch_bytes(int64_t m, int64_t n, int64_t k);
 int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m, cudaStream_t stream);
+// 16 < m <= 128: up to kMaxProj projections that read the same activations (same k) as one launch of the
+// operand-swapped kernel; Ds[i] receives projection i (leading dimension projs[i].ldd).
+bool gemm_tc_group_supported(int64_t m, int64_t k, const int64_t* n, int nproj);
+int launch_gemm_tc_group(const LinearArgs* projs, void* const* Ds, int nproj, const __half* A, int64_t lda, int64_t m,
+                         cudaStream_t stream);
 
 // Hadamard transform of fp16 rows (used by the fused linear); signals dependents early when pdl is set.
 int launch_hadamard(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int64_t dim, float scale,

@@ -137,7 +137,8 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& weight, const at::Tenso
 
 // One decode launch for projections that read the same activations (uniql_w4a16_linear_group): q/k/v, gate+up with
 // act_fn(gate) * up (modeling/llama/llama_qblocks.py:48-51, :104-106), or one projection with the block's residual.
-// Returns one tensor per projection (one tensor for the SwiGLU epilogue).  Up to 16 rows.
+// Returns one tensor per projection (one tensor for the SwiGLU epilogue).  Up to 16 rows; 17..128 rows for plain
+// outputs (one launch of the operand-swapped tensor-core kernel over all projections).
 std::vector<at::Tensor> linear_group(const at::Tensor& x, const std::vector<at::Tensor>& weights,
                                      const std::vector<at::Tensor>& scales,
                                      const std::vector<std::optional<at::Tensor>>& biases,
@@ -157,7 +158,9 @@ std::vector<at::Tensor> linear_group(const at::Tensor& x, const std::vector<at::
   }
   const at::Tensor x2 = rows_of(x, pad_in, k);
   const int64_t m = x2.size(0);
-  TORCH_CHECK(m >= 1 && m <= 16, "grouped launches take 1 to 16 rows");
+  TORCH_CHECK(m >= 1 && m <= 128, "grouped launches take 1 to 128 rows");
+  TORCH_CHECK(m <= 16 || (epilogue == UNIQL_EPILOGUE_NONE && !hadamard && !(residual.has_value() && residual->defined())),
+              "above 16 rows a grouped launch has plain outputs only");
   const c10::cuda::CUDAGuard guard(x2.device());
   const int dev = x2.device().index();
   const int nout = epilogue == UNIQL_EPILOGUE_SWIGLU ? 1 : np;

@@ -34,6 +34,7 @@
 
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
 namespace uniql {
 
@@ -538,16 +539,36 @@ inline int smem_bytes(int Mb) {
 }
 }  // namespace tcs
 
-struct TcSwapParams {
+// Up to kMaxProj projections that read the same activations share one launch: their 128-column tiles form one list
+// (q/k/v, or gate and up, of a decoder block at batches of 17..128 rows).
+struct TcSwapProj {
   const uint4* S;
   const __half* bias;
   __half* D;
   int64_t ldd;
-  int M, Mb, N, n_out, K;
+  int N, n_out;
+};
+struct TcSwapParams {
+  TcSwapProj proj[kMaxProj];
+  int tile_start[kMaxProj + 1];                 // first tile of each projection in the launch's tile list
+  int nproj;
+  int M, Mb, K;
   int ntiles;
   int split;                                    // CTAs of a cluster that share one column tile, each a slice of k
   int* status_word;
 };
+struct TcSwapMaps {
+  CUtensorMap w[kMaxProj];                      // packed weights of each projection
+};
+
+// tile of the launch -> (projection, tile inside it)
+__device__ __forceinline__ void tcs_proj_of(const TcSwapParams& p, int nt, int& pi, int& lt) {
+  pi = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxProj; ++i)
+    if (i < p.nproj && nt >= p.tile_start[i]) pi = i;
+  lt = nt - p.tile_start[pi];
+}
 
 __device__ __forceinline__ void tcs_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -590,8 +611,8 @@ __device__ __forceinline__ uint32_t tcs_issue_stage(uint32_t tmem_d, uint32_t tm
 }
 
 __global__ void __launch_bounds__(tcs::THREADS, 1)
-w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensorMap xmap,
-                          const __grid_constant__ CUtensorMap wmap) {
+w4a16_gemm_tc_swap_kernel(const __grid_constant__ TcSwapParams p, const __grid_constant__ CUtensorMap xmap,
+                          const __grid_constant__ TcSwapMaps wmaps) {
   using namespace tcs;
   extern __shared__ uint8_t smem_unaligned[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
@@ -623,7 +644,7 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
   pdl_launch_dependents();                       // the next kernel in the stream may start its own set-up and weights
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&xmap) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+    for (int i = 0; i < p.nproj; ++i) asm volatile("prefetch.tensormap [%0];" ::"l"(&wmaps.w[i]) : "memory");
     for (int s = 0; s < STAGES; ++s) {
       tc_mbar_init(bar_full + 8 * s, 1 + DEQ_WARPS);
       tc_mbar_init(bar_empty + 8 * s, 1);
@@ -656,11 +677,13 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
     if (lane == 0) {
       int it = 0;
       for (int nt = tile0; nt < p.ntiles; nt += tile_step) {
+        int pi, lt;
+        tcs_proj_of(p, nt, pi, lt);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int sp = it % P_STAGES;
           if (!timed_out && !tc_mbar_wait(bar_empty_p + 8 * sp, ((it / P_STAGES) & 1) ^ 1)) timed_out = true;
           tc_mbar_expect_tx(bar_full_p + 8 * sp, P_BYTES);
-          tc_tma_2d(sbase + OFF_P + sp * P_BYTES, &wmap, nt * (2 * BNW), (kb0 + kb) * (BK / 16), bar_full_p + 8 * sp);
+          tc_tma_2d(sbase + OFF_P + sp * P_BYTES, &wmaps.w[pi], lt * (2 * BNW), (kb0 + kb) * (BK / 16), bar_full_p + 8 * sp);
         }
       }
     }
@@ -732,17 +755,20 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
       const int buf = it_tile & 1;
       if (!timed_out && !tc_mbar_wait_relaxed(bar_tmem_full + 8 * buf, (it_tile >> 1) & 1)) timed_out = true;
       tc_fence_after();
-      const int n = nt * BNW + q * 32 + lane;
+      int pi, lt;
+      tcs_proj_of(p, nt, pi, lt);
+      const TcSwapProj& pr = p.proj[pi];
+      const int n = lt * BNW + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 128;
-      const float bv = (p.bias && n < p.n_out) ? __half2float(p.bias[n]) : 0.f;
+      const float bv = (pr.bias && n < pr.n_out) ? __half2float(pr.bias[n]) : 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < p.Mb; c0 += 32) {
         uint32_t r[32];
         tc_ld32(taddr + c0, r);
-        if (n < p.n_out) {
+        if (n < pr.n_out) {
 #pragma unroll
           for (int e = 0; e < 32; ++e)
-            if (c0 + e < p.M) p.D[(size_t)(c0 + e) * p.ldd + n] = __float2half_rn(__uint_as_float(r[e]) + bv);
+            if (c0 + e < p.M) pr.D[(size_t)(c0 + e) * pr.ldd + n] = __float2half_rn(__uint_as_float(r[e]) + bv);
         }
       }
       tc_fence_before();
@@ -760,33 +786,32 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
     const int q = warp & 3;
     const int blk_local = q >> 1;
     const int g = lane >> 2;
-    const int nblk = p.N >> 6;
-    const uint32_t srow_u4 = (uint32_t)(p.N >> 3);
-    const uint4* sbase_g = p.S + g;
+    // scales of 64-column block `blk_local` of tile `nt` and k-block `kblk` (zero for a block past the projection's width)
+    auto load_scales = [&](int nt, int kblk, bool& valid) {
+      int pi, lt;
+      tcs_proj_of(p, nt, pi, lt);
+      const TcSwapProj& pr = p.proj[pi];
+      const int blk = lt * 2 + blk_local;
+      valid = blk < (pr.N >> 6);
+      if (!valid) return make_uint2(0, 0);
+      return __ldg(reinterpret_cast<const uint2*>(pr.S + g + (size_t)blk * 8 + (size_t)kblk * (size_t)(pr.N >> 3)) + (q & 1));
+    };
     // position of the k-block this warp converts next, and of the one after it (whose scales are requested early)
     int ti = 0, kb = set;
     while (kb >= KB && ti < my_tiles) { kb -= KB; ++ti; }
     int ti2 = ti, kb2 = kb + NSETS;
     while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
     uint2 snext = make_uint2(0, 0);
-    if (set < total_it) {
-      const int blk = (tile0 + ti * tile_step) * 2 + blk_local;
-      if (blk < nblk)
-        snext = __ldg(reinterpret_cast<const uint2*>(sbase_g + (size_t)blk * 8 + (size_t)(kb0 + kb) * srow_u4) + (q & 1));
-    }
+    bool vnext = false;
+    if (set < total_it) snext = load_scales(tile0 + ti * tile_step, kb0 + kb, vnext);
     for (int it = set; it < total_it; it += NSETS) {
-      const int blk = (tile0 + ti * tile_step) * 2 + blk_local;
-      const bool valid = blk < nblk;
+      const bool valid = vnext;
       uint32_t sdup[4];
       sdup[0] = __byte_perm(snext.x, 0, 0x1010);   // word j0:   columns 16 j0 + g
       sdup[1] = __byte_perm(snext.x, 0, 0x3232);   //            columns 16 j0 + g + 8
       sdup[2] = __byte_perm(snext.y, 0, 0x1010);   // word j0+1
       sdup[3] = __byte_perm(snext.y, 0, 0x3232);
-      if (it + NSETS < total_it) {
-        const int blk2 = (tile0 + ti2 * tile_step) * 2 + blk_local;
-        if (blk2 < nblk)
-          snext = __ldg(reinterpret_cast<const uint2*>(sbase_g + (size_t)blk2 * 8 + (size_t)(kb0 + kb2) * srow_u4) + (q & 1));
-      }
+      if (it + NSETS < total_it) snext = load_scales(tile0 + ti2 * tile_step, kb0 + kb2, vnext);
       ti = ti2; kb = kb2;
       kb2 += NSETS;
       while (kb2 >= KB && ti2 < my_tiles) { kb2 -= KB; ++ti2; }
@@ -853,10 +878,13 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
     tcs_cluster_sync();                         // every rank's partial is in its shared memory
     if (rank == 0 && warp >= 3 && warp < FIRST_DEQ_WARP && tile0 < p.ntiles) {
       const int q = warp & 3;
-      const int n = tile0 * BNW + q * 32 + lane;
+      int pi, lt;
+      tcs_proj_of(p, tile0, pi, lt);
+      const TcSwapProj& pr = p.proj[pi];
+      const int n = lt * BNW + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
       const uint32_t part = sbase + OFF_X + (uint32_t)(q * 32 + lane) * 4;
-      const float bv = (p.bias && n < p.n_out) ? __half2float(p.bias[n]) : 0.f;
+      const float bv = (pr.bias && n < pr.n_out) ? __half2float(pr.bias[n]) : 0.f;
       tc_fence_after();
 #pragma unroll 1
       for (int c0 = 0; c0 < p.Mb; c0 += 32) {
@@ -876,10 +904,10 @@ w4a16_gemm_tc_swap_kernel(const TcSwapParams p, const __grid_constant__ CUtensor
 #pragma unroll
           for (int e = 0; e < 32; ++e) acc[e] += v[e];
         }
-        if (n < p.n_out) {
+        if (n < pr.n_out) {
 #pragma unroll
           for (int e = 0; e < 32; ++e)
-            if (c0 + e < p.M) p.D[(size_t)(c0 + e) * p.ldd + n] = __float2half_rn(acc[e] + bv);
+            if (c0 + e < p.M) pr.D[(size_t)(c0 + e) * pr.ldd + n] = __float2half_rn(acc[e] + bv);
         }
       }
     }
@@ -932,13 +960,17 @@ static int max_active_clusters(int split, int smem) {
   return n;
 }
 
-static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m,
-                               cudaStream_t stream) {
+// Projections of one launch (same activations, same k); D[i] receives projection i.
+static int launch_gemm_tc_swap(const LinearArgs* projs, void* const* Ds, int nproj, const __half* A, int64_t lda,
+                               int64_t m, cudaStream_t stream) {
   using namespace tcs;
+  if (nproj < 1 || nproj > kMaxProj) return UNIQL_EINVAL;
+  const LinearArgs& a = projs[0];
   EncodeTiledFn enc = tc_encode_fn();
   if (!enc) return cuda_fail(cudaErrorNotSupported);
   const int Mb = (int)((m + 15) / 16 * 16);
-  CUtensorMap xmap, wmap;
+  CUtensorMap xmap;
+  TcSwapMaps wmaps;
   {
     cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)m};
     cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
@@ -949,20 +981,30 @@ static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cuda_fail(cudaErrorInvalidValue);
   }
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)(2 * a.n), (cuuint64_t)(a.k / 16)};
-    cuuint64_t strides[1] = {(cuuint64_t)(2 * a.n) * 4};
+  TcSwapParams p;
+  memset(&p, 0, sizeof(p));
+  int tiles = 0;
+  for (int i = 0; i < nproj; ++i) {
+    const LinearArgs& q = projs[i];
+    if (q.k != a.k || q.n < 128 || q.n % 64) return UNIQL_ESHAPE;
+    cuuint64_t dims[2] = {(cuuint64_t)(2 * q.n), (cuuint64_t)(q.k / 16)};
+    cuuint64_t strides[1] = {(cuuint64_t)(2 * q.n) * 4};
     cuuint32_t box[2] = {256, (cuuint32_t)(BK / 16)};
     cuuint32_t estr[2] = {1, 1};
-    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(a.B), dims, strides, box, estr,
+    if (enc(&wmaps.w[i], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(q.B), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cuda_fail(cudaErrorInvalidValue);
+    p.proj[i].S = (const uint4*)q.s; p.proj[i].bias = (const __half*)q.bias; p.proj[i].D = (__half*)Ds[i];
+    p.proj[i].ldd = q.ldd; p.proj[i].N = (int)q.n; p.proj[i].n_out = (int)q.n_out;
+    p.tile_start[i] = tiles;
+    tiles += (int)((q.n + BNW - 1) / BNW);
   }
-  TcSwapParams p;
-  p.S = (const uint4*)a.s; p.bias = (const __half*)a.bias; p.D = D; p.ldd = a.ldd;
-  p.M = (int)m; p.Mb = Mb; p.N = (int)a.n; p.n_out = (int)a.n_out; p.K = (int)a.k;
-  p.ntiles = (int)((a.n + BNW - 1) / BNW);
+  for (int i = nproj; i <= kMaxProj; ++i) p.tile_start[i] = tiles;
+  for (int i = nproj; i < kMaxProj; ++i) { wmaps.w[i] = wmaps.w[0]; p.proj[i] = p.proj[0]; }
+  p.nproj = nproj;
+  p.M = (int)m; p.Mb = Mb; p.K = (int)a.k;
+  p.ntiles = tiles;
   p.status_word = a.status_word;
   {
     // function attributes are per device
@@ -1020,14 +1062,30 @@ static int launch_gemm_tc_swap(const LinearArgs& a, const __half* A, int64_t lda
   }
   cfg.attrs = attr;
   cfg.numAttrs = nattr;
-  UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a16_gemm_tc_swap_kernel, p, xmap, wmap));
+  UNIQL_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a16_gemm_tc_swap_kernel, p, xmap, wmaps));
   return launch_status();
+}
+
+bool gemm_tc_group_supported(int64_t m, int64_t k, const int64_t* n, int nproj) {
+  static const int swap_on = [] { const char* e = getenv("UNIQL_B200_TC_SWAP"); return (e && *e) ? atoi(e) : 1; }();
+  if (!swap_on || m <= 16 || m > 128 || k % 128 || nproj < 1 || nproj > kMaxProj) return false;
+  for (int i = 0; i < nproj; ++i)
+    if (n[i] < 128 || n[i] % 64) return false;
+  return true;
+}
+
+int launch_gemm_tc_group(const LinearArgs* projs, void* const* Ds, int nproj, const __half* A, int64_t lda, int64_t m,
+                         cudaStream_t stream) {
+  return launch_gemm_tc_swap(projs, Ds, nproj, A, lda, m, stream);
 }
 
 int launch_gemm_tc(const LinearArgs& a, const __half* A, int64_t lda, __half* D, int64_t m, cudaStream_t stream) {
   using namespace tc;
   static const int swap_on = [] { const char* e = getenv("UNIQL_B200_TC_SWAP"); return (e && *e) ? atoi(e) : 1; }();
-  if (swap_on && m <= 128) return launch_gemm_tc_swap(a, A, lda, D, m, stream);
+  if (swap_on && m <= 128) {
+    void* d1[1] = {D};
+    return launch_gemm_tc_swap(&a, d1, 1, A, lda, m, stream);
+  }
   EncodeTiledFn enc = tc_encode_fn();
   if (!enc) return cuda_fail(cudaErrorNotSupported);
   CUtensorMap amap;

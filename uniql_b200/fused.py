@@ -3,9 +3,9 @@
 The reference's blocks call their quantized linears one by one and glue them with elementwise kernels:
 `down_proj(act_fn(gate_proj(x)) * up_proj(x))` (modeling/llama/llama_qblocks.py:48-51), three q/k/v linears
 (:104-106), `residual + o_proj(...)`.  At decode sizes every one of those launches costs more than the bytes it
-moves, so for up to 16 rows the functions below issue one grouped kernel (uniql_w4a16_linear_group) per step;
-larger batches run the same modules one after the other on the tensor-core kernels, with the elementwise maths
-in PyTorch exactly as the reference does it.  All take and return the tensors the reference's code would.
+moves, so for up to 16 rows the functions below issue one grouped kernel (uniql_w4a16_linear_group) per step; up
+to 128 rows the projections still share one launch (plain outputs, the elementwise maths in PyTorch); larger batches
+run the same modules one after the other on the tensor-core kernels, exactly as the reference does it.  All take and return the tensors the reference's code would.
 """
 from __future__ import annotations
 
@@ -14,7 +14,8 @@ import torch.nn.functional as F
 
 from . import ops
 
-DECODE_ROWS = 16
+DECODE_ROWS = 16         # the decode kernel: SwiGLU, residual and Hadamard inside the launch
+GROUP_ROWS = 128         # plain outputs of several projections in one launch (tensor-core kernel above 16 rows)
 
 
 def _layer(mod):
@@ -35,13 +36,18 @@ def _flat(x, mod):
 def gate_up_swiglu(gate_proj, up_proj, x):
     """silu(gate_proj(x)) * up_proj(x) for two W4A16B16O16Linear modules of the same shape."""
     ext = ops.torch_ext()
-    if ext is not None and _rows(x) <= DECODE_ROWS:
-        return ext.linear_group(x, [gate_proj.weight, up_proj.weight], [gate_proj.scale, up_proj.scale],
-                                [gate_proj.bias, up_proj.bias], [gate_proj.out_features, up_proj.out_features], 1, None,
-                                gate_proj.pad_in, False)[0]
+    if ext is not None and _rows(x) <= GROUP_ROWS:
+        fused_act = _rows(x) <= DECODE_ROWS
+        out = ext.linear_group(x, [gate_proj.weight, up_proj.weight], [gate_proj.scale, up_proj.scale],
+                               [gate_proj.bias, up_proj.bias], [gate_proj.out_features, up_proj.out_features],
+                               1 if fused_act else 0, None, gate_proj.pad_in, False)
+        return out[0] if fused_act else F.silu(out[0]) * out[1]
     x2 = _flat(x, gate_proj)
     if x2.shape[0] <= DECODE_ROWS:
         (h,) = ops.w4a16_linear_group(x2, [_layer(gate_proj), _layer(up_proj)], epilogue="swiglu")
+    elif x2.shape[0] <= GROUP_ROWS:
+        g, u = ops.w4a16_linear_group(x2, [_layer(gate_proj), _layer(up_proj)])
+        h = F.silu(g) * u
     else:
         h = F.silu(gate_proj(x2)) * up_proj(x2)
     return h.view(*x.shape[:-1], gate_proj.out_features)
@@ -51,11 +57,11 @@ def qkv_proj(q_proj, k_proj, v_proj, x):
     """(q_proj(x), k_proj(x), v_proj(x)) for three W4A16B16O16Linear modules with the same in_features."""
     mods = (q_proj, k_proj, v_proj)
     ext = ops.torch_ext()
-    if ext is not None and _rows(x) <= DECODE_ROWS:
+    if ext is not None and _rows(x) <= GROUP_ROWS:
         return tuple(ext.linear_group(x, [m.weight for m in mods], [m.scale for m in mods], [m.bias for m in mods],
                                       [m.out_features for m in mods], 0, None, q_proj.pad_in, False))
     x2 = _flat(x, q_proj)
-    if x2.shape[0] <= DECODE_ROWS:
+    if x2.shape[0] <= GROUP_ROWS:
         outs = ops.w4a16_linear_group(x2, [_layer(m) for m in mods])
     else:
         outs = [m(x2) for m in mods]

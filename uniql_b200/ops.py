@@ -146,7 +146,8 @@ _group_need_cache: dict = {}
 def w4a16_linear_group(x: torch.Tensor | None, layers, epilogue: str = "none", residual: torch.Tensor | None = None,
                        hadamard_dim: int = 0, outs=None, comm=None, tp_flags: int = 0, col_offset: int = 0,
                        k_offset: int = 0, m: int | None = None, prefetch=None):
-    """One decode launch (m <= 16) for up to four projections that read the same activations.
+    """One launch for up to four projections that read the same activations: the decode kernel for m <= 16 (all
+    options below), the operand-swapped tensor-core kernel for 17 <= m <= 128 (plain outputs only).
 
     layers: sequence of (weight int32 [k/16, 2n], scale fp16 [k/128, n], bias fp16 or None, n_out).
     epilogue "swiglu": two layers (gate, up) -> one output silu(gate) * up.  residual: fp16 [m, n_out] added to the
