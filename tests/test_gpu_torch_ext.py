@@ -110,11 +110,23 @@ def test_grouped_launches_embedding_and_hadamard_equal_ctypes_path():
         outs = fz.qkv_proj(q, k_, v, x.reshape(1, m, 1024))
         outs0 = ops.w4a16_linear_group(x, [(t.weight, t.scale, t.bias, t.out_features) for t in (q, k_, v)])
         assert all(o.shape == (1, m, o0.shape[1]) and torch.equal(o[0], o0) for o, o0 in zip(outs, outs0))
-    # larger batches leave the grouped kernel and give the same values as the separate modules
+    # 17..128 rows: gate and up share one tensor-core launch, SiLU and the product stay in PyTorch; beyond that the
+    # separate modules run -- the same values either way (the split over k may order the fp32 sums differently)
+    for rows in (40, 128, 200):
+        xb = make_acts(9, rows, 1024).cuda()
+        got = fz.gate_up_swiglu(gate, up, xb).float()
+        want = (torch.nn.functional.silu(gate(xb)) * up(xb)).float()
+        assert got.shape == (rows, 3584)
+        assert float((got - want).abs().max()) <= 4e-3 * float(want.abs().max()) + 1e-3
+        qo = fz.qkv_proj(q, k_, v, xb)
+        for o, mod in zip(qo, (q, k_, v)):
+            w = mod(xb).float()
+            assert o.shape == w.shape and float((o.float() - w).abs().max()) <= 2e-3 * float(w.abs().max()) + 1e-3
     xb = make_acts(9, 40, 1024).cuda()
-    assert torch.equal(fz.gate_up_swiglu(gate, up, xb), torch.nn.functional.silu(gate(xb)) * up(xb))
     with pytest.raises(RuntimeError):
-        ext.linear_group(xb, [gate.weight], [gate.scale], [None], [3584], 0, None, 0, False)     # more than 16 rows
+        ext.linear_group(make_acts(9, 130, 1024).cuda(), [gate.weight], [gate.scale], [None], [3584], 0, None, 0, False)  # > 128 rows
+    with pytest.raises(RuntimeError):
+        ext.linear_group(xb, [gate.weight, up.weight], [gate.scale, up.scale], [None, None], [3584, 3584], 1, None, 0, False)  # SwiGLU above 16 rows
     with pytest.raises(RuntimeError):
         ext.linear_group(xb[:2], [gate.weight, q.weight], [gate.scale, q.scale], [None, None], [3584, 1024], 1, None, 0, False)
     # embedding and Hadamard
