@@ -732,22 +732,21 @@ w4a16_gemm_tc_swap_kernel(const __grid_constant__ TcSwapParams p, const __grid_c
     const int q = warp & 3;
     int it_tile = 0;
     if (p.split > 1) {
-      // one tile per cluster: ranks other than 0 park their partial accumulator in shared memory (the activation
-      // ring, idle once the last MMA has completed) as part[batch row][column]; rank 0 sums after the cluster barrier
+      // one tile per cluster: every rank parks its partial accumulator in shared memory (the activation ring, idle
+      // once the last MMA has completed) as part[batch row][column]; after the cluster barrier every rank sums a slice
+      // of the batch rows over all ranks
       if (tile0 < p.ntiles) {
         if (!timed_out && !tc_mbar_wait_relaxed(bar_tmem_full, 0)) timed_out = true;
         tc_fence_after();
-        if (rank != 0) {
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-          const uint32_t part = sbase + OFF_X + (uint32_t)(q * 32 + lane) * 4;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t part = sbase + OFF_X + (uint32_t)(q * 32 + lane) * 4;
 #pragma unroll 1
-          for (int c0 = 0; c0 < p.Mb; c0 += 32) {
-            uint32_t r[32];
-            tc_ld32(taddr + c0, r);
+        for (int c0 = 0; c0 < p.Mb; c0 += 32) {
+          uint32_t r[32];
+          tc_ld32(taddr + c0, r);
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (c0 + e < p.M) tc_sts32(part + (uint32_t)(c0 + e) * (BNW * 4), r[e]);
-          }
+          for (int e = 0; e < 32; ++e)
+            if (c0 + e < p.M) tc_sts32(part + (uint32_t)(c0 + e) * (BNW * 4), r[e]);
         }
       }
     } else
@@ -876,38 +875,50 @@ w4a16_gemm_tc_swap_kernel(const __grid_constant__ TcSwapParams p, const __grid_c
   if (p.split > 1) {
     __syncwarp();
     tcs_cluster_sync();                         // every rank's partial is in its shared memory
-    if (rank == 0 && warp >= 3 && warp < FIRST_DEQ_WARP && tile0 < p.ntiles) {
-      const int q = warp & 3;
+    if (warp >= 3 && tile0 < p.ntiles) {
+      // Rank r finishes batch rows [Mb r / split, Mb (r+1) / split).  All twenty warps past the producers take part (the
+      // dequantise warps are idle by now): four warps cover the 128 columns, five such groups interleave the rows, so a
+      // thread has at most four rows x `split` partials to fetch -- all of them independent loads from the ranks'
+      // shared memory (distributed shared memory), in flight together, added in rank order so that the sum does not
+      // depend on timing.  (With rank 0's four warps alone walking the peers one after the other this step took 6 us
+      // at split 4 and 14 us at split 8: every batch of remote loads is a ~1 us round trip.)
+      const int q = (warp - 3) & 3, grp = (warp - 3) >> 2;
       int pi, lt;
       tcs_proj_of(p, tile0, pi, lt);
       const TcSwapProj& pr = p.proj[pi];
       const int n = lt * BNW + q * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
       const uint32_t part = sbase + OFF_X + (uint32_t)(q * 32 + lane) * 4;
       const float bv = (pr.bias && n < pr.n_out) ? __half2float(pr.bias[n]) : 0.f;
-      tc_fence_after();
+      uint32_t remote[8];
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) {
+        remote[rr] = part;
+        if (rr < p.split) asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[rr]) : "r"(part), "r"(rr));
+      }
+      const int row0 = p.Mb * rank / p.split;
+      int row1 = p.Mb * (rank + 1) / p.split;
+      if (row1 > p.M) row1 = p.M;
 #pragma unroll 1
-      for (int c0 = 0; c0 < p.Mb; c0 += 32) {
-        uint32_t r[32];
-        tc_ld32(taddr + c0, r);
-        float acc[32];
+      for (int r0 = row0 + grp; r0 < row1; r0 += 20) {
+        float v[4][8];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(r[e]);
-        for (int rr = 1; rr < p.split; ++rr) {   // fixed order: the sum does not depend on timing
-          uint32_t remote;
-          asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(part), "r"(rr));
-          float v[32];
-          // independent loads, all in flight together (rows past M hold stale data and are never stored)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[e]) : "r"(remote + (uint32_t)(c0 + e) * (BNW * 4)));
-#pragma unroll
-          for (int e = 0; e < 32; ++e) acc[e] += v[e];
-        }
+          for (int rr = 0; rr < 8; ++rr) {
+            v[i][rr] = 0.f;
+            if (rr < p.split && r0 + 5 * i < row1)
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[i][rr]) : "r"(remote[rr] + (uint32_t)(r0 + 5 * i) * (BNW * 4)));
+          }
         if (n < pr.n_out) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (c0 + e < p.M) pr.D[(size_t)(c0 + e) * pr.ldd + n] = __float2half_rn(acc[e] + bv);
+          for (int i = 0; i < 4; ++i)
+            if (r0 + 5 * i < row1) {
+              float acc = v[i][0];
+#pragma unroll
+              for (int rr = 1; rr < 8; ++rr)
+                if (rr < p.split) acc += v[i][rr];
+              pr.D[(size_t)(r0 + 5 * i) * pr.ldd + n] = __float2half_rn(acc + bv);
+            }
         }
       }
     }
