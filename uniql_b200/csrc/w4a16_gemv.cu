@@ -558,18 +558,25 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
     const size_t word = (size_t)vb * kFuseBlockWords + (size_t)m * 32 + ((nv & 63) >> 1);
     const uint2* base = reinterpret_cast<const uint2*>(p.cv.bufs[p.cv.rank] + p.cv.reduce_off) +
                         (size_t)(ep & 1u) * p.cv.world * (size_t)p.cv.block_cap * kFuseBlockWords + word;
-    for (int r = 0; r < p.cv.world; ++r) {
-      const uint2* src = base + (size_t)r * (size_t)p.cv.block_cap * kFuseBlockWords;
-      uint4 w = gemv_ld_word2(src);
-      int spin = 0;
-      while ((w.y != ep || w.w != ep) && !wait_failed) {
-        if (++spin > kGemvSpinLimit) { wait_failed = true; break; }
-        w = gemv_ld_word2(src);
+    // the first look at every rank's words goes out together (one round trip instead of one per rank); a word that
+    // has not arrived yet is then polled on its own
+    const size_t rstride = (size_t)p.cv.block_cap * kFuseBlockWords;
+    uint4 w[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < p.cv.world) w[r] = gemv_ld_word2(base + (size_t)r * rstride);
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < p.cv.world) {
+        int spin = 0;
+        while ((w[r].y != ep || w[r].w != ep) && !wait_failed) {
+          if (++spin > kGemvSpinLimit) { wait_failed = true; break; }
+          w[r] = gemv_ld_word2(base + (size_t)r * rstride);
+        }
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[r].x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w[r].z));
+        acc4.x += a.x; acc4.y += a.y; acc4.z += b.x; acc4.w += b.y;
       }
-      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
-      acc4.x += a.x; acc4.y += a.y; acc4.z += b.x; acc4.w += b.y;
-    }
     return acc4;
   };
   // finishes output items [i0, i1) whose values `sumfn(m, col)` delivers
@@ -626,10 +633,14 @@ w4a16_gemv_kernel(const __grid_constant__ GemvParams p) {
     auto cluster_sum = [&](int m, int col) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       const uint32_t off = ctile_addr + (uint32_t)((m * cta_cols + col) * 4);
-      for (int r = 0; r < p.S_split; ++r) {
-        const float4 t4 = ld_dsmem_f4(off, (uint32_t)r);
-        v.x += t4.x; v.y += t4.y; v.z += t4.z; v.w += t4.w;
-      }
+      // all peers' tiles are requested before the first is added (2 <= S_split <= 8): one remote round trip, not S
+      float4 t4[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < p.S_split) t4[r] = ld_dsmem_f4(off, (uint32_t)r);
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < p.S_split) { v.x += t4[r].x; v.y += t4[r].y; v.z += t4[r].z; v.w += t4[r].w; }
       return v;
     };
     finish_items(i0, i1, cluster_sum);
