@@ -74,6 +74,15 @@ __device__ __forceinline__ uint2 ld_word(const uint2* p) {
   return v;
 }
 
+__device__ __forceinline__ uint4 ld_word2(const uint2* p) {   // two adjacent {data, epoch} words
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
 __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const ArParams p) {
   __shared__ uint32_t s_epoch;
   __shared__ int s_fail;
@@ -105,20 +114,36 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const ArPara
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     bool fail = false;
-    for (int r = 0; r < p.world; ++r) {
-      const uint2* slot = reinterpret_cast<const uint2*>(mine) + ((size_t)parity * p.world + r) * words_per_slot + w0;
+    // the first look at the words of four ranks goes out together (two 16-byte loads per rank: one round trip instead
+    // of sixteen); a word that has not arrived yet is then polled on its own
+    const uint2* slot0 = reinterpret_cast<const uint2*>(mine) + (size_t)parity * p.world * words_per_slot + w0;
+    for (int rb = 0; rb < p.world; rb += 4) {
+      uint4 wa[4], wb[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint2 w = ld_word(slot + i);
-        int it = 0;
-        while (w.y != epoch && !fail) {
-          if (++it > kArSpinLimit) { fail = true; break; }
-          w = ld_word(slot + i);
+      for (int j = 0; j < 4; ++j)
+        if (rb + j < p.world) {
+          wa[j] = ld_word2(slot0 + (size_t)(rb + j) * words_per_slot);
+          wb[j] = ld_word2(slot0 + (size_t)(rb + j) * words_per_slot + 2);
         }
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-        acc[2 * i] += f.x;
-        acc[2 * i + 1] += f.y;
-      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (rb + j < p.world) {
+          const uint2* slot = slot0 + (size_t)(rb + j) * words_per_slot;
+          const uint32_t d0[4] = {wa[j].x, wa[j].z, wb[j].x, wb[j].z};
+          const uint32_t e0w[4] = {wa[j].y, wa[j].w, wb[j].y, wb[j].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint2 w = make_uint2(d0[i], e0w[i]);
+            int it = 0;
+            while (w.y != epoch && !fail) {
+              if (++it > kArSpinLimit) { fail = true; break; }
+              w = ld_word(slot + i);
+            }
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+            acc[2 * i] += f.x;
+            acc[2 * i + 1] += f.y;
+          }
+        }
     }
     if (fail) s_fail = 1;
     uint4 o;
