@@ -579,8 +579,9 @@ def run_ours(args):
 
     # qkv, o, gate+up (SwiGLU in the epilogue), Hadamard, down: the cross-GPU sums and the feature gather ride in the
     # linears' epilogues, the Hadamard kernel of a tensor-parallel layer reads the gathered row directly
-    # (larger batches: q, k, v, o, gate, up, Hadamard, down on the tensor-core kernels; SiLU * up is PyTorch's)
-    launches_per_layer = 5 if m <= 16 else 8
+    # (17..128 rows: qkv, o, gate+up as one tensor-core launch, Hadamard, down; beyond that gate and up are separate
+    # launches; SiLU * up is PyTorch's above 16 rows)
+    launches_per_layer = 5 if m <= 128 else 6
     parity = None
     with torch.cuda.stream(stream):
         # ---- tensor parallel: check the sharded result before timing anything ----
