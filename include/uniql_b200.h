@@ -176,6 +176,16 @@ int uniql_w4a16_dequantize_rows(const void* packed, const void* scales, int64_t 
                                 const int32_t* row_index, int64_t k_new, int64_t n_real, void* out, int64_t ld,
                                 int* status_word, void* stream);
 
+/*
+ * out = silu(gate) * up elementwise on fp16 [rows, cols] (row strides ldg, ldu, ldo; cols and the strides multiples
+ * of 8, pointers 16-byte aligned; out may alias gate or up), with the roundings of the separate PyTorch ops (fp16 SiLU,
+ * fp16 product).  The part of down_proj(act_fn(gate_proj(x)) * up_proj(x)) (modeling/llama/llama_qblocks.py:48-51) that
+ * is left between the launches when the batch has more than 16 rows (up to 16 rows UNIQL_EPILOGUE_SWIGLU does it
+ * inside the grouped launch).  One pass instead of two; launched as a programmatic dependent of the launch before it.
+ */
+int uniql_silu_mul(const void* gate, int64_t ldg, const void* up, int64_t ldu, void* out, int64_t ldo, int64_t rows,
+                   int64_t cols, void* stream);
+
 /* Host helper: writes the base x base ±1 matrix (row-major int8) this library uses for
  * base in {12, 20, 28, 40}; `out` is a HOST pointer.  Returns UNIQL_ESHAPE for other orders. */
 int uniql_hadamard_base_matrix(int base, int8_t* out);

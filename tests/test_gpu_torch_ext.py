@@ -142,3 +142,26 @@ def test_grouped_launches_embedding_and_hadamard_equal_ctypes_path():
     assert ops.read_and_clear_status("cuda") == 0
     # the diagnostics word is the same tensor on both paths
     assert ext.status_tensor(0).data_ptr() == ops.status_word(torch.device("cuda", 0)).data_ptr()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(17, 3584), (64, 14336), (2, 5, 256), (300, 18944), (1, 8)])
+def test_silu_mul_one_pass_equals_the_two_pytorch_ops(shape):
+    """uniql_silu_mul: fp16 SiLU, fp16 product -- the values PyTorch's silu followed by mul give (one fp16 step of
+    slack for a differently rounded exponential), through both bindings, for strided inputs too."""
+    from uniql_b200 import ops
+    ext = _ext()
+    gen = torch.Generator().manual_seed(sum(shape))
+    g = (torch.randn(*shape, generator=gen) * 3).half().cuda()
+    u = (torch.randn(*shape, generator=gen) * 2).half().cuda()
+    want = torch.nn.functional.silu(g) * u
+    for got in (ops.silu_mul(g, u), ext.silu_mul(g, u)):
+        assert got.shape == want.shape and got.dtype == torch.float16
+        diff = (got.float() - want.float()).abs()
+        assert bool((diff <= 2.0 ** -9 * want.float().abs() + 1e-6).all())
+        assert float((got.float() != want.float()).float().mean()) < 0.01      # nearly always the same bits
+    wide = torch.zeros(*shape[:-1], shape[-1] + 8, dtype=torch.float16, device="cuda")
+    wide[..., :shape[-1]] = g
+    assert torch.equal(ext.silu_mul(wide[..., :shape[-1]], u), ext.silu_mul(g, u))
+    with pytest.raises(RuntimeError):
+        ext.silu_mul(g, u[..., :-1] if shape[-1] > 8 else u.float())

@@ -55,6 +55,8 @@ SYMBOLS = {
     "uniql_w4_embedding": (_c.c_int, [
         _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64,
         _c.c_void_p, _c.c_void_p]),
+    "uniql_silu_mul": (_c.c_int, [
+        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p]),
     "uniql_hadamard": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_float, _c.c_int, _c.c_void_p]),
     "uniql_hadamard_base_matrix": (_c.c_int, [_c.c_int, _c.c_void_p]),

@@ -224,6 +224,23 @@ at::Tensor embedding(const at::Tensor& ids, const at::Tensor& weight, const at::
   return out;
 }
 
+// act_fn(gate) * up between the launches of an MLP at more than 16 rows (uniql_silu_mul): one pass, PyTorch's roundings.
+at::Tensor silu_mul(const at::Tensor& gate, const at::Tensor& up) {
+  TORCH_CHECK(gate.is_cuda() && up.is_cuda() && gate.scalar_type() == at::kHalf && up.scalar_type() == at::kHalf,
+              "gate and up must be float16 CUDA tensors");
+  TORCH_CHECK(gate.sizes() == up.sizes() && gate.dim() >= 1, "gate and up must have the same shape");
+  const int64_t cols = gate.size(-1);
+  at::Tensor g2 = gate.reshape({-1, cols}), u2 = up.reshape({-1, cols});
+  if (g2.stride(1) != 1 || g2.stride(0) % 8 || ((uintptr_t)g2.data_ptr()) % 16) g2 = g2.contiguous();
+  if (u2.stride(1) != 1 || u2.stride(0) % 8 || ((uintptr_t)u2.data_ptr()) % 16) u2 = u2.contiguous();
+  const c10::cuda::CUDAGuard guard(gate.device());
+  at::Tensor out = at::empty(gate.sizes(), gate.options());
+  const int code = uniql_silu_mul(g2.data_ptr(), g2.stride(0), u2.data_ptr(), u2.stride(0), out.data_ptr(), cols, g2.size(0),
+                                  cols, at::cuda::getCurrentCUDAStream(gate.device().index()).stream());
+  check_code(code, "uniql_silu_mul");
+  return out;
+}
+
 // Hadamard.forward / had_transform (quantize/hadamard_helpers.py:18-48): y = H x * scale along the last axis.
 at::Tensor hadamard(const at::Tensor& x, double scale) {
   TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor (uniql_b200 has no CPU path)");
@@ -253,4 +270,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("linear_group", &linear_group, "grouped W4A16 decode launch");
   m.def("embedding", &embedding, "4-bit embedding gather");
   m.def("hadamard", &hadamard, "Hadamard transform along the last axis");
+  m.def("silu_mul", &silu_mul, "silu(gate) * up in one pass");
 }

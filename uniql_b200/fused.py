@@ -41,15 +41,15 @@ def gate_up_swiglu(gate_proj, up_proj, x):
         out = ext.linear_group(x, [gate_proj.weight, up_proj.weight], [gate_proj.scale, up_proj.scale],
                                [gate_proj.bias, up_proj.bias], [gate_proj.out_features, up_proj.out_features],
                                1 if fused_act else 0, None, gate_proj.pad_in, False)
-        return out[0] if fused_act else F.silu(out[0]) * out[1]
+        return out[0] if fused_act else ext.silu_mul(out[0], out[1])
     x2 = _flat(x, gate_proj)
     if x2.shape[0] <= DECODE_ROWS:
         (h,) = ops.w4a16_linear_group(x2, [_layer(gate_proj), _layer(up_proj)], epilogue="swiglu")
     elif x2.shape[0] <= GROUP_ROWS:
         g, u = ops.w4a16_linear_group(x2, [_layer(gate_proj), _layer(up_proj)])
-        h = F.silu(g) * u
+        h = ops.silu_mul(g, u)
     else:
-        h = F.silu(gate_proj(x2)) * up_proj(x2)
+        h = ops.silu_mul(gate_proj(x2), up_proj(x2))
     return h.view(*x.shape[:-1], gate_proj.out_features)
 
 

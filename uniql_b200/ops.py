@@ -272,6 +272,26 @@ def hadamard(x: torch.Tensor, scale: float) -> torch.Tensor:
     return y
 
 
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for fp16 CUDA tensors of the same shape, one pass (fp16 SiLU, fp16 product, as the two PyTorch
+    ops would round)."""
+    _require_cuda(gate, "gate"); _require_cuda(up, "up")
+    if gate.dtype != torch.float16 or up.dtype != torch.float16 or gate.shape != up.shape:
+        raise RuntimeError("gate and up must be float16 tensors of the same shape")
+    cols = gate.shape[-1]
+    g2, u2 = gate.reshape(-1, cols), up.reshape(-1, cols)
+    if g2.stride(1) != 1 or g2.stride(0) % 8 or g2.data_ptr() % 16:
+        g2 = g2.contiguous()
+    if u2.stride(1) != 1 or u2.stride(0) % 8 or u2.data_ptr() % 16:
+        u2 = u2.contiguous()
+    out = torch.empty(g2.shape, dtype=torch.float16, device=gate.device)
+    with torch.cuda.device(gate.device):
+        code = lib().uniql_silu_mul(g2.data_ptr(), g2.stride(0), u2.data_ptr(), u2.stride(0), out.data_ptr(), cols,
+                                    g2.shape[0], cols, _stream_handle(gate.device))
+    check(code, "uniql_silu_mul")
+    return out.view(gate.shape)
+
+
 def hadamard_base_matrix(base: int) -> torch.Tensor:
     """The int8 [base, base] matrix of +1 / -1 the library applies for orders 12, 20, 28 and 40 right now."""
     import ctypes
