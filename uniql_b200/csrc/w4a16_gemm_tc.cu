@@ -786,14 +786,19 @@ w4a16_gemm_tc_swap_kernel(const __grid_constant__ TcSwapParams p, const __grid_c
     const int blk_local = q >> 1;
     const int g = lane >> 2;
     // scales of 64-column block `blk_local` of tile `nt` and k-block `kblk` (zero for a block past the projection's width)
+    // (the projection of a tile is looked up when the tile changes, not per stage: this loop is latency-critical)
+    int c_nt = -1, c_lt = 0, c_N = 0;
+    const uint4* c_S = nullptr;
     auto load_scales = [&](int nt, int kblk, bool& valid) {
-      int pi, lt;
-      tcs_proj_of(p, nt, pi, lt);
-      const TcSwapProj& pr = p.proj[pi];
-      const int blk = lt * 2 + blk_local;
-      valid = blk < (pr.N >> 6);
+      if (nt != c_nt) {
+        int pi, lt;
+        tcs_proj_of(p, nt, pi, lt);
+        c_nt = nt; c_lt = lt; c_N = p.proj[pi].N; c_S = p.proj[pi].S;
+      }
+      const int blk = c_lt * 2 + blk_local;
+      valid = blk < (c_N >> 6);
       if (!valid) return make_uint2(0, 0);
-      return __ldg(reinterpret_cast<const uint2*>(pr.S + g + (size_t)blk * 8 + (size_t)kblk * (size_t)(pr.N >> 3)) + (q & 1));
+      return __ldg(reinterpret_cast<const uint2*>(c_S + g + (size_t)blk * 8 + (size_t)kblk * (size_t)(c_N >> 3)) + (q & 1));
     };
     // position of the k-block this warp converts next, and of the one after it (whose scales are requested early)
     int ti = 0, kb = set;
