@@ -1,11 +1,14 @@
-// Decode-regime W4A16 linear (m <= 16) for sm_100a: a persistent, weight-streaming skinny GEMM.
+// Decode-regime W4A16 linear (m <= 16) for sm_100a: the dispatch between the two decode kernels, the entry point that
+// needs no caller scratch, and the second of the two kernels -- a persistent, slot-balanced, weight-streaming skinny GEMM.
 //
-// Replaces the small-batch instantiations of UniQL's Marlin kernel
+// Both kernels replace the small-batch instantiations of UniQL's Marlin kernel
 // (csrc/linear/marlin_gemm_kernel.cuh:176-740, tile table :792-800) while consuming the very same
 // packed buffers (quantize/quantize_helpers.py:145-165 weight order, :54-62 scale order), and the separate
 // launches the reference's blocks make around it: gate_proj / up_proj / act_fn(gate) * up
 // (modeling/llama/llama_qblocks.py:48-51), q/k/v (:104-106), the residual add, and the online Hadamard in front of
-// down_proj / out_proj (quantize/quant_hadamard_layers.py:16-18).
+// down_proj / out_proj (quantize/quant_hadamard_layers.py:16-18).  launch_decode() sends a launch to the CTA-tiled kernel
+// of w4a16_gemv.cu (the default, and the only one that talks to other GPUs) or, with UNIQL_B200_DECODE_ENGINE=slot, to
+// the kernel below (single GPU).
 //
 // How the packed layout is consumed.  Packed row kt (16 k-values) holds, for every 64-column block,
 // 512 contiguous bytes; lane i of a warp owns bytes 16i..16i+15 = four words j=0..3.  With g = i/4 and
@@ -15,23 +18,22 @@
 // So one 16-byte load per lane feeds four tensor-core instructions per 8 batch rows with no data
 // movement between lanes, and all 16 rows of the MMA do useful work even at m = 1.
 //
-// Work split.  The unit of work is a *slot*: one quantisation group (128 k-values = 8 packed rows) of one 64-column
-// block = 4 KB of packed weights.  A launch is one CTA per SM; the T slots of all projections of the launch are
-// laid out in one fixed order and warp w of the W = SMs x warps takes slots [T w / W, T (w+1) / W): every SM streams
-// the same number of bytes (to within one slot) whatever the matrix shape.  Each warp owns a two-slot ring; one
-// elected lane fills a slot with one 2-D TMA tile (weights, landing on the slot's mbarrier: bounded wait, status bit
-// on give-up) while all lanes fetch the group's 64 scales and the m x 128 activations with 16-byte asynchronous
-// copies (one commit group per slot).
-// A run of slots of one block ends in a 64 x m fp32 tile that goes to scratch; a ticket counts the slots that have
-// arrived for the block and the warp that brings the last one adds the tiles up in a fixed order (no spinning, no
-// floating-point atomics: same bits on every run) and applies the epilogue: bias, SwiGLU product of a gate/up pair,
-// residual add, fp16 store, or the cross-GPU exchange of a tensor-parallel layer.
+// Work split of the slot kernel.  The unit of work is a *slot*: one quantisation group (128 k-values = 8 packed rows) of
+// one 64-column block = 4 KB of packed weights.  A launch is one CTA of 8..16 warps per SM; the T slots of all
+// projections of the launch are laid out in one fixed order and warp w of the W = SMs x warps takes slots
+// [T w / W, T (w+1) / W): every SM streams the same number of bytes (to within one slot) whatever the matrix shape.
+// Each warp owns a ring of two or three slots; one elected lane fills a slot with one 2-D TMA tile (weights, landing on
+// the slot's mbarrier: bounded wait, status bit on give-up) while all lanes fetch the group's 64 scales and the
+// m x 128 activations with 16-byte asynchronous copies (one commit group per slot).
+// A run of slots of one block ends in a 64 x m fp32 tile.  Tiles of a block that spans warps meet in scratch as 8-byte
+// words {two values, tag}: the word is its own ready flag, and the warp that holds the block's last slot adds the tiles
+// of the lower-numbered warps in a fixed order (bounded polls; no floating-point atomics: same bits on every run),
+// clears them, and applies the epilogue: bias, SwiGLU product of a gate/up pair, residual add, fp16 store.  For up to
+// four rows the online Hadamard transform of the activations runs in the kernel's own prologue.
 //
-// Overlap between launches.  The kernel is sized so that TWO launches fit on an SM (<= 113 KB of shared memory and
-// <= 64 K registers together).  Every launch carries the programmatic-dependent-launch attribute, fills its rings,
-// releases its own dependents and only then waits for its predecessor: while one launch drains (ticket, tile sum,
-// stores, grid completion) and the next one fetches its activations, the next one's first 100 KB per SM of weights
-// are already on their way, so HBM does not idle between dependent GEMVs.
+// Every launch carries the programmatic-dependent-launch attribute, fills its rings, releases its own dependents and only
+// then waits for its predecessor.  Measured against the tiled kernel this kernel is slower (its reduction crosses global
+// memory); it is kept as a tested alternative.
 //
 // Roofline: HBM.  Algorithmic bytes per launch = sum over projections of k*n/2 + (k/128)*n*2 + m*n_out*2, + m*k*2.
 #include "common.cuh"
@@ -55,7 +57,7 @@ constexpr int kMaxSeg = 3;             // Hadamard segments a CTA may need in th
 constexpr int kSegRowBytes = 2048;     // room per (segment, batch row) in the prologue: 512 floats
 constexpr int kSegRowStride = 1040;    // bytes between batch rows of a transformed segment (1024 + 16)
 constexpr int kMaxPrefetch = 4;
-constexpr int kSpinLimit = 1 << 22;    // polls of a word another GPU has to write before giving up
+constexpr int kSpinLimit = 1 << 22;    // polls of a tagged word another warp has to write before giving up
 
 // ------------------------------------------------------------------------------------------------ index arithmetic
 // Every divisor of the slot arithmetic is a constant of the launch, so divisions are multiplications by a reciprocal
