@@ -13,19 +13,24 @@
 // movement between lanes, and all 16 rows of the MMA do useful work even at m = 1.
 //
 // Parallelisation.  A CTA has 8 warps arranged WN (along n, adjacent 64-column blocks) x WK (along k).
-// The grid is (ceil(n/64/WN), S): S CTAs split k.  Every warp streams its own contiguous k-range with
-// a ring of 8 outstanding 16-byte loads per lane (one quantisation group ahead), L2 evict-first.
-// Group scales are applied to the fp32 group accumulator once per group (16 FMAs) instead of once per
-// weight.  Warps of a CTA are reduced through shared memory in a fixed order; CTAs along k write fp32
-// partials to scratch and the last one to arrive (atomic ticket, no spinning) adds them in a fixed
-// order -> deterministic results, no inter-CTA waits.
+// The grid is (ceil(blocks/WN), S): S CTAs split k.  Every warp streams its own contiguous k-range through a ring of
+// two or three 4 KB shared-memory slots that one elected lane fills with 2-D TMA tiles (one quantisation group of one
+// 64-column block each, L2 evict-first, no multicast; bounded mbarrier waits).  Group scales are applied to the fp32
+// group accumulator once per group (16 FMAs) instead of once per weight.  Warps of a CTA are reduced through shared
+// memory in a fixed order; CTAs along k (S <= 8) form a thread-block cluster and add up their tiles through
+// distributed shared memory, for S > 8 they write fp32 partials to scratch and the last one to arrive (atomic ticket,
+// no spinning) adds them in a fixed order -> deterministic results, no inter-CTA waits outside a cluster barrier.
+// Every launch is a programmatic dependent: it starts its weight stream, releases its own dependents and only then
+// waits for the producer of its activations.
 //
 // Grouped launches.  Up to four projections that read the same activations form one launch: their 64-column blocks
 // are laid side by side in one virtual column space (block by block for q/k/v; gate and up blocks interleaved for a
 // SwiGLU pair, so that a CTA holds a gate block and its up partner and the epilogue can form silu(gate) * up).
-// The epilogue also adds the bias and an optional residual.  This kernel serves single-GPU launches; launches that
-// exchange data with other GPUs, and the Hadamard-in-the-prologue form, use the slot-balanced kernel of
-// w4a16_decode.cu.
+// The epilogue also adds the bias and an optional residual.
+//
+// Tensor parallelism.  The same epilogue carries the cross-GPU steps of a sharded layer (CommView): the sum of a
+// row-parallel shard over the ranks and the gather of a column-parallel shard into every rank's feature area, both as
+// epoch-tagged 8-byte words stored into the consumer's memory, every wait bounded.
 //
 // Roofline: HBM.  Algorithmic bytes per launch = sum over projections of k*n/2 + (k/128)*n*2 + m*n_out*2, + m*k*2.
 #include "common.cuh"
