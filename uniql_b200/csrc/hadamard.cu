@@ -5,12 +5,17 @@
 // i = a * 2^j + b: b runs through a Sylvester-ordered Walsh-Hadamard transform, a through a fixed
 // base x base Hadamard matrix (Paley I for 12 and 20, Paley II for 28, H_2 (x) H_20 for 40).
 //
-// Many rows: one CTA per row.  hadamard_rows32_kernel (P >= 32): each thread takes 32 contiguous elements (four
+// Many rows of a 16-bit type with 128 <= P <= 512: hadamard_mma_kernel -- the base matrix (or H_16 / H_32 for a
+// power-of-two size) is applied first, to the raw inputs, as an mma.sync with a +1/-1 operand; the P-point part follows
+// in fp32; persistent CTAs prefetch the next row while they work (see the comment at the kernel).
+// Other many-row cases: one CTA per row.  hadamard_rows32_kernel (P >= 32): each thread takes 32 contiguous elements (four
 // 16-byte loads for 16-bit types), does 5 butterfly stages in registers and parks the result in a padded fp32 copy in
 // shared memory; the remaining stages run radix-8/4/2 out of shared memory (stride >= 32, bank-conflict free); the base
 // matrix is applied per column b with compile-time signs, scaled, converted and stored coalesced.  hadamard_kernel
 // (tiny transforms): 8 contiguous elements per thread, 3 register stages and up to 5 shuffle stages.
-// Few rows (decode): hadamard_split_kernel, one CTA per (segment, row).
+// Few rows (decode): hadamard_split_kernel, one CTA per (segment, row); hadamard_split_feat_kernel reads the row from a
+// tensor-parallel layer's feature area.  A base matrix replaced at run time (uniql_hadamard_set_base_matrix) is honoured
+// by every path (hadamard_rt_kernel where the signs are otherwise compiled in).
 // HBM-bound for many rows (2 * dim * sizeof(T) bytes per row); latency-bound for a single row.
 #include "common.cuh"
 #include "linear_internal.cuh"
