@@ -5,9 +5,14 @@
     python bench.py --impl reference --steps K --warmup W     # CPU dequantise + matmul (the reference's math)
 
 One step = one pass over the 32-layer stack of projections (qkv 6144x4096, o 4096x4096, gate and up
-14336x4096, down 4096x14336 with a 14336-point online Hadamard on its input) at decode batch M.
-With N > 1 the linears are tensor-parallel (column-parallel qkv/gate/up, row-parallel o/down + all-reduce).
-Prints ONE JSON line on rank 0.
+14336x4096 as one launch with the SwiGLU product in its epilogue, down 4096x14336 with a 14336-point online
+Hadamard on its input) at decode batch M, replayed from a CUDA graph.
+With N > 1 the linears are tensor-parallel (column-parallel qkv/gate/up, row-parallel o/down; the cross-GPU sums and
+the feature gather run inside the linears' own launches) and the sharded result is checked against the unsharded layer
+before anything is timed (`tp_parity`; a failure exits with code 4).
+Prints ONE JSON line on rank 0: the headline (`value`, `roofline`, `e2e`, `cpu_baseline`, `clocks`, `gpu_launches`)
+plus extra keys -- step percentiles, the same stack at 16 and 64 rows, the tensor-core kernels at 64 and 4096 rows,
+the Qwen2.5-7B and Mamba2-8B legs and the auxiliary kernels (one GPU only).
 """
 from __future__ import annotations
 
