@@ -314,6 +314,12 @@ int uniql_w4a16_linear_group_tp(void* comm, int flags, int64_t col_offset, int64
 int uniql_w4a16_plan_selftest(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t hadamard_dim,
                               int64_t k_offset, int* fused_hadamard_out);
 
+/* Host-only check of the plan the CTA-tiled decode kernel would use for a launch of this shape (no device work, usable
+ * without a GPU): the invariants its index arithmetic relies on (warp arrangement, split, shared-memory carve-up, scratch
+ * size) and that the k-ranges of its warps cover every packed row exactly once.  Returns 0, or the number of the check
+ * that failed; out5 (may be NULL) receives {WN, S, cluster (0/1), dynamic shared memory bytes, partial-sum bytes}. */
+int uniql_w4a16_gemv_plan_check(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t* out5);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,3 +55,57 @@ def test_geometries_the_kernel_refuses(built_lib):
     assert run(1, 256, [256, 128], epilogue=1) == -1   # SwiGLU pair of different widths
     assert run(1, 12160, [4096], had=12160) == -3  # no Hadamard of that size exists
     assert run(1, 1792, [4096], had=14336, koff=13000) == -3   # slice not on a group boundary / past the row
+
+
+def _tiled_plan(m, k, widths, epilogue=0):
+    import ctypes
+
+    from uniql_b200._lib import lib
+    n = (ctypes.c_int64 * len(widths))(*widths)
+    out = (ctypes.c_int64 * 5)()
+    code = lib().uniql_w4a16_gemv_plan_check(m, k, n, len(widths), epilogue, out)
+    return code, list(out)
+
+
+def _pad(n, unit=256):
+    return (n + unit - 1) // unit * unit
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 9, 16])
+def test_tiled_kernel_plans_hold_for_every_benchmarked_shard(built_lib, world, m):
+    """uniql_w4a16_gemv_plan_check (host only): the plans of the CTA-tiled decode kernel for the Llama-3.1-8B,
+    Qwen2.5-7B and Mamba2-8B projections, whole and sharded over 2, 4 and 8 ranks the way uniql_b200.tp shards them
+    (columns on 64-column blocks, rows on 128-row groups, uneven splits included)."""
+    from uniql_b200 import tp
+    cases = []
+    for hidden, inter, qkv in ((4096, 14336, 6144), (3584, 18944, 4608), (4096, 12160, 6144)):
+        col = [b - a for a, b in tp.column_bounds(_pad(inter), world)]
+        qcol = [b - a for a, b in tp.column_bounds(_pad(qkv), world)]
+        krow_o = [b - a for a, b in tp.row_bounds(_pad(hidden, 128), world)]
+        krow_d = [b - a for a, b in tp.row_bounds(_pad(inter, 128), world)]
+        for r in range(world):
+            cases.append((hidden, [qcol[r]], 0))                       # qkv shard
+            cases.append((krow_o[r], [_pad(hidden)], 0))               # o shard (row-parallel)
+            cases.append((hidden, [col[r], col[r]], 1))                # gate + up with SwiGLU
+            cases.append((hidden, [col[r]], 0))
+            cases.append((krow_d[r], [_pad(hidden)], 0))               # down shard (row-parallel)
+    cases += [(4096, [18688], 0), (8192, [4096], 0), (3584, [152064], 0), (4096, [4096, 1024, 1024], 0),
+              (3584, [3584, 512, 512], 0), (256, [256], 0), (128, [64], 0), (384, [128, 128, 64, 192], 0)]
+    seen = set()
+    for k, widths, epi in cases:
+        key = (k, tuple(widths), epi)
+        if key in seen or k <= 0 or min(widths) <= 0:
+            continue
+        seen.add(key)
+        code, (wn, s, cluster, smem, partial) = _tiled_plan(m, k, widths, epi)
+        assert code == 0, f"check {code} failed for m={m} k={k} n={widths} epilogue={epi}: WN={wn} S={s} smem={smem}"
+        assert wn in (1, 2, 4, 8) and 1 <= s <= 64 and (epi == 0 or wn >= 2)
+        assert (partial == 0) == (s == 1 or cluster == 1)
+
+
+def test_tiled_kernel_plan_check_refuses_bad_shapes(built_lib):
+    assert _tiled_plan(17, 4096, [4096])[0] == 1          # decode kernel: at most 16 rows
+    assert _tiled_plan(1, 4000, [4096])[0] == 1           # k must be a multiple of 128
+    assert _tiled_plan(1, 4096, [4096, 2048], 1)[0] == 2  # SwiGLU needs two equal widths
+    assert _tiled_plan(1, 4096, [100])[0] == 3            # widths are multiples of 64

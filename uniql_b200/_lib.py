@@ -52,6 +52,8 @@ SYMBOLS = {
     "uniql_w4a16_plan_selftest": (_c.c_int, [
         _c.c_int64, _c.c_int64, _c.POINTER(_c.c_int64), _c.c_int, _c.c_int, _c.c_int64, _c.c_int64,
         _c.POINTER(_c.c_int)]),
+    "uniql_w4a16_gemv_plan_check": (_c.c_int, [
+        _c.c_int64, _c.c_int64, _c.POINTER(_c.c_int64), _c.c_int, _c.c_int, _c.POINTER(_c.c_int64)]),
     "uniql_w4_embedding": (_c.c_int, [
         _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64,
         _c.c_void_p, _c.c_void_p]),

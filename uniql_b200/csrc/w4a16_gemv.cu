@@ -825,6 +825,52 @@ static int64_t virtual_width(const int64_t* n, int nproj) {
   return w;
 }
 
+// Host-only check of the plan a launch of this shape would get (no device work): the invariants the kernel's index
+// arithmetic relies on, and that the k-ranges of its warps tile [0, k/16) exactly once.  0, or the number of the
+// failed check; out5 (may be null) receives {WN, S, cluster, dynamic shared memory, partial bytes}.
+int gemv_plan_check(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t* out5) {
+  if (m < 1 || m > 16 || k <= 0 || k % 128 || nproj < 1 || nproj > kMaxProj) return 1;
+  const bool pair = epilogue == UNIQL_EPILOGUE_SWIGLU;
+  if (pair && (nproj != 2 || n[0] != n[1])) return 2;
+  for (int i = 0; i < nproj; ++i)
+    if (n[i] <= 0 || n[i] % 64) return 3;
+  const int64_t nv = virtual_width(n, nproj);
+  const GemvPlan pl = plan_gemv(m, nv, k, pair);
+  if (out5) { out5[0] = pl.WN; out5[1] = pl.S; out5[2] = pl.cluster; out5[3] = (int64_t)pl.smem; out5[4] = (int64_t)pl.partial_bytes; }
+  const int KT = (int)(k / 16), nblk = (int)(nv / 64);
+  if (!(pl.WN == 1 || pl.WN == 2 || pl.WN == 4 || pl.WN == 8) || pl.WN * pl.WK != kGemvWarps) return 10;
+  if (pair && pl.WN < 2) return 11;
+  if (pl.S < 1 || pl.S > KT || pl.S > 64) return 12;
+  if (pl.cluster && (pl.S < 2 || pl.S > 8)) return 13;
+  if (pl.MT != (m <= 8 ? 1 : 2) || pl.R < 1 || pl.R > 4 || pl.GCH < 1 || pl.GCH > 8) return 14;
+  if (pl.xs_rows != (int)(m < 8 * pl.MT ? m : 8 * pl.MT) + 1) return 15;
+  const int grid_x = (nblk + pl.WN - 1) / pl.WN;
+  if ((size_t)grid_x * sizeof(int) > UNIQL_SCRATCH_COUNTER_BYTES) return 16;
+  // two CTAs per SM must fit (227 KB of shared memory per SM, 1 KB reserved per CTA, the kernel's static part on top)
+  if (pl.smem > 160 * 1024 || 2 * (pl.smem + 2048) > 227 * 1024) return 17;
+  const size_t ring_bytes = (size_t)kGemvWarps * pl.R * kSlotBytes;
+  const size_t xs_bytes = (size_t)pl.WK * pl.xs_rows * (pl.GCH * 128 + kXsPad) * 2 + (size_t)pl.WK * pl.GCH * 64;
+  if (ring_bytes + xs_bytes > pl.smem) return 18;
+  if ((size_t)kGemvWarps * 8 * pl.MT * kRedStride * 4 > pl.smem) return 19;
+  if (pl.cluster && (size_t)pl.ctile_off + (size_t)m * pl.WN * 64 * 4 > pl.smem) return 20;
+  if (pl.partial_bytes != ((pl.S > 1 && !pl.cluster) ? (size_t)pl.S * (size_t)m * nv * 4 : 0)) return 21;
+  if (gemv_scratch_bytes(m, k, n, nproj, epilogue) != UNIQL_SCRATCH_COUNTER_BYTES + (pl.partial_bytes + 255) / 256 * 256)
+    return 22;
+  // the warps' k-ranges, as the kernel computes them: disjoint, in order, covering every packed row once
+  int next = 0;
+  for (int y = 0; y < pl.S; ++y) {
+    const int k0 = (int)((unsigned)KT * (unsigned)y / (unsigned)pl.S), k1 = (int)((unsigned)KT * (unsigned)(y + 1) / (unsigned)pl.S);
+    for (int wk = 0; wk < pl.WK; ++wk) {
+      const int r0 = k0 + (int)((unsigned)(k1 - k0) * (unsigned)wk / (unsigned)pl.WK);
+      const int r1 = k0 + (int)((unsigned)(k1 - k0) * (unsigned)(wk + 1) / (unsigned)pl.WK);
+      if (r0 != next || r1 < r0) return 23;
+      next = r1;
+    }
+  }
+  if (next != KT) return 24;
+  return 0;
+}
+
 size_t gemv_scratch_bytes(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue) {
   if (m < 1 || m > 16 || nproj < 1 || nproj > kMaxProj) return UNIQL_SCRATCH_COUNTER_BYTES;
   const GemvPlan plan = plan_gemv(m, virtual_width(n, nproj), k, epilogue == UNIQL_EPILOGUE_SWIGLU);
@@ -931,3 +977,8 @@ int launch_gemv_group(const DecodeArgs& a, const __half* A, int64_t lda, cudaStr
 }
 
 }  // namespace uniql
+
+extern "C" int uniql_w4a16_gemv_plan_check(int64_t m, int64_t k, const int64_t* n, int nproj, int epilogue, int64_t* out5) {
+  if (!n) return 1;
+  return uniql::gemv_plan_check(m, k, n, nproj, epilogue, out5);
+}
