@@ -1,4 +1,6 @@
 """Shared input generators for the parity tests (seeded, synthetic)."""
+import functools
+
 import numpy as np
 import torch
 
@@ -19,8 +21,11 @@ def make_acts(seed, m, k, outliers=True):
     return x.to(torch.float16)
 
 
+@functools.lru_cache(maxsize=16)
 def quantized_layer(seed, n, k, bias=False):
-    """Returns dict with packed/scales (numpy), w_deq fp16 [k, n_padded], n_pad, bias."""
+    """Returns dict with packed/scales (numpy), w_deq fp16 [k, n_padded], n_pad, bias.  The last few layers are kept:
+    parametrised tests ask for the same (seed, shape) several times and quantising a large layer on the CPU takes
+    seconds; callers treat the arrays as read-only."""
     w = make_weights(seed, n, k)
     pad_out = (256 - n % 256) % 256
     w_ref, packed, scales = orc.w4a16_quantize(np.ascontiguousarray(w.numpy().T), pad_out)

@@ -211,7 +211,7 @@ def test_sliced_llama_shapes_at_2048_rows(n, k):
                                  (3584, 18944), (512, 2048), (192, 640)])
 @pytest.mark.parametrize("m", [17, 48, 64, 100, 128])
 def test_baseline_shapes_mid_batch(n, k, m):
-    layer = quantized_layer(n + k + m, n, k, bias=(n == 1024))
+    layer = quantized_layer(n + k + 1, n, k, bias=(n == 1024))      # one layer per shape, reused for every m
     x = make_acts(m + 7, m, k)
     linear_tolerance_check(_run(layer, x), _ref(layer, x))
 
